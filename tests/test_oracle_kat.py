@@ -1,0 +1,180 @@
+"""The oracle against the known answers held by the reference's own tests.
+
+Each case names the reference test file and lines that state the expected numbers.
+"""
+import numpy as np
+import pytest
+
+from oracle import oracle
+from slang_b200 import config as C
+
+
+def _params(cfg, layers):
+    """layers: list of (W [out][in], b [out]) -> padded storage-type segment."""
+    w_off, b_off, total = C.param_layout(cfg)
+    p = np.zeros(total, dtype=np.float32)
+    for l, (w, b) in enumerate(layers):
+        w = np.asarray(w, dtype=np.float32).reshape(-1)
+        b = np.asarray(b, dtype=np.float32).reshape(-1)
+        p[w_off[l]:w_off[l] + w.size] = w
+        p[b_off[l]:b_off[l] + b.size] = b
+    return C.to_storage(p, cfg.dtype)
+
+
+def _grad_with_unit_dout(cfg, params, x, y, count=1, preset=None):
+    """Gradients for dL/dout = `dout` using the L2 loss: target = out - dout/2."""
+    w_off, b_off, total = C.param_layout(cfg)
+    grads = np.zeros(total, dtype=np.float32) if preset is None else preset
+    xs = np.tile(np.asarray(x, dtype=np.float32), (count, 1))
+    tg = np.tile(np.asarray(y, dtype=np.float32), (count, 1))
+    oracle.learn_gradient(cfg, params, grads, C.to_storage(xs, cfg.input_dtype), tg, count)
+    return grads, w_off, b_off
+
+
+def test_layout_matches_python_restatement():
+    for name in ["c1", "c2", "c3", "c4", "c5_w16", "c5_w128"]:
+        cfg = C.named_config(name)
+        assert oracle.param_layout(cfg) == C.param_layout(cfg)
+    # Appendix shapes: logical parameter counts of the benchmark configurations.
+    assert C.logical_param_count(C.named_config("c1")) == 609
+    assert C.logical_param_count(C.named_config("c2")) == 3460
+    assert C.logical_param_count(C.named_config("c3")) == 10627
+    assert C.logical_param_count(C.named_config("c4")) == 66112
+
+
+def test_ffn_forward_known_answer():
+    # tests/neural/basic-ilayer-ffn-forward-test.slang:56-68 : y = -40.5
+    cfg = C.make_config([2, 2, 1], C.F32, C.ACT_IDENTITY, loss=C.LOSS_L2_SUM)
+    p = _params(cfg, [([[2, -1], [0.5, 3]], [1, -2]), ([[-2, 4]], [0.5])])
+    y = oracle.forward(cfg, p, np.array([[1.5, -2.0]], dtype=np.float32), 1)
+    assert y.shape == (1, 1) and y[0, 0] == -40.5
+
+
+def test_ffn_backward_known_answer():
+    # tests/neural/basic-ilayer-ffn-backward-test.slang:76-93 : nine gradients for dL/dy = 1
+    cfg = C.make_config([2, 2, 1], C.F32, C.ACT_IDENTITY, loss=C.LOSS_L2_SUM)
+    p = _params(cfg, [([[2, -1], [0.5, 3]], [1, -2]), ([[-2, 4]], [0.5])])
+    g, w_off, b_off = _grad_with_unit_dout(cfg, p, [1.5, -2.0], [-40.5 - 0.5])
+    assert list(g[w_off[0]:w_off[0] + 4]) == [-3.0, 4.0, 6.0, -8.0]
+    assert list(g[b_off[0]:b_off[0] + 2]) == [-2.0, 4.0]
+    assert list(g[w_off[1]:w_off[1] + 2]) == [6.0, -7.25]
+    assert list(g[b_off[1]:b_off[1] + 1]) == [1.0]
+
+
+@pytest.mark.parametrize("dtype", [C.F32, C.F16])
+@pytest.mark.parametrize("batch", [32, 64, 128])
+def test_fflayer_batch_known_answer(dtype, batch):
+    # tests/neural/fflayer-wavetangled-vector-test.slang:95-153 : forward [39, 80]; dInput [6,8,10,12];
+    # dW = BatchSize * [[1,2,3,4],[1,2,3,4]]; dBias = [BatchSize, BatchSize].
+    # An identity first layer exposes dInput of the tested layer as that layer's bias gradient.
+    cfg = C.make_config([4, 4, 2], dtype, C.ACT_IDENTITY, loss=C.LOSS_L2_SUM)
+    p = _params(cfg, [(np.eye(4), np.zeros(4)), ([[1, 2, 3, 4], [5, 6, 7, 8]], [9, 10])])
+    x = [1.0, 2.0, 3.0, 4.0]
+    y = oracle.forward(cfg, p, C.to_storage(np.array([x], dtype=np.float32), cfg.input_dtype), 1)
+    assert list(y[0]) == [39.0, 80.0]
+    g, w_off, b_off = _grad_with_unit_dout(cfg, p, x, [39.0 - 0.5, 80.0 - 0.5], count=batch)
+    assert list(g[w_off[1]:w_off[1] + 8]) == [batch * v for v in [1, 2, 3, 4, 1, 2, 3, 4]]
+    assert list(g[b_off[1]:b_off[1] + 2]) == [batch, batch]
+    assert list(g[b_off[0]:b_off[0] + 4]) == [batch * v for v in [6, 8, 10, 12]]
+
+
+def test_activation_known_answers():
+    # tests/neural/activation-functions-test.slang:31-154
+    A = oracle.activation
+    assert [A(C.ACT_IDENTITY, 0, v) for v in (-1.0, 0.0, 2.5)] == [-1.0, 0.0, 2.5]
+    assert [A(C.ACT_RELU, 0, v) for v in (-2.0, 0.0, 3.0)] == [0.0, 0.0, 3.0]
+    np.testing.assert_allclose([A(C.ACT_LEAKY_RELU, 0.1, v) for v in (-2.0, 0.0, 3.0)], [-0.2, 0.0, 3.0], atol=1e-6)
+    np.testing.assert_allclose([A(C.ACT_SIGMOID, 0, v) for v in (0.0, 1.0, -1.0)], [0.5, 0.7310586, 0.2689414], atol=1e-3)
+    np.testing.assert_allclose([A(C.ACT_TANH, 0, v) for v in (0.0, 1.0, -1.0)], [0.0, 0.7615942, -0.7615942], atol=1e-3)
+    np.testing.assert_allclose([A(C.ACT_EXP, 0, v) for v in (0.0, 1.0, -1.0)], [1.0, 2.7182818, 0.3678794], atol=1e-3)
+    np.testing.assert_allclose([A(C.ACT_SINE, 0, v) for v in (0.0, np.pi / 2, np.pi)], [0.0, 1.0, 0.0], atol=1e-3)
+    np.testing.assert_allclose([A(C.ACT_SILU, 0, v) for v in (0.0, 1.0, -1.0)], [0.0, 0.7310586, -0.2689414], atol=1e-3)
+    np.testing.assert_allclose([A(C.ACT_QUICK_GELU, 0, v) for v in (0.0, 1.0, -1.0)], [0.0, 0.8458, -0.1542], atol=1e-3)
+
+
+def test_activation_derivatives_against_finite_differences():
+    D, A = oracle.activation_deriv, oracle.activation
+    for act in range(11):
+        for x in (-1.7, -0.3, 0.4, 2.1):
+            h = 1e-3
+            fd = (A(act, 0.01, x + h) - A(act, 0.01, x - h)) / (2 * h)
+            assert abs(D(act, 0.01, x) - fd) < 2e-3, (act, x)
+
+
+def test_max_tie_rule():
+    # source/slang/diff.meta.slang:2268-2273 : a tie in max() sends half of the gradient to each side,
+    # so ReLU = max(x, 0) has derivative 1/2 at exactly zero; the select form of LeakyReLU has 1.
+    assert oracle.activation_deriv(C.ACT_RELU, 0.0, 0.0) == 0.5
+    assert oracle.activation_deriv(C.ACT_LEAKY_RELU, 0.01, 0.0) == 1.0
+    assert abs(oracle.activation_deriv(C.ACT_LEAKY_MAX, 0.001, 0.0) - 0.5005) < 1e-6
+
+
+@pytest.mark.parametrize("acc_mode", [0, 1, 2])
+def test_coopvec_matrix_mul_bias(acc_mode):
+    # tests/cooperative-vector/matrix-mul-bias.slang:8-12 (runs on the reference's CPU target)
+    cfg = C.make_config([4, 4], C.F16, C.ACT_IDENTITY, input_dtype=C.F16)
+    p = _params(cfg, [(np.arange(1, 17).reshape(4, 4), [5, 6, 7, 8])])
+    x = C.to_storage(np.array([[1, 2, 3, 4]], dtype=np.float32), C.F16)
+    y = oracle.forward(cfg, p, x, 1, acc_mode=acc_mode)
+    assert list(y[0]) == [35.0, 76.0, 117.0, 158.0]
+
+
+def test_coopvec_outer_product_and_reduce_sum_accumulate():
+    # tests/cooperative-vector/outer-product.slang:9-41 : A=[1..4], B=[1..8], output[0] preset to 111
+    # tests/cooperative-vector/reduce-sum-accumulate.slang:9-13 : [111+1, 2, 3, 4]
+    cfg = C.make_config([8, 4], C.F16, C.ACT_IDENTITY, loss=C.LOSS_L2_SUM, input_dtype=C.F16)
+    p = _params(cfg, [(np.zeros((4, 8)), np.zeros(4))])
+    w_off, b_off, total = C.param_layout(cfg)
+    preset = np.zeros(total, dtype=np.float32)
+    preset[w_off[0]] = 111.0
+    preset[b_off[0]] = 111.0
+    # out = 0, so target = -dout/2 gives dL/dout = [1, 2, 3, 4]
+    g, _, _ = _grad_with_unit_dout(cfg, p, np.arange(1, 9), [-0.5, -1.0, -1.5, -2.0], preset=preset)
+    expect = np.outer(np.arange(1, 5), np.arange(1, 9)).astype(np.float32).reshape(-1)
+    expect[0] += 111.0
+    assert list(g[w_off[0]:w_off[0] + 32]) == list(expect)
+    assert list(g[b_off[0]:b_off[0] + 4]) == [112.0, 2.0, 3.0, 4.0]
+
+
+def test_example_float_to_half_rounds_half_up():
+    # examples/mlp-training/mlp-training.cpp:314-339
+    f2h = oracle.example_float_to_half
+    assert f2h(0.0) == 0 and f2h(1.0) == 0x3C00 and f2h(-2.0) == 0xC000
+    assert f2h(65536.0) == 0x7C00 and f2h(1e-9) == 0
+    # 1 + 2^-11 sits exactly between two halves: ties go up here, to even in IEEE.
+    assert f2h(1.0 + 2.0 ** -11) == 0x3C01
+    assert int(np.float16(1.0 + 2.0 ** -11).view(np.uint16)) == 0x3C00
+    rng = np.random.default_rng(0)
+    for v in rng.uniform(-1, 1, 200).astype(np.float32):
+        got = np.array([f2h(float(v))], dtype=np.uint16).view(np.float16)[0]
+        assert abs(float(got) - float(v)) <= 2.0 ** -11 * max(abs(float(v)), 2.0 ** -14)
+
+
+def test_example_kernels_quirks():
+    # examples/mlp-training/mlp_sw.slang:22-24 vs 35-39: negatives are scaled by 0.001 going forward
+    # but their gradients by 0.01 going back; kernels.slang:22-27: the loss word is a running max.
+    params = np.zeros(192, dtype=np.float16)
+    grads = np.zeros(192, dtype=np.float16)
+    # layer 1 (16x4) at 0, bias at 64; layer 2 (4x16) at 96, bias at 160 (64-byte sub-allocations of halfs)
+    w1 = params[0:64].reshape(16, 4); b1 = params[64:80]
+    w2 = params[96:160].reshape(4, 16); b2 = params[160:164]
+    w1[0, 0] = -1.0
+    w2[0, 0] = 1.0
+    base_p, base_g = params.ctypes.data, grads.ctypes.data
+    net = np.array([[base_p + 0, base_g + 0, base_p + 128, base_g + 128],
+                    [base_p + 192, base_g + 192, base_p + 320, base_g + 320]], dtype=np.uint64)
+    loss = np.zeros(2, dtype=np.uint32)
+    x = np.array([[0.5, 0.25]], dtype=np.float32)
+    oracle.example_learn_gradient(net, loss, x, 1)
+    h = np.float16(-0.5) * np.float16(0.001)
+    out0 = np.float16(h * np.float16(0.001))      # layer 2 applies the same leaky step to its own negative output
+    gt0 = np.float16((0.5 + 0.25) / (1 + 0.25 * 0.25))
+    diff0 = np.float16(out0 - gt0)
+    g_out0 = np.float16(diff0 + diff0)           # out0 < 0, so the backward slope applies
+    g_out0 = np.float16(g_out0 * np.float16(0.01))
+    assert grads[160] == g_out0
+    assert grads[96] == np.float16(g_out0 * h)
+    assert loss[0] > 0
+    before = int(loss[0])
+    oracle.example_learn_gradient(net, loss, np.zeros((1, 2), dtype=np.float32), 1)
+    assert int(loss[0]) == before  # a smaller loss does not lower the word
