@@ -1,0 +1,147 @@
+/*
+ * C ABI of the B200 small-MLP training step.
+ *
+ * The reference's example host loop (examples/mlp-training/mlp-training.cpp:92-214) talks to the GPU
+ * through slang-rhi: create a device, load two compute kernels by name, create buffers, clear them,
+ * dispatch a kernel with one packed argument struct and a grid size, wait, read a buffer back.  Each
+ * function below stands in for one of those calls, so a copy of that loop can be compiled against
+ * this header instead of slang-rhi.  Kernels are prebuilt for sm_100a; nothing is compiled at run time.
+ *
+ * Conventions (include/slang.h:1377-1426 of the reference): every function returns an int32 result,
+ * 0 on success and negative on failure; no exceptions cross the boundary; the text of the last failure
+ * on the calling thread is available from mlp_last_error_string().  Handles are opaque and are
+ * destroyed explicitly.  A device handle owns one in-order CUDA stream (or borrows the caller's);
+ * calls on one device handle are not thread-safe, which matches the example's single host thread and
+ * single queue (mlp-training.cpp:174).
+ */
+#ifndef SLANG_B200_MLP_H
+#define SLANG_B200_MLP_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#include "slang_b200_mlp_config.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MLP_OK 0
+#define MLP_FAIL (-1)             /* SLANG_FAIL */
+#define MLP_E_INVALID_ARG (-2)    /* SLANG_E_INVALID_ARG */
+#define MLP_E_NOT_AVAILABLE (-3)  /* SLANG_E_NOT_AVAILABLE: no kernel of that name / unsupported shape */
+#define MLP_E_CUDA (-4)           /* a CUDA call failed; see mlp_last_error_string() */
+#define MLP_E_DEVICE_STATUS (-5)  /* a kernel gave up on a bounded wait and set its status word */
+
+typedef struct MlpDevice MlpDevice;
+typedef struct MlpBuffer MlpBuffer;
+typedef struct MlpKernel MlpKernel;
+
+/* ---- argument structs packed by the host, one per entry point ------------------------------- */
+
+/* learnGradient of the literal example: LearnGradParams (mlp-training.cpp:55-61), 28 bytes used. */
+typedef struct MlpLearnGradParams {
+    uint64_t networkBuffer; /* device address of MlpLayerPointers[n_layers] */
+    uint64_t lossBuffer;    /* device address of two 32-bit words, cleared by the host every step */
+    uint64_t inputs;        /* device address of the inputs */
+    uint32_t count;         /* samples */
+} MlpLearnGradParams;
+
+/* adjustParameters: AdjustParamsParams (mlp-training.cpp:63-69), 28 bytes used. */
+typedef struct MlpAdjustParamsParams {
+    uint64_t adamStates;
+    uint64_t params;
+    uint64_t gradients;
+    uint32_t count; /* elements of the padded parameter segment */
+} MlpAdjustParamsParams;
+
+/* learnGradient of the configurable path: the example's struct plus a targets address, because the
+ * benchmark configurations read their targets from a buffer instead of computing a closed form
+ * inside the kernel (examples/mlp-training/network.slang:49-58 is the closed form of the example). */
+typedef struct MlpLearnGradParamsEx {
+    uint64_t networkBuffer;
+    uint64_t lossBuffer; /* word 0: float bits of the largest per-sample loss (unsigned max);
+                            word 1: float sum of the per-sample losses (atomic add) */
+    uint64_t inputs;
+    uint64_t targets;
+    uint32_t count;
+    uint32_t flags; /* MLP_FLAG_* */
+} MlpLearnGradParamsEx;
+
+/* forward only: outputs are fp32 [count][dims[n_layers]]. */
+typedef struct MlpForwardParams {
+    uint64_t networkBuffer;
+    uint64_t inputs;
+    uint64_t outputs;
+    uint32_t count;
+    uint32_t flags;
+} MlpForwardParams;
+
+/* Gradient sums in ascending sample order, one add at a time, as the reference's CPU target runs
+ * them (source/slang/slang-emit-cpp.cpp:2210-2284): bit-identical to a sequential machine, slow. */
+#define MLP_FLAG_SEQUENTIAL_SUM 1u
+
+/* ---- device ------------------------------------------------------------------------------- */
+
+/* rhi::getRHI()->createDevice (mlp-training.cpp:96-100).  `ordinal` is the CUDA device index. */
+int32_t mlp_device_create(int32_t ordinal, MlpDevice** out_device);
+/* Same, but work is issued on an existing CUDA stream (a cudaStream_t passed as a pointer) so that
+ * the caller's own stream-ordered work (copies, collectives) interleaves with the kernels. */
+int32_t mlp_device_create_on_stream(int32_t ordinal, void* cuda_stream, MlpDevice** out_device);
+int32_t mlp_device_destroy(MlpDevice* device);
+/* queue->waitOnHost() (mlp-training.cpp:207).  Also reports a pending device status word. */
+int32_t mlp_wait(MlpDevice* device);
+
+/* ---- buffers ------------------------------------------------------------------------------ */
+
+/* createBuffer(size, initData) (mlp-training.cpp:271-280): device-local, optional initial contents. */
+int32_t mlp_buffer_create(MlpDevice* device, size_t size, const void* init_data, MlpBuffer** out_buffer);
+/* Adopts device memory owned by the caller (for example a tensor of a host framework). */
+int32_t mlp_buffer_wrap(MlpDevice* device, uint64_t device_address, size_t size, MlpBuffer** out_buffer);
+int32_t mlp_buffer_destroy(MlpBuffer* buffer);
+/* IBuffer::getDeviceAddress() (mlp-training.cpp:148).  Stable for the buffer's lifetime. */
+uint64_t mlp_buffer_address(const MlpBuffer* buffer);
+/* clearBuffer(buffer[, range]) (mlp-training.cpp:282-289): zero fill, stream ordered. */
+int32_t mlp_buffer_clear(MlpDevice* device, MlpBuffer* buffer, size_t offset, size_t size);
+/* gDevice->readBuffer(buffer, offset, size, blob) (mlp-training.cpp:208): waits for prior work. */
+int32_t mlp_buffer_read(MlpDevice* device, const MlpBuffer* buffer, size_t offset, size_t size, void* dst);
+int32_t mlp_buffer_write(MlpDevice* device, MlpBuffer* buffer, size_t offset, size_t size, const void* src);
+
+/* ---- kernels ------------------------------------------------------------------------------ */
+
+/* loadComputeProgram / findEntryPointByName (mlp-training.cpp:291-312): the literal example's entry
+ * points "learnGradient" and "adjustParameters" (examples/mlp-training/kernels.slang:8-41). */
+int32_t mlp_kernel_get(MlpDevice* device, const char* entry_point, MlpKernel** out_kernel);
+/* The same entry points specialised for a problem description, the way the reference specialises
+ * FeedForwardLayer<In, Out> at compile time.  entry_point is one of
+ *   "learnGradient"      args MlpLearnGradParamsEx   (fastest implementation for the shape)
+ *   "learnGradient_simt" args MlpLearnGradParamsEx   (one thread per sample, any shape)
+ *   "adjustParameters"   args MlpAdjustParamsParams  (MlpAdamState per element, fp32 gradients)
+ *   "forward"            args MlpForwardParams
+ *   "forward_simt"       args MlpForwardParams */
+int32_t mlp_kernel_get_for_config(MlpDevice* device, const MlpConfig* config, const char* entry_point,
+                                  MlpKernel** out_kernel);
+int32_t mlp_kernel_destroy(MlpKernel* kernel);
+/* Name of the implementation a kernel handle resolved to ("simt", "tcgen05", ...). */
+const char* mlp_kernel_implementation(const MlpKernel* kernel);
+
+/* dispatchKernel (mlp-training.cpp:252-268): bind, setData(offset 0, &args, size), dispatchCompute.
+ * The host passes the grid it would give a [numthreads(256,1,1)] kernel, ceil(count / 256); kernels
+ * that are persistent size their own grid and treat the argument as a hint. */
+int32_t mlp_dispatch(MlpDevice* device, MlpKernel* kernel, const void* args, size_t args_size,
+                     uint32_t grid_x, uint32_t grid_y, uint32_t grid_z);
+/* Number of CUDA kernels launched through this device handle since it was created. */
+uint64_t mlp_device_launch_count(const MlpDevice* device);
+
+/* ---- host-side layout helpers ------------------------------------------------------------- */
+
+/* allocateNetworkParameterStorage (mlp-training.cpp:217-250) in elements of the storage type:
+ * w_off / b_off receive n_layers entries, total the padded element count of one segment. */
+int32_t mlp_param_layout(const MlpConfig* config, int64_t* w_off, int64_t* b_off, int64_t* total);
+
+const char* mlp_last_error_string(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,35 @@
+// Host-side launch functions implemented by the kernel translation units and called by the C ABI.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <string>
+
+#include "../../include/slang_b200_mlp.h"
+
+namespace mlpb200 {
+
+// One-thread-per-sample kernels (simt_kernels.cu).
+cudaError_t launch_example_learn_gradient(cudaStream_t st, const MlpLearnGradParams& a, uint32_t grid);
+cudaError_t launch_example_adjust_parameters(cudaStream_t st, const MlpAdjustParamsParams& a, uint32_t grid);
+cudaError_t launch_forward_simt(cudaStream_t st, const MlpConfig& c, const MlpForwardParams& a, int* launches,
+                                std::string* err);
+cudaError_t launch_learn_gradient_simt(cudaStream_t st, const MlpConfig& c, const MlpLearnGradParamsEx& a,
+                                       float* seq_scratch, int* launches, std::string* err);
+size_t sequential_scratch_floats_per_sample(const MlpConfig& c);
+cudaError_t launch_adjust_parameters(cudaStream_t st, const MlpConfig& c, const MlpAdjustParamsParams& a, int* launches);
+
+// Tensor-core kernels (tc_kernels.cu).  tc_supported() says whether the shape is one they are built for.
+bool tc_forward_supported(const MlpConfig& c);
+bool tc_train_supported(const MlpConfig& c);
+struct TcWorkspace;  // per-device state: status word, SM count, tensor maps cache
+TcWorkspace* tc_workspace_create(int device_ordinal, std::string* err);
+void tc_workspace_destroy(TcWorkspace* ws);
+cudaError_t launch_forward_tc(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const MlpForwardParams& a,
+                              int* launches, std::string* err);
+cudaError_t launch_learn_gradient_tc(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c,
+                                     const MlpLearnGradParamsEx& a, int* launches, std::string* err);
+// Reads and clears the device status word (0 = no kernel gave up on a bounded wait).
+cudaError_t tc_read_status(cudaStream_t st, TcWorkspace* ws, uint32_t* status);
+
+}  // namespace mlpb200

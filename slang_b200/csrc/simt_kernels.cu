@@ -1,0 +1,513 @@
+// One-thread-per-sample kernels: the literal example entry points and the shape-generic path.
+//
+// These keep the reference's dispatch contract exactly: [numthreads(256,1,1)], thread id =
+// blockIdx.x * blockDim.x + threadIdx.x, grid = ceil(count / 256)
+// (examples/mlp-training/kernels.slang:8-41, examples/mlp-training/mlp-training.cpp:181-204).
+// They serve every shape and number format; the tensor-core kernels take over for the shapes they
+// are built for.  This file is compiled with -fmad=false: every multiply and add is separately
+// rounded unless fmaf is written out, so fp32 results match a sequential CPU bit for bit.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <string>
+
+#include "mlp_common.cuh"
+#include "launchers.h"
+
+namespace mlpb200 {
+
+// ------------------------------------------------------------------------------------------------
+// The literal example: 4 -> 16 -> 4 in half (examples/mlp-training/{kernels,network,mlp_sw,mlvec_sw}.slang).
+// Every half operation is rounded on its own, as IEEE half arithmetic does.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ __half hmul_(__half a, __half b) { return __float2half_rn(__half2float(a) * __half2float(b)); }
+__device__ __forceinline__ __half hadd_(__half a, __half b) { return __float2half_rn(__half2float(a) + __half2float(b)); }
+__device__ __forceinline__ __half hsub_(__half a, __half b) { return __float2half_rn(__half2float(a) - __half2float(b)); }
+__device__ __forceinline__ __half hdiv_(__half a, __half b) { return __float2half_rn(__fdiv_rn(__half2float(a), __half2float(b))); }
+__device__ __forceinline__ bool hneg_(__half a) { return __half2float(a) < 0.0f; }
+
+template <int In, int Out>
+__device__ void ex_layer_eval(const MlpLayerPointers& lp, const __half* x, __half* y)
+{
+    const __half* W = (const __half*)lp.weights;
+    const __half* B = (const __half*)lp.biases;
+    for (int i = 0; i < Out; ++i) {
+        __half r = B[i];
+        for (int j = 0; j < In; ++j) r = hadd_(r, hmul_(W[i * In + j], x[j]));
+        y[i] = r;
+    }
+    const __half slope = __float2half_rn(0.001f);
+    for (int i = 0; i < Out; ++i)
+        if (hneg_(y[i])) y[i] = hmul_(y[i], slope);
+}
+
+// Backward of one layer for one sample.  The per-sample weight- and bias-gradient terms are left in
+// shared memory (g and x) for the ordered block-level sum; dx = W^T g.
+template <int In, int Out>
+__device__ void ex_layer_bwd(const MlpLayerPointers& lp, const __half* x, __half* g, __half* dx)
+{
+    __half fwd[Out];
+    ex_layer_eval<In, Out>(lp, x, fwd);
+    const __half slope = __float2half_rn(0.01f);
+    for (int i = 0; i < Out; ++i)
+        if (hneg_(fwd[i])) g[i] = hmul_(g[i], slope);
+    const __half* W = (const __half*)lp.weights;
+    for (int i = 0; i < In; ++i) {
+        __half r = __float2half_rn(0.0f);
+        for (int j = 0; j < Out; ++j) r = hadd_(r, hmul_(W[j * In + i], g[j]));
+        dx[i] = r;
+    }
+}
+
+// Atomic half add through a 32-bit compare-and-swap on the containing word
+// (the job of InterlockedAddF16Emulated, source/slang/hlsl.meta.slang:34654-34667).
+__device__ void atomic_add_half(__half* addr, __half v)
+{
+    unsigned int* word = (unsigned int*)((uintptr_t)addr & ~(uintptr_t)3);
+    const bool hi = ((uintptr_t)addr & 2) != 0;
+    unsigned int old = *word, assumed;
+    do {
+        assumed = old;
+        unsigned short cur = hi ? (unsigned short)(assumed >> 16) : (unsigned short)(assumed & 0xffffu);
+        __half sum = hadd_(__ushort_as_half(cur), v);
+        unsigned int repl = hi ? ((assumed & 0x0000ffffu) | ((unsigned int)__half_as_ushort(sum) << 16))
+                               : ((assumed & 0xffff0000u) | (unsigned int)__half_as_ushort(sum));
+        old = atomicCAS(word, assumed, repl);
+    } while (old != assumed);
+}
+
+// Ordered sum over the block's samples of g[s][i] * x[s][j] (half, one rounding per multiply and per
+// add, ascending sample order), then one atomic per element per block.  With a single block (the
+// example runs 16 samples) the result is what a sequential machine produces.
+template <int In, int Out>
+__device__ void ex_accumulate(const MlpLayerPointers& lp, const __half* sg, const __half* sx, int n_valid, int gstride,
+                              int xstride)
+{
+    __half* dW = (__half*)lp.weightsGrad;
+    __half* dB = (__half*)lp.biasesGrad;
+    const bool single = gridDim.x == 1;
+    for (int p = threadIdx.x; p < In * Out + Out; p += blockDim.x) {
+        const bool is_w = p < In * Out;
+        const int i = is_w ? p / In : p - In * Out, j = is_w ? p % In : 0;
+        __half* dst = is_w ? dW + p : dB + i;
+        // A single block continues from the stored value, like the sequential machine; several
+        // blocks each sum their own samples first and then add once.
+        __half acc = single ? *dst : __float2half_rn(0.0f);
+        bool first = !single;
+        for (int s = 0; s < n_valid; ++s) {
+            const __half term = is_w ? hmul_(sg[s * gstride + i], sx[s * xstride + j]) : sg[s * gstride + i];
+            acc = first ? term : hadd_(acc, term);
+            first = false;
+        }
+        if (single) *dst = acc;
+        else if (n_valid > 0) atomic_add_half(dst, acc);
+    }
+}
+
+extern "C" __global__ void __launch_bounds__(256)
+learnGradient(const MlpLayerPointers* __restrict__ network, uint32_t* lossBuffer, const float2* __restrict__ inputs,
+              uint32_t count)
+{
+    // Per-sample vectors staged for the ordered sums: encoding (4), layer-1 output (16), g2 (4), g1 (16).
+    __shared__ __half s_enc[256 * 4];
+    __shared__ __half s_h1[256 * 16];
+    __shared__ __half s_g2[256 * 4];
+    __shared__ __half s_g1[256 * 16];
+
+    const uint32_t tid = blockIdx.x * blockDim.x + threadIdx.x;
+    const bool valid = tid < count;
+    const MlpLayerPointers L1 = network[0], L2 = network[1];
+    float this_loss = 0.0f;
+    if (valid) {
+        const float2 in = inputs[tid];
+        const __half x = __float2half_rn(in.x), y = __float2half_rn(in.y);
+        __half enc[4] = {x, y, hmul_(x, x), hmul_(y, y)};
+        __half h1[16], out[4], g2[4], g1[16], dead[4];
+        ex_layer_eval<4, 16>(L1, enc, h1);
+        ex_layer_eval<16, 4>(L2, h1, out);
+        const __half one = __float2half_rn(1.0f), half_ = __float2half_rn(0.5f);
+        __half gt[4];
+        gt[0] = hdiv_(hadd_(x, y), hadd_(one, hmul_(y, y)));
+        gt[1] = hadd_(hmul_(__float2half_rn(2.0f), x), y);
+        gt[2] = hadd_(hmul_(hmul_(half_, x), x), hmul_(__float2half_rn(1.2f), y));
+        gt[3] = hadd_(x, hmul_(hmul_(half_, y), y));
+        __half l = __float2half_rn(0.0f);
+        for (int k = 0; k < 4; ++k) {
+            const __half d = hsub_(out[k], gt[k]);
+            g2[k] = hadd_(hmul_(d, one), hmul_(d, one));
+            l = hadd_(l, hmul_(d, d));
+        }
+        this_loss = __half2float(l);
+        ex_layer_bwd<16, 4>(L2, h1, g2, g1);
+        ex_layer_bwd<4, 16>(L1, enc, g1, dead);
+        for (int k = 0; k < 4; ++k) { s_enc[threadIdx.x * 4 + k] = enc[k]; s_g2[threadIdx.x * 4 + k] = g2[k]; }
+        for (int k = 0; k < 16; ++k) { s_h1[threadIdx.x * 16 + k] = h1[k]; s_g1[threadIdx.x * 16 + k] = g1[k]; }
+    }
+    __syncthreads();
+    const int first = blockIdx.x * blockDim.x;
+    const int n_valid = count > (uint32_t)first ? min((int)blockDim.x, (int)(count - first)) : 0;
+    ex_accumulate<16, 4>(L2, s_g2, s_h1, n_valid, 4, 16);
+    ex_accumulate<4, 16>(L1, s_g1, s_enc, n_valid, 16, 4);
+
+    // WaveActiveMax, then the first lane folds the wave's value into the loss word.
+    float m = this_loss;
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((threadIdx.x & 31) == 0 && first + (int)(threadIdx.x) < (int)count) atomicMax(lossBuffer, __float_as_uint(m));
+}
+
+extern "C" __global__ void __launch_bounds__(256)
+adjustParameters(MlpExampleAdamState* states, __half* params, __half* gradients, uint32_t count)
+{
+    const uint32_t tid = blockIdx.x * blockDim.x + threadIdx.x;
+    if (tid >= count) return;
+    __half g = gradients[tid];
+    if (__hisnan(g)) { gradients[tid] = __float2half_rn(0.0f); return; }
+    const __half beta1 = __float2half_rn(0.9f), beta2 = __float2half_rn(0.999f);
+    const __half eps = __float2half_rn(1e-7f), lr = __float2half_rn(0.01f), one = __float2half_rn(1.0f);
+    MlpExampleAdamState st = states[tid];
+    st.iteration++;
+    if (__hisinf(g)) g = __float2half_rn(__half2float(g) > 0.0f ? 10000.0f : -10000.0f);
+    __half m = __ushort_as_half(st.mean), v = __ushort_as_half(st.variance);
+    m = hadd_(hmul_(beta1, m), hmul_(hsub_(one, beta1), g));
+    v = hadd_(hmul_(beta2, v), hmul_(hmul_(hsub_(one, beta2), g), g));
+    const __half it = __float2half_rn((float)st.iteration);
+    const __half p1 = __float2half_rn(powf(__half2float(beta1), __half2float(it)));
+    const __half p2 = __float2half_rn(powf(__half2float(beta2), __half2float(it)));
+    const __half mean_hat = hdiv_(m, hsub_(one, p1));
+    const __half var_hat = hdiv_(v, hsub_(one, p2));
+    const __half mx = __half2float(var_hat) > 0.0f ? var_hat : __float2half_rn(0.0f);
+    const __half den = __float2half_rn(__fsqrt_rn(__half2float(hadd_(mx, eps))));
+    __half p = params[tid];
+    p = hsub_(p, hdiv_(hmul_(lr, mean_hat), den));
+    params[tid] = p;
+    st.mean = __half_as_ushort(m);
+    st.variance = __half_as_ushort(v);
+    states[tid] = st;
+    gradients[tid] = __float2half_rn(0.0f);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Shape-generic path: any MlpConfig within the scratch limits, one thread per sample.
+// ------------------------------------------------------------------------------------------------
+constexpr int kMaxActFloats = 768;  // sum of all layer widths a thread may hold
+
+struct SimtNet {
+    MlpConfig cfg;
+    int a_off[MLP_MAX_LAYERS + 2];  // offset of the vector entering layer l in the per-thread arrays
+};
+
+__device__ __forceinline__ void encode_input(const MlpConfig& c, const void* inputs, int64_t s, float* a0)
+{
+    if (c.encoding == MLP_ENC_FREQ2D) {
+        for (int u = 0; u < 2; ++u) {
+            const float v = load_as_f32(c.input_dtype, inputs, s * 2 + u);
+            for (int k = 0; k < 8; ++k) {
+                const float arg = ldexpf(3.14159265358979323846f, k) * v;
+                a0[u * 16 + k * 2 + 0] = round_to(c.dtype, sinf(arg));
+                a0[u * 16 + k * 2 + 1] = round_to(c.dtype, cosf(arg));
+            }
+        }
+    } else {
+        for (int i = 0; i < c.dims[0]; ++i)
+            a0[i] = round_to(c.dtype, load_as_f32(c.input_dtype, inputs, s * c.dims[0] + i));
+    }
+}
+
+// Forward of one sample; a holds every layer's input vector, z every pre-activation (both rounded to
+// the storage type); the last slot of a holds the fp32 outputs.
+__device__ void simt_forward(const SimtNet& net, const MlpLayerPointers* __restrict__ lp, const void* inputs, int64_t s,
+                             float* a, float* z)
+{
+    const MlpConfig& c = net.cfg;
+    encode_input(c, inputs, s, a);
+    for (int l = 0; l < c.n_layers; ++l) {
+        const int in = c.dims[l], out = c.dims[l + 1];
+        const bool last = (l == c.n_layers - 1);
+        const float* ain = a + net.a_off[l];
+        float* aout = a + net.a_off[l + 1];
+        float* zl = z + net.a_off[l + 1] - net.a_off[1];
+        const void* W = (const void*)lp[l].weights;
+        const void* B = (const void*)lp[l].biases;
+        for (int j = 0; j < out; ++j) {
+            float r = load_as_f32(c.dtype, B, j);
+            for (int i = 0; i < in; ++i) r = fmaf(load_as_f32(c.dtype, W, int64_t(j) * in + i), ain[i], r);
+            const float zs = round_to(c.dtype, r);
+            zl[j] = zs;
+            aout[j] = last ? act_value(c.output_act, c.act_alpha, zs)
+                           : round_to(c.dtype, act_value(c.hidden_act, c.act_alpha, zs));
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256)
+forward_simt_kernel(SimtNet net, const MlpLayerPointers* __restrict__ lp, const void* __restrict__ inputs,
+                    float* __restrict__ outputs, uint32_t count)
+{
+    const uint32_t tid = blockIdx.x * blockDim.x + threadIdx.x;
+    if (tid >= count) return;
+    float a[kMaxActFloats], z[kMaxActFloats];
+    simt_forward(net, lp, inputs, tid, a, z);
+    const int od = net.cfg.dims[net.cfg.n_layers];
+    const float* o = a + net.a_off[net.cfg.n_layers];
+    for (int j = 0; j < od; ++j) outputs[int64_t(tid) * od + j] = o[j];
+}
+
+// learnGradient, generic.  Phase A (per thread): forward, loss, backward; every layer's input vector
+// a_l and output gradient dz_l stay in the per-thread arrays.  Phase B (per block): for each layer the
+// block stages `group` samples' (dz_l, a_l) in shared memory and each thread owns a strided set of
+// parameters, summing its terms over the staged samples in ascending order before one atomic add per
+// parameter per group.  With MLP_FLAG_SEQUENTIAL_SUM the per-sample vectors go to a global scratch
+// area instead and a second kernel adds them one sample at a time.
+__global__ void __launch_bounds__(256)
+learn_gradient_simt_kernel(SimtNet net, const MlpLayerPointers* __restrict__ lp, uint32_t* lossBuffer,
+                           const void* __restrict__ inputs, const void* __restrict__ targets, uint32_t count,
+                           int group, float* __restrict__ seq_scratch)
+{
+    extern __shared__ float smem[];
+    const MlpConfig& c = net.cfg;
+    const int nl = c.n_layers;
+    const uint32_t tid = blockIdx.x * blockDim.x + threadIdx.x;
+    const bool valid = tid < count;
+    float a[kMaxActFloats];   // inputs of every layer; outputs in the last slot
+    float zd[kMaxActFloats];  // pre-activations going forward, overwritten by dz going backward
+    float loss = 0.0f;
+    const int od = c.dims[nl];
+    if (valid) {
+        simt_forward(net, lp, inputs, tid, a, zd);
+        const float scale = (c.loss == MLP_LOSS_MSE_MEAN) ? 1.0f / float(od) : 1.0f;
+        const float* o = a + net.a_off[nl];
+        float* dzl = zd + net.a_off[nl] - net.a_off[1];
+        for (int j = 0; j < od; ++j) {
+            const float t = load_as_f32(c.target_dtype, targets, int64_t(tid) * od + j);
+            const float diff = o[j] - t;
+            loss = fmaf(diff * scale, diff, loss);
+            const float dout = (2.0f * scale) * diff;
+            const float d = act_deriv(c.output_act, c.act_alpha, dzl[j]);
+            dzl[j] = round_to(c.dtype, dout * d);
+        }
+        for (int l = nl - 1; l >= 1; --l) {
+            const int in = c.dims[l], out = c.dims[l + 1];
+            const float* dz = zd + net.a_off[l + 1] - net.a_off[1];
+            float* zprev = zd + net.a_off[l] - net.a_off[1];
+            const void* W = (const void*)lp[l].weights;
+            for (int i = 0; i < in; ++i) {
+                float r = 0.0f;
+                for (int j = 0; j < out; ++j) r = fmaf(load_as_f32(c.dtype, W, int64_t(j) * in + i), dz[j], r);
+                const float d = round_to(c.dtype, act_deriv(c.hidden_act, c.act_alpha, zprev[i]));
+                zprev[i] = round_to(c.dtype, r * d);
+            }
+        }
+    }
+
+    // Loss words: wave max folded in by the first lane; block sum added once.
+    {
+        float m = loss;
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        float sum = loss;
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if ((threadIdx.x & 31) == 0) {
+            if (blockIdx.x * blockDim.x + (threadIdx.x & ~31u) < count) atomicMax(lossBuffer, __float_as_uint(m));
+            atomicAdd((float*)(lossBuffer + 1), sum);
+        }
+    }
+
+    if (seq_scratch) {
+        // Layout per sample: [a of all layers (a_off[nl] floats)][dz of all layers (a_off[nl+1]-a_off[1] floats)].
+        if (valid) {
+            const int na = net.a_off[nl], nz = net.a_off[nl + 1] - net.a_off[1];
+            float* dst = seq_scratch + int64_t(tid) * (na + nz);
+            for (int i = 0; i < na; ++i) dst[i] = a[i];
+            for (int i = 0; i < nz; ++i) dst[na + i] = zd[i];
+        }
+        return;
+    }
+
+    const int first = blockIdx.x * blockDim.x;
+    const int n_block = count > (uint32_t)first ? min((int)blockDim.x, (int)(count - first)) : 0;
+    for (int l = 0; l < nl; ++l) {
+        const int in = c.dims[l], out = c.dims[l + 1];
+        const float* al = a + net.a_off[l];
+        const float* dz = zd + net.a_off[l + 1] - net.a_off[1];
+        float* dW = (float*)lp[l].weightsGrad;
+        float* dB = (float*)lp[l].biasesGrad;
+        const int stride = in + out;
+        for (int g0 = 0; g0 < n_block; g0 += group) {
+            const int gn = min(group, n_block - g0);
+            __syncthreads();
+            const int local = (int)threadIdx.x - g0;
+            if (local >= 0 && local < gn) {
+                float* row = smem + local * stride;
+                for (int i = 0; i < in; ++i) row[i] = al[i];
+                for (int j = 0; j < out; ++j) row[in + j] = dz[j];
+            }
+            __syncthreads();
+            for (int p = threadIdx.x; p < in * out + out; p += blockDim.x) {
+                float acc = 0.0f;
+                if (p < in * out) {
+                    const int j = p / in, i = p % in;
+                    for (int s = 0; s < gn; ++s) acc = fmaf(smem[s * stride + in + j], smem[s * stride + i], acc);
+                    atomicAdd(dW + p, acc);
+                } else {
+                    const int j = p - in * out;
+                    for (int s = 0; s < gn; ++s) acc += smem[s * stride + in + j];
+                    atomicAdd(dB + j, acc);
+                }
+            }
+        }
+    }
+}
+
+// Second pass of the sequential mode: one thread per parameter walks the samples in ascending order,
+// exactly the adds a sequential machine performs (load, fused multiply-add, store).
+__global__ void __launch_bounds__(256)
+sequential_sum_kernel(SimtNet net, const MlpLayerPointers* __restrict__ lp, const float* __restrict__ scratch,
+                      uint32_t count, int layer)
+{
+    const MlpConfig& c = net.cfg;
+    const int in = c.dims[layer], out = c.dims[layer + 1];
+    const int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= in * out + out) return;
+    const int nl = c.n_layers;
+    const int na = net.a_off[nl], nz = net.a_off[nl + 1] - net.a_off[1];
+    const int64_t stride = na + nz;
+    const float* abase = scratch + net.a_off[layer];
+    const float* zbase = scratch + na + net.a_off[layer + 1] - net.a_off[1];
+    if (p < in * out) {
+        const int j = p / in, i = p % in;
+        float* dst = (float*)lp[layer].weightsGrad + p;
+        float acc = *dst;
+        for (uint32_t s = 0; s < count; ++s) acc = fmaf(zbase[s * stride + j], abase[s * stride + i], acc);
+        *dst = acc;
+    } else {
+        const int j = p - in * out;
+        float* dst = (float*)lp[layer].biasesGrad + j;
+        float acc = *dst;
+        for (uint32_t s = 0; s < count; ++s) acc += zbase[s * stride + j];
+        *dst = acc;
+    }
+}
+
+// adjustParameters, fp32 state (examples/mlp-training/adam.slang:21-37 widened to float):
+// NaN gradient -> zero it and skip; +-inf -> +-10000; eps inside the square root; gradient zeroed.
+__global__ void __launch_bounds__(256)
+adjust_parameters_kernel(MlpConfig c, MlpAdamState* __restrict__ states, void* __restrict__ params,
+                         float* __restrict__ grads, uint32_t count)
+{
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    float g = grads[i];
+    if (isnan(g)) { grads[i] = 0.0f; return; }
+    float4 raw = reinterpret_cast<float4*>(states)[i];
+    float mean = raw.x, var = raw.y;
+    int32_t it = __float_as_int(raw.z) + 1;
+    if (isinf(g)) g = g > 0.0f ? 10000.0f : -10000.0f;
+    mean = c.beta1 * mean + (1.0f - c.beta1) * g;
+    var = c.beta2 * var + ((1.0f - c.beta2) * g) * g;
+    const float mean_hat = __fdiv_rn(mean, 1.0f - pow_int(c.beta1, it));
+    const float var_hat = __fdiv_rn(var, 1.0f - pow_int(c.beta2, it));
+    float p = c.adam_master ? raw.w : load_as_f32(c.dtype, params, i);
+    const float denom = __fsqrt_rn(fmaxf(0.0f, var_hat) + c.eps);
+    p = p - __fdiv_rn(c.lr * mean_hat, denom);
+    reinterpret_cast<float4*>(states)[i] = make_float4(mean, var, __int_as_float(it), p);
+    store_from_f32(c.dtype, params, i, p);
+    grads[i] = 0.0f;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Host launchers
+// ------------------------------------------------------------------------------------------------
+static bool make_simt_net(const MlpConfig& c, SimtNet* net, std::string* err)
+{
+    net->cfg = c;
+    int off = 0;
+    for (int l = 0; l <= c.n_layers; ++l) { net->a_off[l] = off; off += c.dims[l]; }
+    net->a_off[c.n_layers + 1] = off;
+    if (off > kMaxActFloats) {
+        if (err) *err = "sum of layer widths exceeds the per-thread limit of the one-thread-per-sample kernels";
+        return false;
+    }
+    return true;
+}
+
+cudaError_t launch_example_learn_gradient(cudaStream_t st, const MlpLearnGradParams& a, uint32_t grid)
+{
+    learnGradient<<<grid, 256, 0, st>>>((const MlpLayerPointers*)a.networkBuffer, (uint32_t*)a.lossBuffer,
+                                        (const float2*)a.inputs, a.count);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_example_adjust_parameters(cudaStream_t st, const MlpAdjustParamsParams& a, uint32_t grid)
+{
+    adjustParameters<<<grid, 256, 0, st>>>((MlpExampleAdamState*)a.adamStates, (__half*)a.params, (__half*)a.gradients,
+                                           a.count);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_forward_simt(cudaStream_t st, const MlpConfig& c, const MlpForwardParams& a, int* launches,
+                                std::string* err)
+{
+    SimtNet net;
+    if (!make_simt_net(c, &net, err)) return cudaErrorInvalidValue;
+    if (a.count == 0) return cudaSuccess;
+    const uint32_t grid = (a.count + 255) / 256;
+    forward_simt_kernel<<<grid, 256, 0, st>>>(net, (const MlpLayerPointers*)a.networkBuffer, (const void*)a.inputs,
+                                              (float*)a.outputs, a.count);
+    *launches += 1;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_learn_gradient_simt(cudaStream_t st, const MlpConfig& c, const MlpLearnGradParamsEx& a,
+                                       float* seq_scratch, int* launches, std::string* err)
+{
+    SimtNet net;
+    if (!make_simt_net(c, &net, err)) return cudaErrorInvalidValue;
+    if (a.count == 0) return cudaSuccess;
+    int max_stride = 0;
+    for (int l = 0; l < c.n_layers; ++l) max_stride = std::max(max_stride, c.dims[l] + c.dims[l + 1]);
+    const int budget = 96 * 1024;
+    int group = budget / (max_stride * 4);
+    group = std::min(256, group / 32 * 32);
+    if (group < 32) {
+        if (err) *err = "layer too wide for the one-thread-per-sample kernel's staging buffer";
+        return cudaErrorInvalidValue;
+    }
+    const size_t smem = size_t(group) * max_stride * 4;
+    {
+        cudaError_t e = cudaFuncSetAttribute(learn_gradient_simt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, budget);
+        if (e != cudaSuccess) return e;
+    }
+    const uint32_t grid = (a.count + 255) / 256;
+    const bool seq = (a.flags & MLP_FLAG_SEQUENTIAL_SUM) != 0;
+    learn_gradient_simt_kernel<<<grid, 256, smem, st>>>(net, (const MlpLayerPointers*)a.networkBuffer,
+                                                        (uint32_t*)a.lossBuffer, (const void*)a.inputs,
+                                                        (const void*)a.targets, a.count, group,
+                                                        seq ? seq_scratch : nullptr);
+    *launches += 1;
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess || !seq) return e;
+    for (int l = 0; l < c.n_layers; ++l) {
+        const int np = c.dims[l] * c.dims[l + 1] + c.dims[l + 1];
+        sequential_sum_kernel<<<(np + 255) / 256, 256, 0, st>>>(net, (const MlpLayerPointers*)a.networkBuffer,
+                                                                seq_scratch, a.count, l);
+        *launches += 1;
+    }
+    return cudaGetLastError();
+}
+
+size_t sequential_scratch_floats_per_sample(const MlpConfig& c)
+{
+    size_t n = 0;
+    for (int l = 0; l < c.n_layers; ++l) n += size_t(c.dims[l]) + size_t(c.dims[l + 1]);
+    return n;
+}
+
+cudaError_t launch_adjust_parameters(cudaStream_t st, const MlpConfig& c, const MlpAdjustParamsParams& a, int* launches)
+{
+    if (a.count == 0) return cudaSuccess;
+    adjust_parameters_kernel<<<(a.count + 255) / 256, 256, 0, st>>>(c, (MlpAdamState*)a.adamStates, (void*)a.params,
+                                                                   (float*)a.gradients, a.count);
+    *launches += 1;
+    return cudaGetLastError();
+}
+
+}  // namespace mlpb200

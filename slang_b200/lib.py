@@ -1,0 +1,74 @@
+"""Loads the C-ABI shared library and declares its entry points for ctypes.
+
+There is no fallback: if the library has not been built, or no sm_100 device is present when a device
+handle is requested, the caller gets an exception.
+"""
+import ctypes
+import os
+
+from .config import MlpConfig
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libslang_b200_mlp.so")
+
+# Every symbol include/slang_b200_mlp.h declares.
+EXPORTS = [
+    "mlp_device_create", "mlp_device_create_on_stream", "mlp_device_destroy", "mlp_wait",
+    "mlp_buffer_create", "mlp_buffer_wrap", "mlp_buffer_destroy", "mlp_buffer_address", "mlp_buffer_clear",
+    "mlp_buffer_read", "mlp_buffer_write",
+    "mlp_kernel_get", "mlp_kernel_get_for_config", "mlp_kernel_destroy", "mlp_kernel_implementation",
+    "mlp_dispatch", "mlp_device_launch_count", "mlp_param_layout", "mlp_last_error_string",
+]
+
+_lib = None
+
+
+class MlpError(RuntimeError):
+    def __init__(self, code, text):
+        super().__init__("mlp error %d: %s" % (code, text))
+        self.code = code
+
+
+def load():
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError("%s is missing: run `python -m slang_b200.build` (there is no fallback path)" % LIB_PATH)
+    L = ctypes.CDLL(LIB_PATH)
+    vp, u64, u32, i32, sz = ctypes.c_void_p, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_int32, ctypes.c_size_t
+    pp = ctypes.POINTER(ctypes.c_void_p)
+    L.mlp_device_create.argtypes = [i32, pp]
+    L.mlp_device_create_on_stream.argtypes = [i32, vp, pp]
+    L.mlp_device_destroy.argtypes = [vp]
+    L.mlp_wait.argtypes = [vp]
+    L.mlp_buffer_create.argtypes = [vp, sz, vp, pp]
+    L.mlp_buffer_wrap.argtypes = [vp, u64, sz, pp]
+    L.mlp_buffer_destroy.argtypes = [vp]
+    L.mlp_buffer_address.argtypes = [vp]
+    L.mlp_buffer_address.restype = u64
+    L.mlp_buffer_clear.argtypes = [vp, vp, sz, sz]
+    L.mlp_buffer_read.argtypes = [vp, vp, sz, sz, vp]
+    L.mlp_buffer_write.argtypes = [vp, vp, sz, sz, vp]
+    L.mlp_kernel_get.argtypes = [vp, ctypes.c_char_p, pp]
+    L.mlp_kernel_get_for_config.argtypes = [vp, ctypes.POINTER(MlpConfig), ctypes.c_char_p, pp]
+    L.mlp_kernel_destroy.argtypes = [vp]
+    L.mlp_kernel_implementation.argtypes = [vp]
+    L.mlp_kernel_implementation.restype = ctypes.c_char_p
+    L.mlp_dispatch.argtypes = [vp, vp, vp, sz, u32, u32, u32]
+    L.mlp_device_launch_count.argtypes = [vp]
+    L.mlp_device_launch_count.restype = u64
+    L.mlp_param_layout.argtypes = [ctypes.POINTER(MlpConfig), ctypes.POINTER(ctypes.c_int64),
+                                   ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64)]
+    L.mlp_last_error_string.restype = ctypes.c_char_p
+    for name in EXPORTS:
+        fn = getattr(L, name)
+        if fn.restype is ctypes.c_int:
+            fn.restype = i32
+    _lib = L
+    return L
+
+
+def check(rc):
+    if rc != 0:
+        raise MlpError(rc, load().mlp_last_error_string().decode("utf-8", "replace"))

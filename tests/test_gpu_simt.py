@@ -1,0 +1,214 @@
+"""GPU parity of the one-thread-per-sample kernels against the CPU oracle, through the C ABI."""
+import ctypes
+
+import numpy as np
+import pytest
+
+from oracle import oracle
+from slang_b200 import config as C
+
+from mlp_testlib import gpu_trajectory, layer_rel_errs, make_problem, oracle_trajectory, rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def device():
+    from slang_b200.api import Device
+    d = Device(0)
+    yield d
+    d.destroy()
+
+
+def test_c1_sequential_sum_is_bit_exact(device):
+    """fp32 2-16-16-16-1, batch 4096, 100 steps with a fresh seeded batch each step.
+    With the sequential-sum flag the GPU performs the same rounded operations in the same order as the
+    oracle, so parameters, gradients and Adam states agree bit for bit (bar: 1e-5 relative)."""
+    cfg, p0, batches = make_problem("c1", 4096, seed=0, steps=100)
+    p_ref, l_ref, g_ref, s_ref = oracle_trajectory(cfg, p0, batches)
+    from slang_b200.api import FLAG_SEQUENTIAL_SUM
+    p_gpu, l_gpu, g_gpu, s_gpu, _ = gpu_trajectory(device, cfg, p0, batches, "learnGradient_simt", FLAG_SEQUENTIAL_SUM)
+    assert np.array_equal(g_gpu.view(np.uint32), g_ref.view(np.uint32))
+    assert np.array_equal(p_gpu.view(np.uint32), p_ref.view(np.uint32))
+    assert np.array_equal(s_gpu["iteration"], s_ref["iteration"])
+    for (mg, sg), (mr, sr) in zip(l_gpu, l_ref):
+        assert mg == mr
+        assert abs(sg - sr) <= 1e-5 * abs(sr)
+
+
+def test_c1_block_sum_within_bar(device):
+    """Same run with the fast block-level sums and one atomic per parameter per block:
+    parameters within 1e-5 relative after 100 steps (per tensor, relative to its largest magnitude)."""
+    cfg, p0, batches = make_problem("c1", 4096, seed=0, steps=100)
+    p_ref, l_ref, g_ref, _ = oracle_trajectory(cfg, p0, batches)
+    p64, _, _, _ = oracle_trajectory(cfg, p0, batches, acc_mode=1)
+    p_gpu, l_gpu, g_gpu, _, _ = gpu_trajectory(device, cfg, p0, batches, "learnGradient_simt")
+    errs = layer_rel_errs(cfg, p_gpu, p_ref)
+    errs64 = layer_rel_errs(cfg, p_gpu, p64)
+    print("c1 block-sum: worst per-tensor rel err vs fp32 oracle %.3g, vs fp64-accumulate oracle %.3g" % (max(errs), max(errs64)))
+    assert rel_err(g_gpu, g_ref) < 1e-5
+    assert max(errs) < 1e-5
+
+
+@pytest.mark.parametrize("name,count,steps", [("c2", 2048, 10), ("c3", 1024, 10), ("c4", 512, 6)])
+def test_16bit_configs_simt(device, name, count, steps):
+    """fp16 / bf16 configurations: per-step loss within 1e-2 relative, final parameters within 2e-2
+    relative (per tensor, relative to its largest magnitude)."""
+    cfg, p0, batches = make_problem(name, count, seed=3, steps=steps)
+    p_ref, l_ref, g_ref, _ = oracle_trajectory(cfg, p0, batches)
+    p_gpu, l_gpu, g_gpu, _, _ = gpu_trajectory(device, cfg, p0, batches, "learnGradient_simt")
+    assert rel_err(g_gpu, g_ref) < 1e-2
+    for (mg, sg), (mr, sr) in zip(l_gpu, l_ref):
+        assert abs(sg - sr) <= 1e-2 * abs(sr)
+        assert abs(mg - mr) <= 1e-2 * abs(mr)
+    errs = layer_rel_errs(cfg, C.from_storage(p_gpu, cfg.dtype), C.from_storage(p_ref, cfg.dtype))
+    print(name, "worst per-tensor rel err", max(errs))
+    assert max(errs) < 2e-2
+
+
+@pytest.mark.parametrize("count", [0, 1, 31, 32, 33, 255, 256, 257])
+def test_ragged_batches(device, count):
+    cfg, p0, batches = make_problem("c1", count, seed=5, steps=1)
+    _, l_ref, g_ref, _ = oracle_trajectory(cfg, p0, batches)
+    from slang_b200.api import FLAG_SEQUENTIAL_SUM
+    _, l_gpu, g_gpu, _, _ = gpu_trajectory(device, cfg, p0, batches, "learnGradient_simt", FLAG_SEQUENTIAL_SUM)
+    assert np.array_equal(g_gpu.view(np.uint32), g_ref.view(np.uint32))
+    assert l_gpu[0][0] == l_ref[0][0]
+    _, _, g_fast, _, _ = gpu_trajectory(device, cfg, p0, batches, "learnGradient_simt")
+    if count:
+        assert rel_err(g_fast, g_ref) < 1e-5
+    else:
+        assert not g_fast.any()
+
+
+def test_reference_known_answers_on_gpu(device):
+    """tests/neural/basic-ilayer-ffn-backward-test.slang:76-93 and
+    tests/neural/fflayer-wavetangled-vector-test.slang:95-153 through the GPU kernels."""
+    from slang_b200.api import Trainer
+    cfg = C.make_config([2, 2, 1], C.F32, C.ACT_IDENTITY, loss=C.LOSS_L2_SUM)
+    w_off, b_off, total = C.param_layout(cfg)
+    p = np.zeros(total, dtype=np.float32)
+    p[w_off[0]:w_off[0] + 4] = [2, -1, 0.5, 3]; p[b_off[0]:b_off[0] + 2] = [1, -2]
+    p[w_off[1]:w_off[1] + 2] = [-2, 4]; p[b_off[1]] = 0.5
+    tr = Trainer(device, cfg, p, learn_entry="learnGradient_simt", forward_entry="forward_simt")
+    x = device.create_buffer(8, np.array([1.5, -2.0], dtype=np.float32))
+    t = device.create_buffer(4, np.array([-41.0], dtype=np.float32))
+    y = device.create_buffer(4)
+    tr.forward(x.address, y.address, 1)
+    assert y.read(np.float32)[0] == -40.5
+    tr.learn_gradient(x.address, t.address, 1)
+    g = tr.read_grads()
+    assert list(g[w_off[0]:w_off[0] + 4]) == [-3.0, 4.0, 6.0, -8.0]
+    assert list(g[b_off[0]:b_off[0] + 2]) == [-2.0, 4.0]
+    assert list(g[w_off[1]:w_off[1] + 2]) == [6.0, -7.25]
+    assert g[b_off[1]] == 1.0
+
+    for dtype in (C.F32, C.F16):
+        for batch in (32, 64, 128):
+            cfg = C.make_config([4, 4, 2], dtype, C.ACT_IDENTITY, loss=C.LOSS_L2_SUM)
+            w_off, b_off, total = C.param_layout(cfg)
+            p = np.zeros(total, dtype=np.float32)
+            p[w_off[0]:w_off[0] + 16] = np.eye(4).reshape(-1)
+            p[w_off[1]:w_off[1] + 8] = np.arange(1, 9); p[b_off[1]:b_off[1] + 2] = [9, 10]
+            tr = Trainer(device, cfg, C.to_storage(p, dtype), learn_entry="learnGradient_simt")
+            xs = np.tile(np.array([1, 2, 3, 4], dtype=np.float32), (batch, 1))
+            ts = np.tile(np.array([38.5, 79.5], dtype=np.float32), (batch, 1))
+            xb = device.create_buffer(xs.nbytes, xs); tb = device.create_buffer(ts.nbytes, ts)
+            tr.learn_gradient(xb.address, tb.address, batch)
+            g = tr.read_grads()
+            assert list(g[w_off[1]:w_off[1] + 8]) == [batch * v for v in [1, 2, 3, 4, 1, 2, 3, 4]]
+            assert list(g[b_off[1]:b_off[1] + 2]) == [batch, batch]
+            assert list(g[b_off[0]:b_off[0] + 4]) == [batch * v for v in [6, 8, 10, 12]]
+
+
+def test_adam_guards(device):
+    """examples/mlp-training/kernels.slang:35-39, adam.slang:24-30: a NaN gradient is zeroed and the
+    element skipped (iteration not advanced); an infinite gradient is clamped to +-10000."""
+    from slang_b200.api import Trainer
+    cfg = C.named_config("c1")
+    _, _, total = C.param_layout(cfg)
+    p0 = C.init_params(cfg, seed=9)
+    tr = Trainer(device, cfg, p0)
+    g = np.zeros(total, dtype=np.float32)
+    g[0], g[1], g[2], g[3] = np.nan, np.inf, -np.inf, 0.25
+    tr.grads.write(g)
+    tr.adjust_parameters()
+    device.wait()
+    states = np.zeros(total, dtype=C.ADAM_STATE_DTYPE); states["master"] = p0
+    p_ref = p0.copy(); g_ref = g.copy()
+    oracle.adjust_parameters(cfg, states, p_ref, g_ref)
+    s_gpu = tr.read_states()
+    assert s_gpu["iteration"][0] == 0 and s_gpu["iteration"][1] == 1
+    assert np.array_equal(tr.read_params().view(np.uint32), p_ref.view(np.uint32))
+    assert not tr.read_grads().any()
+    assert np.array_equal(s_gpu["mean"].view(np.uint32), states["mean"].view(np.uint32))
+
+
+def test_example_entry_points_match_oracle(device):
+    """The literal example (examples/mlp-training/mlp-training.cpp:106-212): srand(1072), parameters
+    uniform in [-1,1] through the host's floatToHalf, 16 samples, learnGradient then adjustParameters."""
+    from slang_b200.api import AdjustParamsParams, LearnGradParams
+    libc = ctypes.CDLL("libc.so.6")
+    libc.srand(1072)
+    RAND_MAX = 2147483647
+    n_elems = 384  # both segments, halfs: 16x4|16|4x16|4 with 64-byte sub-allocations, twice
+    init = np.zeros(n_elems, dtype=np.uint16)
+    for i in range(192):
+        v = np.float32(libc.rand() / np.float32(RAND_MAX))
+        init[i] = oracle.example_float_to_half(float(np.float32(v * np.float32(2.0) - np.float32(1.0))))
+    inputs = np.array([libc.rand() / np.float32(RAND_MAX) for _ in range(32)], dtype=np.float32)
+    offs = [(0, 128), (192, 320)]  # byte offsets of (weights, bias) per layer inside a segment
+    steps = 200
+
+    # oracle on host memory
+    host = init.copy()
+    base = host.ctypes.data
+    net = np.array([[base + w, base + 384 + w, base + b, base + 384 + b] for w, b in offs], dtype=np.uint64)
+    st = np.zeros(192, dtype=C.EXAMPLE_ADAM_STATE_DTYPE)
+    ref_losses = []
+    for k in range(steps):
+        loss = np.zeros(2, dtype=np.uint32)
+        oracle.example_learn_gradient(net, loss, inputs, 16)
+        oracle.example_adjust_parameters(st, host[:192], host[192:], 192)
+        ref_losses.append(int(loss[0]))
+
+    buf = device.create_buffer(init.nbytes, init)
+    states = device.create_buffer(192 * 8)
+    netd = np.array([[buf.address + w, buf.address + 384 + w, buf.address + b, buf.address + 384 + b] for w, b in offs], dtype=np.uint64)
+    netb = device.create_buffer(netd.nbytes, netd)
+    inb = device.create_buffer(inputs.nbytes, inputs)
+    lossb = device.create_buffer(8)
+    k_learn, k_adjust = device.kernel("learnGradient"), device.kernel("adjustParameters")
+    gpu_losses = []
+    for k in range(steps):
+        lossb.clear()
+        k_learn.dispatch(LearnGradParams(netb.address, lossb.address, inb.address, 16), 1)
+        k_adjust.dispatch(AdjustParamsParams(states.address, buf.address, buf.address + 384, 192), 1)
+        gpu_losses.append(int(lossb.read(np.uint32)[0]))
+    got = buf.read(np.uint16)
+    same = np.count_nonzero(got[:192] == host[:192])
+    print("example: %d of 192 parameters bit-identical after %d steps" % (same, steps))
+    a = got[:192].view(np.float16).astype(np.float32); b = host[:192].view(np.float16).astype(np.float32)
+    assert np.max(np.abs(a - b)) <= 2e-2 * np.max(np.abs(b))
+    assert gpu_losses[0] == ref_losses[0]
+    lg = np.array(gpu_losses, dtype=np.uint32).view(np.float32); lr = np.array(ref_losses, dtype=np.uint32).view(np.float32)
+    assert np.all(np.abs(lg - lr) <= 5e-2 * np.maximum(np.abs(lr), 1e-3))
+
+
+def test_argument_errors(device):
+    from slang_b200.api import LearnGradParamsEx
+    from slang_b200.lib import MlpError
+    cfg = C.named_config("c1")
+    with pytest.raises(MlpError):
+        device.kernel("noSuchEntryPoint", cfg)
+    bad = C.named_config("c1"); bad.n_layers = 0
+    with pytest.raises(MlpError):
+        device.kernel("learnGradient", bad)
+    k = device.kernel("learnGradient_simt", cfg)
+    with pytest.raises(MlpError):   # grid does not cover the batch
+        k.dispatch(LearnGradParamsEx(1, 1, 1, 1, 1000, 0), 1)
+    with pytest.raises(MlpError):   # null addresses
+        k.dispatch(LearnGradParamsEx(0, 0, 0, 0, 16, 0), 1)
+    b = device.create_buffer(16)
+    with pytest.raises(MlpError):
+        b.clear(8, 16)
