@@ -1,0 +1,100 @@
+"""GPU parity of the tensor-core learnGradient (64-128-128-128-128-64) against the CPU oracle and
+against the one-thread-per-sample kernel, through the C ABI."""
+import numpy as np
+import pytest
+
+from slang_b200 import config as C
+
+from mlp_testlib import gpu_trajectory, layer_rel_errs, make_problem, oracle_trajectory, rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def device():
+    from slang_b200.api import Device
+    d = Device(0)
+    yield d
+    d.destroy()
+
+
+def _grad_layer_errs(cfg, g, g_ref):
+    return max(layer_rel_errs(cfg, g, g_ref))
+
+
+def test_c4_kernel_is_tensor_core(device):
+    k = device.kernel("learnGradient", C.named_config("c4"))
+    assert k.implementation == "tcgen05"
+    assert device.kernel("learnGradient_simt", C.named_config("c4")).implementation == "simt"
+
+
+@pytest.mark.parametrize("count", [64, 1, 63, 65, 100, 512, 4096 + 17])
+def test_c4_gradients_match_oracle(device, count):
+    """One learnGradient: gradients per tensor within 1e-2 of the oracle (relative to the tensor's
+    largest magnitude), loss words within 1e-2 relative."""
+    cfg, p0, batches = make_problem("c4", count, seed=11, steps=1)
+    _, l_ref, g_ref, _ = oracle_trajectory(cfg, p0, batches, n_threads=8)
+    _, l_gpu, g_gpu, _, tr = gpu_trajectory(device, cfg, p0, batches)
+    assert tr.k_learn.implementation == "tcgen05"
+    err = _grad_layer_errs(cfg, g_gpu, g_ref)
+    print("c4 count=%d worst per-tensor gradient rel err %.3g; loss gpu %s ref %s" % (count, err, l_gpu[0], l_ref[0]))
+    assert err < 1e-2
+    assert abs(l_gpu[0][1] - l_ref[0][1]) <= 1e-2 * abs(l_ref[0][1])
+    assert abs(l_gpu[0][0] - l_ref[0][0]) <= 1e-2 * abs(l_ref[0][0])
+
+
+def test_c4_many_tiles_per_cta(device):
+    """More tiles than SMs, so every CTA accumulates several tiles in tensor memory, plus a ragged tail."""
+    count = 64 * 148 * 3 + 5
+    cfg, p0, batches = make_problem("c4", count, seed=12, steps=1)
+    _, l_ref, g_ref, _ = oracle_trajectory(cfg, p0, batches, n_threads=8)
+    _, l_gpu, g_gpu, _, _ = gpu_trajectory(device, cfg, p0, batches)
+    err = _grad_layer_errs(cfg, g_gpu, g_ref)
+    print("c4 count=%d worst per-tensor gradient rel err %.3g" % (count, err))
+    assert err < 1e-2
+    assert abs(l_gpu[0][1] - l_ref[0][1]) <= 1e-2 * abs(l_ref[0][1])
+
+
+def test_c4_trajectory(device):
+    """bf16 bar: per-step loss within 1e-2 relative, final parameters within 2e-2 relative."""
+    cfg, p0, batches = make_problem("c4", 2048, seed=13, steps=8)
+    p_ref, l_ref, _, _ = oracle_trajectory(cfg, p0, batches, n_threads=8)
+    p_gpu, l_gpu, _, _, _ = gpu_trajectory(device, cfg, p0, batches)
+    for (mg, sg), (mr, sr) in zip(l_gpu, l_ref):
+        assert abs(sg - sr) <= 1e-2 * abs(sr)
+    errs = layer_rel_errs(cfg, C.from_storage(p_gpu, cfg.dtype), C.from_storage(p_ref, cfg.dtype))
+    print("c4 trajectory: worst per-tensor parameter rel err %.3g" % max(errs))
+    assert max(errs) < 2e-2
+
+
+def test_c4_tensor_core_matches_simt_on_large_batch(device):
+    """2^17 samples: too many for the scalar oracle in a test, so the tensor-core kernel is checked
+    against the one-thread-per-sample kernel (itself pinned to the oracle), and the gradient of the
+    whole batch against the sum of the gradients of its two halves."""
+    from slang_b200.api import Trainer
+    count = 1 << 17
+    cfg = C.named_config("c4")
+    p0 = C.init_params(cfg, seed=21, scheme="xavier")
+    rng = np.random.default_rng(5)
+    x = C.to_storage(rng.normal(size=(count, 64)).astype(np.float32), C.BF16)
+    t = C.to_storage(rng.normal(size=(count, 64)).astype(np.float32) * 0.3, C.BF16)
+    xb = device.create_buffer(x.nbytes, x); tb = device.create_buffer(t.nbytes, t)
+    tr_tc = Trainer(device, cfg, p0)
+    tr_simt = Trainer(device, cfg, p0, learn_entry="learnGradient_simt")
+    tr_tc.learn_gradient(xb.address, tb.address, count)
+    tr_simt.learn_gradient(xb.address, tb.address, count)
+    g_tc, g_simt = tr_tc.read_grads(), tr_simt.read_grads()
+    err = _grad_layer_errs(cfg, g_tc, g_simt)
+    print("c4 2^17: tensor-core vs one-thread-per-sample gradient rel err %.3g" % err)
+    assert err < 1e-2
+    l_tc, l_simt = tr_tc.read_loss(), tr_simt.read_loss()
+    assert abs(l_tc[1] - l_simt[1]) <= 1e-3 * abs(l_simt[1])
+    assert abs(l_tc[0] - l_simt[0]) <= 1e-2 * abs(l_simt[0])
+    # additivity over a split of the batch
+    tr_tc.grads.clear()
+    half = count // 2
+    tr_tc.learn_gradient(xb.address, tb.address, half)
+    tr_tc.k_learn.dispatch(__import__("slang_b200.api", fromlist=["LearnGradParamsEx"]).LearnGradParamsEx(
+        tr_tc.network.address, tr_tc.loss.address, xb.address + half * 128, tb.address + half * 128, half, 0), (half + 255) // 256)
+    g_split = tr_tc.read_grads()
+    assert _grad_layer_errs(cfg, g_split, g_tc) < 1e-4

@@ -178,3 +178,43 @@ def test_example_kernels_quirks():
     before = int(loss[0])
     oracle.example_learn_gradient(net, loss, np.zeros((1, 2), dtype=np.float32), 1)
     assert int(loss[0]) == before  # a smaller loss does not lower the word
+
+
+def test_example_half_arithmetic_rounds_every_operation():
+    """The example oracle must round each half operation on its own (IEEE half arithmetic), not keep
+    float intermediates: checked against a numpy float16 restatement of one sample."""
+    rng = np.random.default_rng(1)
+    params = rng.uniform(-1, 1, 192).astype(np.float16)
+    grads = np.zeros(192, dtype=np.float16)
+    P = params.copy()
+    bp, bg = P.ctypes.data, grads.ctypes.data
+    net = np.array([[bp, bg, bp + 128, bg + 128], [bp + 192, bg + 192, bp + 320, bg + 320]], dtype=np.uint64)
+    loss = np.zeros(2, dtype=np.uint32)
+    oracle.example_learn_gradient(net, loss, np.array([[0.3, 0.8]], dtype=np.float32), 1)
+    h = np.float16
+
+    def layer(W, b, xv, n_in, n_out):
+        y = []
+        for i in range(n_out):
+            r = h(b[i])
+            for j in range(n_in):
+                r = h(r + h(W[i * n_in + j] * xv[j]))
+            y.append(r)
+        return [h(v * h(0.001)) if v < 0 else v for v in y]
+
+    x, y = h(0.3), h(0.8)
+    enc = [x, y, h(x * x), h(y * y)]
+    h1 = layer(params[0:64], params[64:80], enc, 4, 16)
+    out = layer(params[96:160], params[160:164], h1, 16, 4)
+    gt = [h(h(x + y) / h(h(1) + h(y * y))), h(h(h(2) * x) + y),
+          h(h(h(h(0.5) * x) * x) + h(h(1.2) * y)), h(x + h(h(h(0.5) * y) * y))]
+    d = [h(out[k] - gt[k]) for k in range(4)]
+    g2 = [h(d[k] + d[k]) for k in range(4)]
+    g2 = [h(g2[k] * h(0.01)) if out[k] < 0 else g2[k] for k in range(4)]
+    dW2 = np.array([h(g2[i] * h1[j]) for i in range(4) for j in range(16)], dtype=np.float16)
+    assert np.array_equal(dW2.view(np.uint16), grads[96:160].view(np.uint16))
+    assert np.array_equal(np.array(g2, dtype=np.float16).view(np.uint16), grads[160:164].view(np.uint16))
+    total = h(0)
+    for k in range(4):
+        total = h(total + h(d[k] * d[k]))
+    assert np.float32(total) == loss[:1].view(np.float32)[0]
