@@ -1,0 +1,348 @@
+"""Benchmark of the small-MLP training step (learnGradient + gradient all-reduce + adjustParameters).
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--config c4] [--batch B]
+
+Workload (default): the wide bf16 network 64-128-128-128-128-64 with GELU (tanh form), global batch
+2^26 split evenly over the N GPUs of one node (strong scaling), MSE against a frozen seeded teacher
+network of the same shape, an fp32 all-reduce of the flat gradient buffer (NCCL over NVLink) and a
+replicated Adam step.  Inputs are seeded synthetic N(0,1) in bf16; the teacher's outputs are computed
+once during set-up.  Two resident batches alternate between steps; each is far larger than L2.
+
+One JSON line is printed by rank 0:
+  value      samples/s with the inputs resident in HBM (K steps, CUDA events, max over ranks)
+  e2e        samples/s through the host-buffer step (pinned host inputs copied in the timed region)
+  roofline   achieved TFLOP/s of the learnGradient kernel against the measured bf16 peak
+  cpu_baseline  the CPU oracle timed on this box's host cores on a bounded sample (N = 1 only)
+`--impl reference` times the CPU oracle (the reference's CPU-target semantics restated in C++; the
+reference itself cannot be built or run here) on all host threads and prints the same line shape.
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+METRIC = "MLP train samples/sec (fwd+bwd+Adam)"
+UNIT = "samples/s"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"bf16_burst": d["bf16_tflops"], "bf16_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]),
+                "hbm_gbs": d["hbm_gbs"], "source": "measured"}
+    return {"bf16_burst": 1590.0, "bf16_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML every 200 ms while the timed region runs."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._halt = threading.Event()
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        if self.nv is None:
+            return
+        nv = self.nv
+        names = {
+            nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+            nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap",
+        }
+        while not self._halt.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._halt.wait(0.2)
+
+    def stop(self):
+        self._halt.set()
+        self.join(timeout=2)
+        med = float(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+def oracle_rate(cfg, name, threads, target_seconds):
+    """samples/s of the CPU oracle's learnGradient + adjustParameters on a bounded sample."""
+    from oracle import oracle
+    from slang_b200 import config as C
+    p0 = C.init_params(cfg, seed=1, scheme="xavier")
+    teacher = C.init_params(cfg, seed=2, scheme="xavier")
+    _, _, total = C.param_layout(cfg)
+
+    def run(n):
+        rng = np.random.default_rng(3)
+        x = C.to_storage(rng.normal(size=(n, cfg.dims[0])).astype(np.float32), cfg.input_dtype)
+        t = C.to_storage(oracle.forward(cfg, teacher, x, min(n, 256)).repeat((n + 255) // 256, axis=0)[:n], cfg.target_dtype)
+        params = p0.copy()
+        grads = np.zeros(total, dtype=np.float32)
+        states = np.zeros(total, dtype=C.ADAM_STATE_DTYPE)
+        states["master"] = C.from_storage(p0, cfg.dtype)
+        t0 = time.perf_counter()
+        oracle.learn_gradient(cfg, params, grads, x, t, n, n_threads=threads)
+        oracle.adjust_parameters(cfg, states, params, grads)
+        return time.perf_counter() - t0
+
+    n = 256 * threads
+    dt = run(n)
+    n_big = int(max(n, min(1 << 20, n * target_seconds / max(dt, 1e-6))))
+    n_big = (n_big + 255) // 256 * 256
+    dt = run(n_big)
+    return n_big / dt, n_big, dt
+
+
+def reference_arm(args, rank):
+    """The reference's CPU implementation of the path, as far as it exists here: the CPU oracle port."""
+    if rank != 0:
+        return
+    from slang_b200 import config as C
+    cfg = C.named_config(args.config)
+    threads = os.cpu_count() or 1
+    rates, sample = [], None
+    per_step = max(2.0, min(20.0, 120.0 / max(args.steps + args.warmup, 1)))
+    for i in range(args.warmup + args.steps):
+        r, n, dt = oracle_rate(cfg, args.config, threads, per_step)
+        sample = n
+        if i >= args.warmup:
+            rates.append((r, dt))
+    total_dt = sum(dt for _, dt in rates)
+    value = sample * len(rates) / total_dt
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * total_dt / len(rates), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": workload_name(args), "global_batch": args.batch, "step_sample": sample,
+                   "note": "each step is a bounded sample of the workload on host cores"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": "%d samples per step, learnGradient + adjustParameters, %d threads" % (sample, threads)},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_name(args):
+    return {"c4": "bf16 MLP 64-128-128-128-128-64 GELU(tanh), MSE vs frozen teacher, Adam lr 3e-4"}.get(args.config, args.config)
+
+
+def teacher_targets(torch, cfg, x, seed):
+    """Outputs of a frozen seeded network of the same shape, in bf16 (set-up only; plain torch)."""
+    from slang_b200 import config as C
+    tp = C.from_storage(C.init_params(cfg, seed=seed, scheme="xavier"), cfg.dtype)
+    w_off, b_off, _ = C.param_layout(cfg)
+    dims = cfg.layer_dims
+    dev = x.device
+    Ws = [torch.from_numpy(tp[w_off[l]:w_off[l] + dims[l] * dims[l + 1]].reshape(dims[l + 1], dims[l]).copy()).to(dev).to(torch.bfloat16) for l in range(cfg.n_layers)]
+    out = torch.empty((x.shape[0], dims[-1]), dtype=torch.bfloat16, device=dev)
+    step = 1 << 21
+    for i0 in range(0, x.shape[0], step):
+        a = x[i0:i0 + step]
+        for l in range(cfg.n_layers):
+            z = (a @ Ws[l].t()).float()
+            a = (torch.nn.functional.gelu(z, approximate="tanh") if l < cfg.n_layers - 1 else z).to(torch.bfloat16)
+        out[i0:i0 + step] = a
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--config", default="c4")
+    ap.add_argument("--batch", type=int, default=1 << 26, help="global batch (samples per step over all GPUs)")
+    ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        reference_arm(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from slang_b200 import config as C
+    from slang_b200.api import Device, Trainer
+    from slang_b200.host_step import HostStepper
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (the library has no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    dev_t = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev_t)
+
+    cfg = C.named_config(args.config)
+    assert args.config == "c4", "the timed workload is the wide bf16 network (c4)"
+    count = args.batch // world
+    stream = torch.cuda.current_stream()
+    device = Device(local_rank, stream.cuda_stream)
+    _, _, total = C.param_layout(cfg)
+
+    # Parameters and gradients live in torch tensors so that the collective sees the same memory.
+    p0 = C.init_params(cfg, seed=1, scheme="xavier")
+    params_t = torch.zeros(total, dtype=torch.bfloat16, device=dev_t)
+    grads_t = torch.zeros(total, dtype=torch.float32, device=dev_t)
+    trainer = Trainer(device, cfg, p0, param_memory=(params_t.data_ptr(), grads_t.data_ptr()))
+    assert trainer.k_learn.implementation == "tcgen05", "the tensor-core kernel did not resolve: %s" % trainer.k_learn.implementation
+
+    n_batches = 2
+    gen = torch.Generator(device=dev_t)
+    xs, ts = [], []
+    for b in range(n_batches):
+        gen.manual_seed(1000 + 17 * b + rank)
+        x = torch.randn((count, 64), dtype=torch.float32, device=dev_t, generator=gen).to(torch.bfloat16) if count <= (1 << 24) else None
+        if x is None:
+            x = torch.empty((count, 64), dtype=torch.bfloat16, device=dev_t)
+            piece = 1 << 23
+            for i0 in range(0, count, piece):
+                x[i0:i0 + piece] = torch.randn((min(piece, count - i0), 64), dtype=torch.float32, device=dev_t, generator=gen).to(torch.bfloat16)
+        xs.append(x)
+        ts.append(teacher_targets(torch, cfg, x, seed=2))
+    torch.cuda.synchronize()
+
+    def allreduce():
+        if world > 1:
+            dist.all_reduce(grads_t)
+
+    def step(i):
+        b = i % n_batches
+        trainer.learn_gradient(xs[b].data_ptr(), ts[b].data_ptr(), count)
+        allreduce()
+        trainer.adjust_parameters()
+
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    launches0 = device.launch_count
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    k_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    ev0.record()
+    for i in range(args.steps):
+        b = i % n_batches
+        k_ev[i][0].record()
+        trainer.learn_gradient(xs[b].data_ptr(), ts[b].data_ptr(), count)
+        k_ev[i][1].record()
+        allreduce()
+        trainer.adjust_parameters()
+    ev1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    launches = device.launch_count - launches0
+    device.wait()  # raises if a kernel set the status word
+
+    elapsed_ms = ev0.elapsed_time(ev1)
+    kernel_ms = float(np.mean([a.elapsed_time(b) for a, b in k_ev]))
+    if world > 1:
+        tt = torch.tensor([elapsed_ms, kernel_ms], dtype=torch.float64, device=dev_t)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        elapsed_ms, kernel_ms = float(tt[0]), float(tt[1])
+        lt = torch.tensor([launches], dtype=torch.int64, device=dev_t)
+        dist.all_reduce(lt)
+        launches = int(lt[0])
+    value = args.batch * args.steps / (elapsed_ms * 1e-3)
+    mx, sm = trainer.read_loss()
+
+    # ---- end to end: pinned host inputs, copies inside the timed region ----
+    e2e = None
+    if not args.no_e2e:
+        stepper = HostStepper(trainer, chunk_samples=min(count, 1 << 21), allreduce=allreduce if world > 1 else None)
+        xh = torch.empty((count, 64), dtype=torch.bfloat16, pin_memory=True)
+        th = torch.empty((count, 64), dtype=torch.bfloat16, pin_memory=True)
+        xh.copy_(xs[0]); th.copy_(ts[0])
+        torch.cuda.synchronize()
+        stepper.step(xh, th)  # warm-up
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        t0 = time.perf_counter()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.e2e_steps):
+            stepper.step(xh, th)
+        e1.record()
+        torch.cuda.synchronize()
+        e2e_ms = e0.elapsed_time(e1)
+        wall_ms = (time.perf_counter() - t0) * 1e3
+        if world > 1:
+            tt = torch.tensor([e2e_ms], dtype=torch.float64, device=dev_t)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            e2e_ms = float(tt[0])
+        e2e = {"value": args.batch * args.e2e_steps / (e2e_ms * 1e-3), "unit": UNIT,
+               "h2d_bytes_per_step": int(stepper.h2d_bytes) * world, "d2h_bytes_per_step": int(stepper.d2h_bytes) * world,
+               "steps": args.e2e_steps, "wall_ms_per_step": wall_ms / args.e2e_steps,
+               "api": "slang_b200.host_step.HostStepper.step (pinned host inputs and targets, chunked copies overlapped with learnGradient)"}
+        del xh, th
+
+    if rank == 0:
+        peaks = measured_peaks()
+        flops = C.flops_per_sample(cfg, training=True)
+        achieved = flops * count / (kernel_ms * 1e-3) / 1e12
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": workload_name(args), "global_batch": args.batch, "per_gpu_batch": count,
+                       "parallelism": "dp%d" % world, "l2": "inputs (%.1f GB per step per GPU) larger than L2; two batches alternate" % (count * 256 / 1e9)},
+            "clocks": clocks, "gpu_launches": launches, "e2e": e2e,
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_sustained"], "unit": "TFLOP/s",
+                         "frac": achieved / peaks["bf16_sustained"], "frac_of_burst": achieved / peaks["bf16_burst"],
+                         "traffic": None, "peak_source": peaks["source"] + " (sustained bf16 GEMM; kernel timed inside the step loop)",
+                         "kernel": "learn_gradient_wide_kernel", "kernel_ms": kernel_ms, "flop_per_sample": flops,
+                         "hbm_gbs": count * 256 / (kernel_ms * 1e-3) / 1e9},
+            "loss": {"max": mx, "mean_local": sm / count},
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            threads = os.cpu_count() or 1
+            r, n, dt = oracle_rate(cfg, args.config, threads, 12.0)
+            line["cpu_baseline"] = {"value": r, "unit": UNIT, "cores": threads, "kind": "port",
+                                    "sample": "%d samples, learnGradient + adjustParameters once, %.1f s" % (n, dt)}
+        print(json.dumps(line), flush=True)
+    device.destroy()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -167,8 +167,11 @@ class Trainer:
         self.k_adjust = device.kernel("adjustParameters", cfg)
         self.k_forward = device.kernel(forward_entry, cfg)
 
-    def learn_gradient(self, inputs_address, targets_address, count, flags=0):
-        self.loss.clear()
+    def learn_gradient(self, inputs_address, targets_address, count, flags=0, clear_loss=True):
+        """One learnGradient dispatch.  Gradients and the loss words accumulate across dispatches, so a
+        batch may be fed in several pieces with clear_loss=False after the first."""
+        if clear_loss:
+            self.loss.clear()
         args = LearnGradParamsEx(self.network.address, self.loss.address, inputs_address, targets_address, count, flags)
         self.k_learn.dispatch(args, groups_for(count))
 

@@ -77,3 +77,20 @@ def layer_rel_errs(cfg, a, b):
         if np.max(np.abs(bb)) > 0:
             out.append(rel_err(a[b_off[l]:b_off[l] + dims[l + 1]], bb))
     return out
+
+
+def per_layer_rel_errs(cfg, a, b):
+    """rel_err per layer with the weight matrix and the bias vector taken together.
+
+    Zero-initialised biases move by about +-lr per Adam step in the first steps whatever the size of
+    their gradient, so the sign of a near-zero gradient decides a bias's early path; measured against
+    the layer's own parameter scale that effect is small, measured against the bias vector alone it is not."""
+    w_off, b_off, _ = C.param_layout(cfg)
+    dims = cfg.layer_dims
+    out = []
+    for l in range(cfg.n_layers):
+        nw = dims[l] * dims[l + 1]
+        ia = np.concatenate([a[w_off[l]:w_off[l] + nw], a[b_off[l]:b_off[l] + dims[l + 1]]])
+        ib = np.concatenate([b[w_off[l]:w_off[l] + nw], b[b_off[l]:b_off[l] + dims[l + 1]]])
+        out.append(rel_err(ia, ib))
+    return out

