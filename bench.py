@@ -207,7 +207,8 @@ def main():
     cfg = C.named_config(args.config)
     assert args.config == "c4", "the timed workload is the wide bf16 network (c4)"
     count = args.batch // world
-    stream = torch.cuda.current_stream()
+    stream = torch.cuda.Stream(device=dev_t)
+    torch.cuda.set_stream(stream)  # kernels, collectives and timing events all go to this stream
     device = Device(local_rank, stream.cuda_stream)
     _, _, total = C.param_layout(cfg)
 

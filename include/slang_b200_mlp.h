@@ -86,7 +86,8 @@ typedef struct MlpForwardParams {
 /* rhi::getRHI()->createDevice (mlp-training.cpp:96-100).  `ordinal` is the CUDA device index. */
 int32_t mlp_device_create(int32_t ordinal, MlpDevice** out_device);
 /* Same, but work is issued on an existing CUDA stream (a cudaStream_t passed as a pointer) so that
- * the caller's own stream-ordered work (copies, collectives) interleaves with the kernels. */
+ * the caller's own stream-ordered work (copies, collectives) interleaves with the kernels.  A null
+ * handle means the legacy default stream. */
 int32_t mlp_device_create_on_stream(int32_t ordinal, void* cuda_stream, MlpDevice** out_device);
 int32_t mlp_device_destroy(MlpDevice* device);
 /* queue->waitOnHost() (mlp-training.cpp:207).  Also reports a pending device status word. */

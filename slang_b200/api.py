@@ -78,6 +78,7 @@ class Device:
         if stream is None:
             check(load().mlp_device_create(ordinal, ctypes.byref(h)))
         else:
+            # `stream` is a cudaStream_t as an integer (0 = the legacy default stream)
             check(load().mlp_device_create_on_stream(ordinal, ctypes.c_void_p(stream), ctypes.byref(h)))
         self.handle = h
         self.ordinal = ordinal

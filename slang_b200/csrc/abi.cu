@@ -81,7 +81,7 @@ extern "C" {
 
 const char* mlp_last_error_string(void) { return g_last_error.c_str(); }
 
-int32_t mlp_device_create_on_stream(int32_t ordinal, void* cuda_stream, MlpDevice** out_device)
+static int32_t device_create(int32_t ordinal, bool borrow_stream, void* cuda_stream, MlpDevice** out_device)
 {
     if (!out_device) return fail(MLP_E_INVALID_ARG, "out_device is null");
     *out_device = nullptr;
@@ -97,8 +97,8 @@ int32_t mlp_device_create_on_stream(int32_t ordinal, void* cuda_stream, MlpDevic
         return fail(MLP_E_NOT_AVAILABLE, "device %d is sm_%d%d; the kernels are built for sm_100a only", ordinal, prop.major, prop.minor);
     MlpDevice* d = new MlpDevice();
     d->ordinal = ordinal;
-    if (cuda_stream) {
-        d->stream = (cudaStream_t)cuda_stream;
+    if (borrow_stream) {
+        d->stream = (cudaStream_t)cuda_stream;  // a null handle is the legacy default stream
     } else {
         cudaError_t se = cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking);
         if (se != cudaSuccess) { delete d; return fail(MLP_E_CUDA, "cudaStreamCreate failed: %s", cudaGetErrorString(se)); }
@@ -117,7 +117,12 @@ int32_t mlp_device_create_on_stream(int32_t ordinal, void* cuda_stream, MlpDevic
 
 int32_t mlp_device_create(int32_t ordinal, MlpDevice** out_device)
 {
-    return mlp_device_create_on_stream(ordinal, nullptr, out_device);
+    return device_create(ordinal, false, nullptr, out_device);
+}
+
+int32_t mlp_device_create_on_stream(int32_t ordinal, void* cuda_stream, MlpDevice** out_device)
+{
+    return device_create(ordinal, true, cuda_stream, out_device);
 }
 
 int32_t mlp_device_destroy(MlpDevice* d)
