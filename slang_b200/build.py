@@ -54,7 +54,8 @@ def build(force=False, verbose=False):
         o = os.path.join(OBJDIR, src.replace(".cu", ".o"))
         objs.append(o)
         if force or not os.path.exists(o) or os.path.getmtime(o) < max(os.path.getmtime(s), newest_header):
-            cmd = [nvcc] + ARCH + COMMON + extra + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
+            more = os.environ.get("MLPB200_NVCC_FLAGS", "").split()  # experiments only, e.g. -DMLPB200_CH=64
+            cmd = [nvcc] + ARCH + COMMON + extra + more + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
             if verbose:
                 print(" ".join(cmd), flush=True)
             subprocess.check_call(cmd)

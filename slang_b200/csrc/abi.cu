@@ -331,6 +331,16 @@ int32_t mlp_dispatch(MlpDevice* d, MlpKernel* k, const void* args, size_t args_s
     return MLP_OK;
 }
 
+// Diagnostics, not part of the public header: cycle counts recorded by CTA 0 of the last
+// tensor-core learnGradient (control thread total / waiting, tiles, epilogue warp total / waiting).
+int32_t mlpb200_debug_tc_timing(MlpDevice* d, unsigned long long* out8)
+{
+    if (!d || !out8) return fail(MLP_E_INVALID_ARG, "null argument");
+    CUDA_TRY(cudaSetDevice(d->ordinal));
+    CUDA_TRY(tc_read_timing(d->stream, d->tc, out8));
+    return MLP_OK;
+}
+
 int32_t mlp_param_layout(const MlpConfig* config, int64_t* w_off, int64_t* b_off, int64_t* total)
 {
     std::string why;

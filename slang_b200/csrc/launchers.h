@@ -29,6 +29,8 @@ cudaError_t launch_forward_tc(cudaStream_t st, TcWorkspace* ws, const MlpConfig&
                               int* launches, std::string* err);
 cudaError_t launch_learn_gradient_tc(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c,
                                      const MlpLearnGradParamsEx& a, int* launches, std::string* err);
+// Cycle counts CTA 0 of the last tensor-core learnGradient recorded (diagnostics).
+cudaError_t tc_read_timing(cudaStream_t st, TcWorkspace* ws, unsigned long long* out8);
 // Reads and clears the device status word (0 = no kernel gave up on a bounded wait).
 cudaError_t tc_read_status(cudaStream_t st, TcWorkspace* ws, uint32_t* status);
 

@@ -40,10 +40,17 @@ enum : uint32_t {
 };
 
 namespace wide {
-constexpr int NS = 64;            // samples per tile (MMA N of the forward / input-gradient products)
+constexpr int NS = 64;            // samples per tile
+#ifndef MLPB200_CH
+#define MLPB200_CH 32
+#endif
+constexpr int CH = MLPB200_CH;    // samples per chain (MMA N of the forward / input-gradient products)
+constexpr int NCH = NS / CH;      // chains per tile
 constexpr int D0 = 64, H = 128, DOUT = 64, NL = 5;
-constexpr int kThreads = 320;     // warp 0: TMA + MMA issue, warp 1: TMEM owner, warps 2-9: epilogue
-constexpr int kEpiThreads = 256;
+constexpr int CPT = 16;           // sample columns per epilogue thread
+constexpr int kEpiWarps = 4 * (NS / CPT);      // one warp per TMEM lane quarter and column group
+constexpr int kWarpsPerChain = 4 * (CH / CPT);
+constexpr int kThreads = 64 + 32 * kEpiWarps;  // warp 0: TMA + MMA issue, warp 1: TMEM owner, then the epilogue warps
 
 // Shared-memory map (bytes from a 1024-aligned base).  Operand buffers are panels of
 // [rows][128 bytes] with the 128-byte swizzle; a panel holds 64 16-bit features of every row.
@@ -57,8 +64,8 @@ constexpr uint32_t kA1 = kX + 2 * 8192;      // A_1..A_4: [64 rows x 2 panels] e
 constexpr uint32_t kDZ4 = kA1 + 4 * 16384;   // [64 rows x 1 panel]: targets land here, dZ_4 replaces them
 constexpr uint32_t kBias = kDZ4 + 8192;      // fp32 [5][128]
 constexpr uint32_t kLossPart = kBias + 5 * 128 * 4;  // fp32 [2][64]
-constexpr uint32_t kBars = kLossPart + 2 * 64 * 4;   // mbarriers: x_full[2], t_full, acc_full, acc_free, loss_bar
-constexpr uint32_t kTmemPtr = kBars + 8 * 8;
+constexpr uint32_t kBars = kLossPart + 2 * 64 * 4;   // mbarriers: x_full[2], t_full, acc_full[2], acc_free[2], loss_bar[2]
+constexpr uint32_t kTmemPtr = kBars + 14 * 8;
 constexpr uint32_t kAbort = kTmemPtr + 4;
 constexpr uint32_t kSmemBytes = kAbort + 4 + 1024;   // + slack for aligning the base
 
@@ -75,13 +82,32 @@ template <> struct Elem<MLP_BF16> {
     static constexpr uint32_t kUmmaFmt = 1;
     __device__ static __forceinline__ uint16_t pack(float v) { return __bfloat16_as_ushort(__float2bfloat16_rn(v)); }
     __device__ static __forceinline__ float unpack(uint16_t b) { return __uint_as_float((uint32_t)b << 16); }
-    __device__ static __forceinline__ float round(float v) { return unpack(pack(v)); }
+    // Round to nearest even with integer operations (keeps the conversion unit free for tanh).
+    __device__ static __forceinline__ float round(float v)
+    {
+        const uint32_t u = __float_as_uint(v);
+        return __uint_as_float((u + 0x7fffu + ((u >> 16) & 1u)) & 0xffff0000u);
+    }
+    __device__ static __forceinline__ uint32_t pack2(float lo, float hi)
+    {
+        __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&t);
+    }
+    __device__ static __forceinline__ float unpack_lo(uint32_t p) { return __uint_as_float(p << 16); }
+    __device__ static __forceinline__ float unpack_hi(uint32_t p) { return __uint_as_float(p & 0xffff0000u); }
 };
 template <> struct Elem<MLP_F16> {
     static constexpr uint32_t kUmmaFmt = 0;
     __device__ static __forceinline__ uint16_t pack(float v) { return __half_as_ushort(__float2half_rn(v)); }
     __device__ static __forceinline__ float unpack(uint16_t b) { return __half2float(__ushort_as_half(b)); }
     __device__ static __forceinline__ float round(float v) { return unpack(pack(v)); }
+    __device__ static __forceinline__ uint32_t pack2(float lo, float hi)
+    {
+        __half2 t = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&t);
+    }
+    __device__ static __forceinline__ float unpack_lo(uint32_t p) { return unpack((uint16_t)(p & 0xffffu)); }
+    __device__ static __forceinline__ float unpack_hi(uint32_t p) { return unpack((uint16_t)(p >> 16)); }
 };
 
 // Hidden activation on a storage-rounded pre-activation: value and derivative.
@@ -115,6 +141,7 @@ struct WideTrainParams {
     uint32_t n_tiles;
     float loss_scale;  // 1 / outputs for the mean-squared error, 1 for the sum of squares
     float act_alpha;
+    unsigned long long* timing;  // diagnostics written by CTA 0: cycles spent waiting / issuing / computing
 };
 
 template <int FMT, int ACT>
@@ -128,11 +155,11 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const uint32_t sbase = smem_u32(smem);
     uint64_t* bars = (uint64_t*)(smem + kBars);
-    uint64_t* x_full = bars;  // [2]
+    uint64_t* x_full = bars;        // [2]
     uint64_t* t_full = bars + 2;
-    uint64_t* acc_full = bars + 3;
-    uint64_t* acc_free = bars + 4;
-    uint64_t* loss_bar = bars + 5;
+    uint64_t* acc_full = bars + 3;  // [2], one per chain
+    uint64_t* acc_free = bars + 5;  // [2]
+    uint64_t* loss_bar = bars + 7;  // [2]
     uint32_t* tmem_ptr = (uint32_t*)(smem + kTmemPtr);
     volatile uint32_t* abort_flag = (volatile uint32_t*)(smem + kAbort);
     float* s_bias = (float*)(smem + kBias);
@@ -146,9 +173,11 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
         mbar_init(&x_full[0], 1);
         mbar_init(&x_full[1], 1);
         mbar_init(t_full, 1);
-        mbar_init(acc_full, 1);
-        mbar_init(acc_free, kEpiThreads / 32);
-        mbar_init(loss_bar, 4);
+        for (int h = 0; h < NCH; ++h) {
+            mbar_init(&acc_full[h], 1);
+            mbar_init(&acc_free[h], kWarpsPerChain);       // the chain's epilogue warps
+            mbar_init(&loss_bar[h], kWarpsPerChain / 2);   // ... of which those that hold output features
+        }
         *abort_flag = 0u;
         fence_mbar_init();
         prefetch_tmap(&tmap_x);
@@ -179,113 +208,177 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
     const uint32_t tmem_base = *tmem_ptr;
 
     if (warp == 0) {
-        // =================================== control thread ========================================
-        if (lane == 0 && n_my_tiles > 0) {
+        // =================================== control warp ==========================================
+        // The 64 samples of a tile run as two independent chains of 32 (h = 0, 1): while the epilogue
+        // warps of one chain work on their accumulator half, the tensor pipe runs the other chain's
+        // product.  Both chains share the operand buffers (rows 32h..32h+31) and the weight-gradient
+        // accumulators; they meet once per tile, at the dW_0 product.
+        // The whole warp walks the schedule so that addresses stay warp-uniform; one elected lane
+        // issues the TMA loads, the MMAs and the commits.  (One control warp per chain was measured
+        // slower: the products of both chains share one tensor pipe either way.)
+        if (n_my_tiles > 0) {
+            const bool leader = elect_one();
             constexpr uint32_t F = E::kUmmaFmt;
-            constexpr uint32_t kIdescFwd = umma_idesc(F, 0, 0, 128, NS);    // W (K) x act (K)
-            constexpr uint32_t kIdescDx = umma_idesc(F, 1, 0, 128, NS);     // W^T (MN) x dZ (K)
+            constexpr uint32_t kIdescFwd = umma_idesc(F, 0, 0, 128, CH);    // W (K) x act (K)
+            constexpr uint32_t kIdescDx = umma_idesc(F, 1, 0, 128, CH);     // W^T (MN) x dZ (K)
             constexpr uint32_t kIdescDw = umma_idesc(F, 1, 1, 128, 128);    // dZ^T (MN) x act (MN)
             constexpr uint32_t kIdescDw64 = umma_idesc(F, 1, 1, 128, 64);   // N = 64 variants (dW_4^T, dW_0)
-            const uint32_t acc = tmem_base + kColAcc;
-            uint32_t step = 0;
+            uint32_t step = 0;   // both chains are at the same step whenever this warp looks
             bool ok = true;
-            auto acc_wait = [&]() {
-                if (step > 0) ok = ok && mbar_wait(acc_free, (step - 1) & 1u, abort_flag, p.status, kStatusCtrlAcc);
+            long long t_wait = 0;
+            const long long t_start = clock64();
+            // Every phase of a barrier is observed in order: a parity wait only means something if
+            // the waiter has seen all earlier phases complete.
+            auto chain_wait = [&](int h) {
+                const long long t0 = clock64();
+                if (step > 0) ok = ok && mbar_wait(&acc_free[h], (step - 1) & 1u, abort_flag, p.status, kStatusCtrlAcc);
                 tc_fence_after();
+                t_wait += clock64() - t0;
             };
-            // K-major operand: rows of 128 bytes, 8-row groups 1024 bytes apart; a K step of 16
-            // elements is 32 bytes inside the swizzled row; 64-element panels are `panel` bytes apart.
-            auto desc_k = [&](uint32_t buf, uint32_t panel, int k) {
-                return smem_desc_sw128(sbase + buf + (uint32_t)(k >> 2) * panel + (uint32_t)(k & 3) * 32u, 16u, 1024u);
+            // Descriptors cost one 32-bit add each: the high word (8-row groups 1024 bytes apart,
+            // version 1, 128-byte swizzle) is the same for every operand and the low word is the
+            // buffer's address in 16-byte units plus compile-time offsets.
+            const uint32_t lo_base = (sbase & 0x3FFFFu) >> 4;
+            constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+            // K-major operand: rows of 128 bytes; a K step of 16 elements is 32 bytes inside the
+            // swizzled row; 64-element panels are `panel` bytes apart.
+            auto desc_k = [&](uint32_t buf, uint32_t panel, int k) -> uint64_t {
+                const uint32_t lo = lo_base + ((buf + (uint32_t)(k >> 2) * panel + (uint32_t)(k & 3) * 32u) >> 4) + (1u << 16);
+                return ((uint64_t)kDescHi << 32) | lo;
             };
             // MN-major operand: a K step of 16 rows is 2048 bytes; 64-element panels are `panel` bytes apart.
-            auto desc_mn = [&](uint32_t buf, uint32_t panel, int k) {
-                return smem_desc_sw128(sbase + buf + (uint32_t)k * 2048u, panel, 1024u);
+            auto desc_mn = [&](uint32_t buf, uint32_t panel, int k) -> uint64_t {
+                const uint32_t lo = lo_base + ((buf + (uint32_t)k * 2048u) >> 4) + ((panel >> 4) << 16);
+                return ((uint64_t)kDescHi << 32) | lo;
             };
-            const uint32_t tile0 = blockIdx.x;
-            mbar_expect_tx(&x_full[0], 8192);
-            tma_load_2d(smem + kX, &tmap_x, 0, (int32_t)(tile0 * NS), &x_full[0]);
-            mbar_expect_tx(t_full, 8192);
-            tma_load_2d(smem + kDZ4, &tmap_t, 0, (int32_t)(tile0 * NS), t_full);
-            uint32_t x_issued = 1, t_issued = 1;  // loads issued so far (for the drain after an abort)
+            if (leader) {
+                mbar_expect_tx(&x_full[0], 8192);
+                tma_load_2d(smem + kX, &tmap_x, 0, (int32_t)(blockIdx.x * NS), &x_full[0]);
+                mbar_expect_tx(t_full, 8192);
+                tma_load_2d(smem + kDZ4, &tmap_t, 0, (int32_t)(blockIdx.x * NS), t_full);
+            }
+            uint32_t loads_issued = 1;  // tiles whose X and target loads have been issued (for the drain after an abort)
 
             for (uint32_t it = 0; it < n_my_tiles && ok; ++it) {
                 const uint32_t b = it & 1u;
                 const uint32_t next_tile = blockIdx.x + (it + 1) * gridDim.x;
                 const bool has_next = it + 1 < n_my_tiles;
                 const uint32_t xbuf = kX + b * 8192u;
-                // ---- forward ----
-                acc_wait();
-                if (!ok) break;
-                if (has_next) {  // the other X buffer was last read by the previous tile's dW_0 product, now complete
-                    mbar_expect_tx(&x_full[b ^ 1u], 8192);
-                    tma_load_2d(smem + kX + (b ^ 1u) * 8192u, &tmap_x, 0, (int32_t)(next_tile * NS), &x_full[b ^ 1u]);
-                    ++x_issued;
+                // ---- forward, layer 0 ----
+#pragma unroll
+                for (int h = 0; h < NCH; ++h) {
+                    chain_wait(h);
+                    if (h == 0) ok = ok && mbar_wait(&x_full[b], (it >> 1) & 1u, abort_flag, p.status, kStatusCtrlX);
+                    if (ok) {
+                        const uint32_t acc = tmem_base + kColAcc + (uint32_t)(h * CH);
+                        if (leader) {
+#pragma unroll
+                            for (int k = 0; k < D0 / 16; ++k)
+                                umma_f16(acc, desc_k(kW0, 16384u, k), desc_k(xbuf + (uint32_t)h * (uint32_t)(CH * 128), 8192u, k), kIdescFwd, k > 0);
+                            umma_commit(&acc_full[h]);
+                        }
+                        __syncwarp();
+                    }
                 }
-                ok = mbar_wait(&x_full[b], (it >> 1) & 1u, abort_flag, p.status, kStatusCtrlX);
-                if (!ok) break;
-                for (int k = 0; k < D0 / 16; ++k)
-                    umma_f16(acc, desc_k(kW0, 16384u, k), desc_k(xbuf, 8192u, k), kIdescFwd, k > 0);
-                umma_commit(acc_full);
                 ++step;
-                for (int l = 1; l < NL && ok; ++l) {
-                    acc_wait();
-                    if (!ok) break;
+                // ---- forward, layers 1..4 ----
+#pragma unroll
+                for (int l = 1; l < NL; ++l) {
                     const uint32_t wpanel = (uint32_t)out_dim(l) * 128u;
                     const uint32_t abuf = kA1 + (uint32_t)(l - 1) * 16384u;
-                    for (int k = 0; k < H / 16; ++k)
-                        umma_f16(acc, desc_k(w_off(l), wpanel, k), desc_k(abuf, 8192u, k), kIdescFwd, k > 0);
-                    umma_commit(acc_full);
+#pragma unroll
+                    for (int h = 0; h < NCH; ++h) {
+                        chain_wait(h);
+                        if (ok) {
+                            const uint32_t acc = tmem_base + kColAcc + (uint32_t)(h * CH);
+                            if (leader) {
+#pragma unroll
+                                for (int k = 0; k < H / 16; ++k)
+                                    umma_f16(acc, desc_k(w_off(l), wpanel, k), desc_k(abuf + (uint32_t)h * (uint32_t)(CH * 128), 8192u, k), kIdescFwd, k > 0);
+                                umma_commit(&acc_full[h]);
+                            }
+                            __syncwarp();
+                        }
+                    }
                     ++step;
                 }
                 // ---- backward ----
-                for (int l = NL - 1; l >= 1 && ok; --l) {
-                    acc_wait();
-                    if (!ok) break;
-                    if (l == NL - 2 && has_next) {  // dZ_4's buffer is free: fetch the next tile's targets
-                        mbar_expect_tx(t_full, 8192);
-                        tma_load_2d(smem + kDZ4, &tmap_t, 0, (int32_t)(next_tile * NS), t_full);
-                        ++t_issued;
-                    }
+#pragma unroll
+                for (int l = NL - 1; l >= 1; --l) {
                     const uint32_t wpanel = (uint32_t)out_dim(l) * 128u;
                     const uint32_t dzbuf = (l == NL - 1) ? kDZ4 : kA1 + (uint32_t)l * 16384u;  // dZ_l lives in A_{l+1}'s buffer
                     const uint32_t abuf = kA1 + (uint32_t)(l - 1) * 16384u;                   // A_l
-                    const int kdx = out_dim(l) / 16;
-                    for (int k = 0; k < kdx; ++k)
-                        umma_f16(acc, desc_mn(w_off(l), wpanel, k), desc_k(dzbuf, 8192u, k), kIdescDx, k > 0);
-                    if (l == NL - 1) {
-                        for (int k = 0; k < NS / 16; ++k)
-                            umma_f16(tmem_base + kColDW4T, desc_mn(abuf, 8192u, k), desc_mn(dzbuf, 8192u, k), kIdescDw64,
-                                     (it > 0 || k > 0));
-                    } else {
-                        for (int k = 0; k < NS / 16; ++k)
-                            umma_f16(tmem_base + kColDW1 + (uint32_t)(l - 1) * 128u, desc_mn(dzbuf, 8192u, k),
-                                     desc_mn(abuf, 8192u, k), kIdescDw, (it > 0 || k > 0));
+#pragma unroll
+                    for (int h = 0; h < NCH; ++h) {
+                        chain_wait(h);
+                        if (ok) {
+                            const uint32_t acc = tmem_base + kColAcc + (uint32_t)(h * CH);
+                            const uint32_t row = (uint32_t)h * (uint32_t)(CH * 128);  // 32 rows of 128 bytes
+                            const uint32_t prior = (it > 0 || h > 0) ? 1u : 0u;  // the launch's first product overwrites
+                            if (leader) {
+#pragma unroll
+                                for (int k = 0; k < out_dim(l) / 16; ++k)
+                                    umma_f16(acc, desc_mn(w_off(l), wpanel, k), desc_k(dzbuf + row, 8192u, k), kIdescDx, k > 0);
+                                if (l == NL - 1) {
+#pragma unroll
+                                    for (int k = 0; k < CH / 16; ++k)
+                                        umma_f16(tmem_base + kColDW4T, desc_mn(abuf + row, 8192u, k), desc_mn(dzbuf + row, 8192u, k),
+                                                 kIdescDw64, prior | (uint32_t)(k > 0));
+                                } else {
+#pragma unroll
+                                    for (int k = 0; k < CH / 16; ++k)
+                                        umma_f16(tmem_base + kColDW1 + (uint32_t)(l - 1) * 128u, desc_mn(dzbuf + row, 8192u, k),
+                                                 desc_mn(abuf + row, 8192u, k), kIdescDw, prior | (uint32_t)(k > 0));
+                                }
+                                umma_commit(&acc_full[h]);
+                            }
+                            __syncwarp();
+                        }
                     }
-                    umma_commit(acc_full);
                     ++step;
                 }
-                if (!ok) break;
-                // ---- dW_0 into the shared accumulator; the epilogue adds it to registers ----
-                acc_wait();
-                if (!ok) break;
-                for (int k = 0; k < NS / 16; ++k)
-                    umma_f16(acc, desc_mn(kA1, 8192u, k), desc_mn(xbuf, 8192u, k), kIdescDw64, k > 0);
-                umma_commit(acc_full);
+                // ---- dW_0 of the whole tile into the 64 accumulator columns (both chains' epilogues
+                //      add their columns to registers); then the next tile's loads ----
+#pragma unroll
+                for (int h = 0; h < NCH; ++h) chain_wait(h);
+                if (ok) {
+                    if (leader) {
+#pragma unroll
+                        for (int k = 0; k < NS / 16; ++k)
+                            umma_f16(tmem_base + kColAcc, desc_mn(kA1, 8192u, k), desc_mn(xbuf, 8192u, k), kIdescDw64, k > 0);
+#pragma unroll
+                        for (int h = 0; h < NCH; ++h) umma_commit(&acc_full[h]);
+                        if (has_next) {
+                            // Both chains are past every product that read the other X buffer and dZ_4.
+                            mbar_expect_tx(&x_full[b ^ 1u], 8192);
+                            tma_load_2d(smem + kX + (b ^ 1u) * 8192u, &tmap_x, 0, (int32_t)(next_tile * NS), &x_full[b ^ 1u]);
+                            mbar_expect_tx(t_full, 8192);
+                            tma_load_2d(smem + kDZ4, &tmap_t, 0, (int32_t)(next_tile * NS), t_full);
+                        }
+                    }
+                    if (has_next) ++loads_issued;
+                    __syncwarp();
+                }
                 ++step;
             }
-            if (*abort_flag) {
+            if (blockIdx.x == 0 && p.timing && leader) {
+                p.timing[0] = (unsigned long long)(clock64() - t_start);  // control warp: whole tile loop
+                p.timing[1] = (unsigned long long)t_wait;                 // ... of which waiting for epilogues
+                p.timing[2] = n_my_tiles;
+            }
+            if (*abort_flag && leader) {
                 // Give the copies still in flight a bounded time to land before the CTA exits.
-                if (x_issued > 0) mbar_drain(&x_full[(x_issued - 1) & 1u], ((x_issued - 1) >> 1) & 1u);
-                if (t_issued > 0) mbar_drain(t_full, (t_issued - 1) & 1u);
+                mbar_drain(&x_full[(loads_issued - 1) & 1u], ((loads_issued - 1) >> 1) & 1u);
+                mbar_drain(t_full, (loads_issued - 1) & 1u);
             }
         }
     } else if (warp >= 2) {
         // =================================== epilogue warps ========================================
         const int q = warp & 3;                // TMEM lane quarter this warp may read
-        const int h = (warp - 2) >> 2;         // which half of the 64 sample columns
+        const int e = (warp - 2) >> 2;         // which group of CPT sample columns
         const int f = q * 32 + lane;           // the feature (TMEM lane) this thread owns
-        const int col0 = h * 32;
+        const int col0 = e * CPT;
+        const int h = col0 / CH;               // the chain those columns belong to
         const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16) + kColAcc + (uint32_t)col0;
         // Byte offset of (row col0, feature f) inside a [64 x W] operand buffer, minus the swizzled chunk.
         const uint32_t pbase = (uint32_t)(f >> 6) * 8192u + (uint32_t)col0 * 128u + (uint32_t)(f & 7) * 2u;
@@ -296,22 +389,29 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
         float bias[NL];
 #pragma unroll
         for (int l = 0; l < NL; ++l) bias[l] = s_bias[l * 128 + f];
-        uint32_t dreg[NL - 1][16];   // activation derivatives of the four hidden layers, two per register
-        float dw0[32];               // this thread's slice of dW_0 (row f, columns col0..col0+31), summed over tiles
-        float db[NL];                // bias-gradient partial sums
+        uint32_t dreg[NL - 1][CPT / 2];  // activation derivatives of the four hidden layers, two per register
+        float dw0[CPT];                  // this thread's slice of dW_0 (row f, columns col0..), summed over tiles
+        float db[NL];                    // bias-gradient partial sums
 #pragma unroll
-        for (int i = 0; i < 32; ++i) dw0[i] = 0.0f;
+        for (int i = 0; i < CPT; ++i) dw0[i] = 0.0f;
 #pragma unroll
         for (int l = 0; l < NL; ++l) db[l] = 0.0f;
         float run_max = 0.0f, run_sum = 0.0f;
         uint32_t step = 0;
         bool ok = true;
-
+        long long e_wait = 0;
+        const long long e_start = clock64();
+        auto wait_acc = [&]() {
+            const long long t0 = clock64();
+            ok = ok && mbar_wait(&acc_full[h], step & 1u, abort_flag, p.status, kStatusEpiAcc);
+            ++step;
+            e_wait += clock64() - t0;
+        };
         auto release_acc = [&]() {
             tc_fence_before();
             fence_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive(acc_free);
+            if (lane == 0) mbar_arrive(&acc_free[h]);
         };
 
         for (uint32_t it = 0; it < n_my_tiles && ok; ++it) {
@@ -319,41 +419,42 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
             // ---- forward, hidden layers ----
 #pragma unroll
             for (int l = 0; l < NL - 1; ++l) {
-                ok = ok && mbar_wait(acc_full, step & 1u, abort_flag, p.status, kStatusEpiAcc);
-                ++step;
-                if (!ok) break;
-                tc_fence_after();
-                uint32_t v[32];
-                tmem_ld_32x32(t_acc, v);
-                tmem_ld_wait();
-                uint8_t* dst = smem + kA1 + (uint32_t)l * 16384u;
+                wait_acc();
+                if (ok) {
+                    tc_fence_after();
+                    uint32_t v[CPT];
+                    tmem_ld_cols(t_acc, v);
+                    tmem_ld_wait();
+                    uint8_t* dst = smem + kA1 + (uint32_t)l * 16384u;
 #pragma unroll
-                for (int s = 0; s < 32; s += 2) {
-                    float a0, d0, a1, d1;
-                    act_pair<ACT>(E::round(__uint_as_float(v[s]) + bias[l]), p.act_alpha, a0, d0);
-                    act_pair<ACT>(E::round(__uint_as_float(v[s + 1]) + bias[l]), p.act_alpha, a1, d1);
-                    *(uint16_t*)(dst + xo[s & 7] + s * 128) = E::pack(a0);
-                    *(uint16_t*)(dst + xo[(s + 1) & 7] + (s + 1) * 128) = E::pack(a1);
-                    dreg[l][s >> 1] = (uint32_t)E::pack(d0) | ((uint32_t)E::pack(d1) << 16);
+                    for (int s = 0; s < CPT; s += 2) {
+                        float a0, d0, a1, d1;
+                        const float z0 = __uint_as_float(v[s]) + bias[l], z1 = __uint_as_float(v[s + 1]) + bias[l];
+                        act_pair<ACT>(E::round(z0), p.act_alpha, a0, d0);
+                        act_pair<ACT>(E::round(z1), p.act_alpha, a1, d1);
+                        const uint32_t ap = E::pack2(a0, a1);
+                        *(uint16_t*)(dst + xo[s & 7] + s * 128) = (uint16_t)(ap & 0xffffu);
+                        *(uint16_t*)(dst + xo[(s + 1) & 7] + (s + 1) * 128) = (uint16_t)(ap >> 16);
+                        dreg[l][s >> 1] = E::pack2(d0, d1);
+                    }
+                    release_acc();
                 }
-                release_acc();
             }
             if (!ok) break;
             // ---- output layer, loss and dZ_4 ----
             {
-                ok = ok && mbar_wait(acc_full, step & 1u, abort_flag, p.status, kStatusEpiAcc);
-                ++step;
+                wait_acc();
                 ok = ok && mbar_wait(t_full, it & 1u, abort_flag, p.status, kStatusEpiTarget);
                 if (!ok) break;
                 tc_fence_after();
                 if (q < 2) {
-                    uint32_t v[32];
-                    tmem_ld_32x32(t_acc, v);
+                    uint32_t v[CPT];
+                    tmem_ld_cols(t_acc, v);
                     tmem_ld_wait();
                     uint8_t* dst = smem + kDZ4;
-                    float lsq[32];
+                    float lsq[CPT];
 #pragma unroll
-                    for (int s = 0; s < 32; ++s) {
+                    for (int s = 0; s < CPT; ++s) {
                         const bool valid = tile * NS + col0 + s < p.count;
                         uint16_t* slot = (uint16_t*)(dst + xo[s & 7] + s * 128);
                         const float out = E::round(__uint_as_float(v[s]) + bias[NL - 1]);
@@ -363,28 +464,36 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                         *slot = E::pack(dz);
                         db[NL - 1] += dz;
                     }
-                    // Sum over this warp's 32 features for each of the 32 sample columns: after the
-                    // five exchange rounds lane c holds the sum of column c.
+                    // Sum over this warp's 32 features for each sample column: every exchange round
+                    // halves the number of columns a lane carries; afterwards lane c * (32 / CPT)
+                    // holds the sum of column c.
+                    int cnt = CPT;
 #pragma unroll
                     for (int w = 16; w >= 1; w >>= 1) {
-                        const bool upper = (lane & w) != 0;
+                        if (cnt > 1) {
+                            const int half = cnt / 2;
+                            const bool upper = (lane & w) != 0;
 #pragma unroll
-                        for (int i = 0; i < w; ++i) {
-                            const float keep = upper ? lsq[i + w] : lsq[i];
-                            const float send = upper ? lsq[i] : lsq[i + w];
-                            lsq[i] = keep + __shfl_xor_sync(0xffffffffu, send, w);
+                            for (int i = 0; i < half; ++i) {
+                                const float keep = upper ? lsq[i + half] : lsq[i];
+                                const float send = upper ? lsq[i] : lsq[i + half];
+                                lsq[i] = keep + __shfl_xor_sync(0xffffffffu, send, w);
+                            }
+                            cnt = half;
+                        } else {
+                            lsq[0] += __shfl_xor_sync(0xffffffffu, lsq[0], w);
                         }
                     }
-                    s_loss_part[q * 64 + col0 + lane] = lsq[0];
+                    if ((lane % (32 / CPT)) == 0) s_loss_part[q * 64 + col0 + lane / (32 / CPT)] = lsq[0];
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(loss_bar);
+                    if (lane == 0) mbar_arrive(&loss_bar[h]);
                 }
                 release_acc();
                 if (q == 0) {
-                    // The other feature half of these 32 samples comes from the warp of quarter 1.
-                    ok = ok && mbar_wait(loss_bar, it & 1u, abort_flag, p.status, kStatusEpiLoss);
+                    // The other feature half of these samples comes from the warp of quarter 1.
+                    ok = ok && mbar_wait(&loss_bar[h], it & 1u, abort_flag, p.status, kStatusEpiLoss);
                     if (!ok) break;
-                    float tot = s_loss_part[col0 + lane] + s_loss_part[64 + col0 + lane];
+                    float tot = lane < CPT ? s_loss_part[col0 + lane] + s_loss_part[64 + col0 + lane] : 0.0f;
                     float mx = tot;
 #pragma unroll
                     for (int o = 16; o > 0; o >>= 1) {
@@ -398,51 +507,55 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
             // ---- backward: dA_l arrives in the accumulator, dZ_{l-1} replaces A_l in shared memory ----
 #pragma unroll
             for (int l = NL - 1; l >= 1; --l) {
-                ok = ok && mbar_wait(acc_full, step & 1u, abort_flag, p.status, kStatusEpiAcc);
-                ++step;
-                if (!ok) break;
-                tc_fence_after();
-                uint32_t v[32];
-                tmem_ld_32x32(t_acc, v);
-                tmem_ld_wait();
-                uint8_t* dst = smem + kA1 + (uint32_t)(l - 1) * 16384u;
+                wait_acc();
+                if (ok) {
+                    tc_fence_after();
+                    uint32_t v[CPT];
+                    tmem_ld_cols(t_acc, v);
+                    tmem_ld_wait();
+                    uint8_t* dst = smem + kA1 + (uint32_t)(l - 1) * 16384u;
 #pragma unroll
-                for (int s = 0; s < 32; s += 2) {
-                    const uint32_t dd = dreg[l - 1][s >> 1];
-                    const float dz0 = E::round(__uint_as_float(v[s]) * E::unpack((uint16_t)(dd & 0xffffu)));
-                    const float dz1 = E::round(__uint_as_float(v[s + 1]) * E::unpack((uint16_t)(dd >> 16)));
-                    *(uint16_t*)(dst + xo[s & 7] + s * 128) = E::pack(dz0);
-                    *(uint16_t*)(dst + xo[(s + 1) & 7] + (s + 1) * 128) = E::pack(dz1);
-                    db[l - 1] += dz0 + dz1;
+                    for (int s = 0; s < CPT; s += 2) {
+                        const uint32_t dd = dreg[l - 1][s >> 1];
+                        const uint32_t zp = E::pack2(__uint_as_float(v[s]) * E::unpack_lo(dd),
+                                                     __uint_as_float(v[s + 1]) * E::unpack_hi(dd));
+                        *(uint16_t*)(dst + xo[s & 7] + s * 128) = (uint16_t)(zp & 0xffffu);
+                        *(uint16_t*)(dst + xo[(s + 1) & 7] + (s + 1) * 128) = (uint16_t)(zp >> 16);
+                        db[l - 1] += E::unpack_lo(zp) + E::unpack_hi(zp);
+                    }
+                    release_acc();
                 }
-                release_acc();
             }
             if (!ok) break;
             // ---- dW_0 of this tile: add the accumulator to the register slice ----
             {
-                ok = ok && mbar_wait(acc_full, step & 1u, abort_flag, p.status, kStatusEpiAcc);
-                ++step;
+                wait_acc();
                 if (!ok) break;
                 tc_fence_after();
-                uint32_t v[32];
-                tmem_ld_32x32(t_acc, v);
+                uint32_t v[CPT];
+                tmem_ld_cols(t_acc, v);
                 tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) dw0[i] += __uint_as_float(v[i]);
+                for (int i = 0; i < CPT; ++i) dw0[i] += __uint_as_float(v[i]);
                 release_acc();
             }
         }
 
+        if (blockIdx.x == 0 && warp == 2 && lane == 0 && p.timing) {
+            p.timing[3] = (unsigned long long)(clock64() - e_start);  // epilogue warp: whole tile loop
+            p.timing[4] = (unsigned long long)e_wait;                 // ... of which waiting for the tensor pipe
+        }
         // ---- one add per parameter per CTA ----
         if (ok && !*abort_flag && n_my_tiles > 0) {
             tc_fence_after();
+            constexpr int NE = NS / CPT;  // column groups: each takes 1/NE of every accumulator's columns
             const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
             for (int l = 1; l <= 3; ++l) {
                 float* dW = (float*)p.net[l].weightsGrad + (size_t)f * 128;
-                for (int c = 0; c < 2; ++c) {
-                    const int col = h * 64 + c * 32;
+                for (int c = 0; c < 128 / NE; c += 32) {
+                    const int col = e * (128 / NE) + c;
                     uint32_t v[32];
-                    tmem_ld_32x32(lane_base + kColDW1 + (uint32_t)(l - 1) * 128u + (uint32_t)col, v);
+                    tmem_ld_cols(lane_base + kColDW1 + (uint32_t)(l - 1) * 128u + (uint32_t)col, v);
                     tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 32; ++i) atomicAdd(dW + col + i, __uint_as_float(v[i]));
@@ -451,16 +564,16 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
             {
                 // dW_4^T: lane = input feature, column = output feature.
                 float* dW = (float*)p.net[4].weightsGrad;
-                uint32_t v[32];
-                tmem_ld_32x32(lane_base + kColDW4T + (uint32_t)col0, v);
+                uint32_t v[CPT];
+                tmem_ld_cols(lane_base + kColDW4T + (uint32_t)col0, v);
                 tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) atomicAdd(dW + (size_t)(col0 + i) * 128 + f, __uint_as_float(v[i]));
+                for (int i = 0; i < CPT; ++i) atomicAdd(dW + (size_t)(col0 + i) * 128 + f, __uint_as_float(v[i]));
             }
             {
                 float* dW = (float*)p.net[0].weightsGrad + (size_t)f * 64 + col0;
 #pragma unroll
-                for (int i = 0; i < 32; ++i) atomicAdd(dW + i, dw0[i]);
+                for (int i = 0; i < CPT; ++i) atomicAdd(dW + i, dw0[i]);
             }
 #pragma unroll
             for (int l = 0; l < NL; ++l)
@@ -492,6 +605,7 @@ struct TcWorkspace {
     int sm_count = 0;
     uint32_t* status = nullptr;       // device word, set by kernels that give up on a wait
     uint32_t* status_host = nullptr;  // pinned copy
+    unsigned long long* timing = nullptr;  // device, 8 words of kernel diagnostics
     EncodeTiledFn encode = nullptr;
 };
 
@@ -518,6 +632,8 @@ TcWorkspace* tc_workspace_create(int ordinal, std::string* err)
     if (e == cudaSuccess) e = cudaMalloc((void**)&ws->status, sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMemset(ws->status, 0, sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMallocHost((void**)&ws->status_host, sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMalloc((void**)&ws->timing, 8 * sizeof(unsigned long long));
+    if (e == cudaSuccess) e = cudaMemset(ws->timing, 0, 8 * sizeof(unsigned long long));
     if (e == cudaSuccess) {
         void* fn = nullptr;
         cudaDriverEntryPointQueryResult qres;
@@ -538,7 +654,15 @@ void tc_workspace_destroy(TcWorkspace* ws)
     if (!ws) return;
     if (ws->status) cudaFree(ws->status);
     if (ws->status_host) cudaFreeHost(ws->status_host);
+    if (ws->timing) cudaFree(ws->timing);
     delete ws;
+}
+
+cudaError_t tc_read_timing(cudaStream_t st, TcWorkspace* ws, unsigned long long* out8)
+{
+    cudaError_t e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return e;
+    return cudaMemcpy(out8, ws->timing, 8 * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
 }
 
 cudaError_t tc_read_status(cudaStream_t st, TcWorkspace* ws, uint32_t* status)
@@ -596,6 +720,7 @@ cudaError_t launch_learn_gradient_tc(cudaStream_t st, TcWorkspace* ws, const Mlp
     p.n_tiles = (a.count + wide::NS - 1) / wide::NS;
     p.loss_scale = c.loss == MLP_LOSS_MSE_MEAN ? 1.0f / 64.0f : 1.0f;
     p.act_alpha = c.act_alpha;
+    p.timing = ws->timing;
     cudaError_t e = cudaErrorInvalidValue;
 #define MLPB200_DISPATCH(FMT_, ACT_) \
     if (c.dtype == FMT_ && c.hidden_act == ACT_) e = launch_wide<FMT_, ACT_>(st, ws, mx, mt, p);
