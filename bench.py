@@ -234,9 +234,11 @@ def main():
         ts.append(teacher_targets(torch, cfg, x, seed=2))
     torch.cuda.synchronize()
 
+    from slang_b200.dist import allreduce_gradients
+
     def allreduce():
         if world > 1:
-            dist.all_reduce(grads_t)
+            allreduce_gradients(grads_t)  # fp32 sum of the flat gradient segment (NCCL over NVLink)
 
     def step(i):
         b = i % n_batches
