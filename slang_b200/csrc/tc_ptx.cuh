@@ -67,7 +67,7 @@ __device__ __forceinline__ void mbar_drain(uint64_t* bar, uint32_t parity)
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // 2-D tiled TMA load into this CTA's shared memory, completion counted in bytes on an mbarrier.
-// No cluster multicast in any form.
+// A plain per-CTA load: every CTA fetches its own tile.
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int32_t c0, int32_t c1, uint64_t* bar)
 {
     asm volatile(
