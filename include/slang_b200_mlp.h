@@ -134,6 +134,29 @@ int32_t mlp_dispatch(MlpDevice* device, MlpKernel* kernel, const void* args, siz
 /* Number of CUDA kernels launched through this device handle since it was created. */
 uint64_t mlp_device_launch_count(const MlpDevice* device);
 
+/* ---- learnGradient without any allocation ------------------------------------------------- */
+
+/* No counterpart in the reference.  For hosts that must not touch the CUDA allocator while they
+ * train: an engine that claimed its whole device-memory budget at start-up and sub-allocates from its
+ * own arena, or a frame loop that fits a small network between draws and cannot afford the implicit
+ * device-wide synchronisation of cudaMalloc / cudaFree.  This is learnGradient with ordered sums
+ * (the same two kernels and the same results as entry point "learnGradient_simt" with
+ * MLP_FLAG_SEQUENTIAL_SUM), but the per-sample vectors it parks between its two passes live in a
+ * fixed 4 MiB area inside the library image rather than in a buffer the library would allocate.
+ *   - Needs no MlpDevice: pass the device index and a cudaStream_t (null = legacy default stream).
+ *     The network, loss, input and target addresses in `args` are the caller's own memory.
+ *   - Limit: count * (sum over layers of in + out widths) floats must fit in 1 048 576 floats
+ *     (e.g. 10 591 samples of the 2-16-16-16-1 network); larger batches get MLP_E_INVALID_ARG with
+ *     the limit in the message.  Split them: gradients and loss words accumulate across calls.
+ *   - The first call on each device resolves the area's device address (no allocation, but a CUDA
+ *     runtime query): make that first call before any stream capture begins.
+ *   - Every call on a device uses the same area and leaves its contents behind; each call
+ *     overwrites all the slots it later reads, so nothing has to be cleared.  Two calls whose
+ *     kernels overlap on the GPU (different streams, no ordering between them) race on the area.
+ *   - The 4 MiB are resident on every GPU that loads the library until the process exits. */
+int32_t mlp_learn_gradient_ordered_noalloc(int32_t device_ordinal, void* cuda_stream, const MlpConfig* config,
+                                           const MlpLearnGradParamsEx* args);
+
 /* ---- host-side layout helpers ------------------------------------------------------------- */
 
 /* allocateNetworkParameterStorage (mlp-training.cpp:217-250) in elements of the storage type:

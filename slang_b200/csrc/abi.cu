@@ -54,6 +54,11 @@ bool config_ok(const MlpConfig* c, std::string* why)
 
 }  // namespace
 
+namespace mlpb200 {
+// Lets the other translation units report through mlp_last_error_string().
+void set_last_error(const char* text) { g_last_error = text ? text : ""; }
+}  // namespace mlpb200
+
 struct MlpDevice {
     int ordinal = 0;
     cudaStream_t stream = nullptr;

@@ -9,6 +9,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <cstdio>
 #include <string>
 
 #include "mlp_common.cuh"
@@ -510,4 +511,72 @@ cudaError_t launch_adjust_parameters(cudaStream_t st, const MlpConfig& c, const 
     return cudaGetLastError();
 }
 
+// ------------------------------------------------------------------------------------------------
+// learnGradient with ordered sums and no allocation
+// ------------------------------------------------------------------------------------------------
+// The ordered-sum mode parks every sample's layer inputs and output gradients in global memory
+// between its two passes.  The variant below keeps that parking area inside the library image
+// instead of asking the CUDA allocator for it: 4 MiB per GPU that has loaded the library, resident
+// until the process exits.
+constexpr size_t kStaticScratchFloats = size_t(1) << 20;
+static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
+
+// In host code `g_static_scratch` is only a handle for the symbol; the address a kernel may
+// dereference differs per device and comes from cudaGetSymbolAddress with that device current.
+constexpr int kMaxDevices = 64;
+static float* g_static_scratch_addr[kMaxDevices] = {};
+
+void set_last_error(const char* text);  // abi.cu
+
 }  // namespace mlpb200
+
+using namespace mlpb200;
+
+extern "C" int32_t mlp_learn_gradient_ordered_noalloc(int32_t device_ordinal, void* cuda_stream, const MlpConfig* config,
+                                                      const MlpLearnGradParamsEx* args)
+{
+    if (!config || !args) { set_last_error("null argument"); return MLP_E_INVALID_ARG; }
+    if (device_ordinal < 0 || device_ordinal >= kMaxDevices) { set_last_error("device ordinal out of range"); return MLP_E_INVALID_ARG; }
+    const MlpConfig& c = *config;
+    if (c.n_layers < 1 || c.n_layers > MLP_MAX_LAYERS) { set_last_error("bad config: n_layers out of range"); return MLP_E_INVALID_ARG; }
+    for (int l = 0; l <= c.n_layers; ++l)
+        if (c.dims[l] < 1 || c.dims[l] > 1024) { set_last_error("bad config: layer width out of range"); return MLP_E_INVALID_ARG; }
+    if (!args->networkBuffer || !args->lossBuffer || (args->count && (!args->inputs || !args->targets))) {
+        set_last_error("null device address in the argument struct");
+        return MLP_E_INVALID_ARG;
+    }
+    const size_t need = sequential_scratch_floats_per_sample(c) * size_t(args->count);
+    if (need > kStaticScratchFloats) {
+        char buf[256];
+        snprintf(buf, sizeof buf,
+                 "%u samples need %zu scratch floats; the built-in scratch area holds %zu (at most %zu samples of this network)",
+                 args->count, need, (size_t)kStaticScratchFloats,
+                 (size_t)kStaticScratchFloats / sequential_scratch_floats_per_sample(c));
+        set_last_error(buf);
+        return MLP_E_INVALID_ARG;
+    }
+    cudaError_t e = cudaSetDevice(device_ordinal);
+    if (e == cudaSuccess && !g_static_scratch_addr[device_ordinal]) {
+        // First call on this device: look the array's device address up once and keep it.
+        float* addr = nullptr;
+        e = cudaGetSymbolAddress((void**)&addr, g_static_scratch);
+        if (e == cudaSuccess) g_static_scratch_addr[device_ordinal] = addr;
+    }
+    if (e != cudaSuccess) {
+        std::string msg = std::string("CUDA set-up for the built-in scratch area failed: ") + cudaGetErrorString(e);
+        set_last_error(msg.c_str());
+        return MLP_E_CUDA;
+    }
+    if (args->count == 0) return MLP_OK;
+    MlpLearnGradParamsEx a = *args;
+    a.flags |= MLP_FLAG_SEQUENTIAL_SUM;
+    int launches = 0;
+    std::string err;
+    e = launch_learn_gradient_simt((cudaStream_t)cuda_stream, c, a, g_static_scratch_addr[device_ordinal], &launches, &err);
+    if (e != cudaSuccess) {
+        if (err.empty()) err = std::string("kernel launch failed: ") + cudaGetErrorString(e);
+        set_last_error(err.c_str());
+        return e == cudaErrorInvalidValue ? MLP_E_NOT_AVAILABLE : MLP_E_CUDA;
+    }
+    return MLP_OK;
+}

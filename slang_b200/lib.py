@@ -18,6 +18,7 @@ EXPORTS = [
     "mlp_buffer_read", "mlp_buffer_write",
     "mlp_kernel_get", "mlp_kernel_get_for_config", "mlp_kernel_destroy", "mlp_kernel_implementation",
     "mlp_dispatch", "mlp_device_launch_count", "mlp_param_layout", "mlp_last_error_string",
+    "mlp_learn_gradient_ordered_noalloc",
 ]
 
 _lib = None
@@ -61,6 +62,7 @@ def load():
     L.mlp_param_layout.argtypes = [ctypes.POINTER(MlpConfig), ctypes.POINTER(ctypes.c_int64),
                                    ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64)]
     L.mlp_last_error_string.restype = ctypes.c_char_p
+    L.mlp_learn_gradient_ordered_noalloc.argtypes = [i32, vp, ctypes.POINTER(MlpConfig), vp]
     for name in EXPORTS:
         fn = getattr(L, name)
         if fn.restype is ctypes.c_int:
