@@ -133,6 +133,28 @@ __device__ __forceinline__ void act_pair(float z, float alpha, float& a, float& 
     }
 }
 
+// The same on two samples at once with the packed fp32 instructions of sm_100 (two results per
+// issued instruction): the epilogue is bound by instruction issue, not by the arithmetic units.
+template <int ACT>
+__device__ __forceinline__ void act_pair2(float2 z, float alpha, float2& a, float2& d)
+{
+    if constexpr (ACT == MLP_ACT_GELU_TANH) {
+        const float c0 = MLPB200_SQRT_2_OVER_PI, c1 = MLPB200_SQRT_2_OVER_PI * MLPB200_GELU_C;
+        const float2 C0 = make_float2(c0, c0), C1 = make_float2(c1, c1), C3 = make_float2(3.0f * c1, 3.0f * c1);
+        const float2 HALF = make_float2(0.5f, 0.5f), ONE = make_float2(1.0f, 1.0f);
+        const float2 z2 = __fmul2_rn(z, z);
+        const float2 u = __fmul2_rn(z, __ffma2_rn(C1, z2, C0));
+        const float2 t = make_float2(tanh_approx(u.x), tanh_approx(u.y));
+        const float2 hz = __fmul2_rn(z, HALF);
+        a = __ffma2_rn(hz, t, hz);
+        const float2 oms = __ffma2_rn(make_float2(-t.x, -t.y), t, ONE);
+        d = __ffma2_rn(__fmul2_rn(hz, oms), __ffma2_rn(C3, z2, C0), __ffma2_rn(HALF, t, HALF));
+    } else {
+        act_pair<ACT>(z.x, alpha, a.x, d.x);
+        act_pair<ACT>(z.y, alpha, a.y, d.y);
+    }
+}
+
 struct WideTrainParams {
     const MlpLayerPointers* net;
     uint32_t* loss_words;
@@ -427,15 +449,18 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                     tmem_ld_wait();
                     uint8_t* dst = smem + kA1 + (uint32_t)l * 16384u;
 #pragma unroll
+                    const float2 bias2 = make_float2(bias[l], bias[l]);
+#pragma unroll
                     for (int s = 0; s < CPT; s += 2) {
-                        float a0, d0, a1, d1;
-                        const float z0 = __uint_as_float(v[s]) + bias[l], z1 = __uint_as_float(v[s + 1]) + bias[l];
-                        act_pair<ACT>(E::round(z0), p.act_alpha, a0, d0);
-                        act_pair<ACT>(E::round(z1), p.act_alpha, a1, d1);
-                        const uint32_t ap = E::pack2(a0, a1);
+                        // bias, storage rounding of the pre-activation (one paired conversion), activation
+                        const float2 zf = __fadd2_rn(make_float2(__uint_as_float(v[s]), __uint_as_float(v[s + 1])), bias2);
+                        const uint32_t zr = E::pack2(zf.x, zf.y);
+                        float2 a, d;
+                        act_pair2<ACT>(make_float2(E::unpack_lo(zr), E::unpack_hi(zr)), p.act_alpha, a, d);
+                        const uint32_t ap = E::pack2(a.x, a.y);
                         *(uint16_t*)(dst + xo[s & 7] + s * 128) = (uint16_t)(ap & 0xffffu);
                         *(uint16_t*)(dst + xo[(s + 1) & 7] + (s + 1) * 128) = (uint16_t)(ap >> 16);
-                        dreg[l][s >> 1] = E::pack2(d0, d1);
+                        dreg[l][s >> 1] = E::pack2(d.x, d.y);
                     }
                     release_acc();
                 }
@@ -464,6 +489,7 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                         *slot = E::pack(dz);
                         db[NL - 1] += dz;
                     }
+                    release_acc();  // dZ_4 is in place: the backward products can start
                     // Sum over this warp's 32 features for each sample column: every exchange round
                     // halves the number of columns a lane carries; afterwards lane c * (32 / CPT)
                     // holds the sum of column c.
@@ -487,8 +513,9 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                     if ((lane % (32 / CPT)) == 0) s_loss_part[q * 64 + col0 + lane / (32 / CPT)] = lsq[0];
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&loss_bar[h]);
+                } else {
+                    release_acc();
                 }
-                release_acc();
                 if (q == 0) {
                     // The other feature half of these samples comes from the warp of quarter 1.
                     ok = ok && mbar_wait(&loss_bar[h], it & 1u, abort_flag, p.status, kStatusEpiLoss);
@@ -515,14 +542,18 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                     tmem_ld_wait();
                     uint8_t* dst = smem + kA1 + (uint32_t)(l - 1) * 16384u;
 #pragma unroll
+                    float2 dbp = make_float2(0.0f, 0.0f);
+#pragma unroll
                     for (int s = 0; s < CPT; s += 2) {
                         const uint32_t dd = dreg[l - 1][s >> 1];
-                        const uint32_t zp = E::pack2(__uint_as_float(v[s]) * E::unpack_lo(dd),
-                                                     __uint_as_float(v[s + 1]) * E::unpack_hi(dd));
+                        const float2 g = __fmul2_rn(make_float2(__uint_as_float(v[s]), __uint_as_float(v[s + 1])),
+                                                    make_float2(E::unpack_lo(dd), E::unpack_hi(dd)));
+                        const uint32_t zp = E::pack2(g.x, g.y);
                         *(uint16_t*)(dst + xo[s & 7] + s * 128) = (uint16_t)(zp & 0xffffu);
                         *(uint16_t*)(dst + xo[(s + 1) & 7] + (s + 1) * 128) = (uint16_t)(zp >> 16);
-                        db[l - 1] += E::unpack_lo(zp) + E::unpack_hi(zp);
+                        dbp = __fadd2_rn(dbp, make_float2(E::unpack_lo(zp), E::unpack_hi(zp)));
                     }
+                    db[l - 1] += dbp.x + dbp.y;
                     release_acc();
                 }
             }
