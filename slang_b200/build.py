@@ -26,6 +26,7 @@ UNITS = [
     ("abi.cu", []),
     ("simt_kernels.cu", ["-fmad=false"]),
     ("tc_kernels.cu", []),
+    ("tc_forward.cu", []),
 ]
 
 

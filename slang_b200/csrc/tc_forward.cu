@@ -1,0 +1,382 @@
+// Forward-only MLP on the tensor cores (tcgen05 / TMEM / TMA) for sm_100a: the inference sweep
+// (depth-4 networks of constant width 16..128, 16-bit weights, fp32 outputs) and any network whose
+// widths are DIN -> DH -> ... -> DH -> DOUT with every width in {16, 32, 64, 128}.
+//
+// Orientation: samples run along the 128 TMEM lanes (the MMA's M), features along the columns:
+//   Z_l [128 x out] = A_l [128 x in] . W_l^T        A: activations, K-major      B: W_l [out][in], K-major
+// An epilogue thread owns one sample row: it reads the row's accumulator columns, adds the bias,
+// applies the activation and writes the row of the next layer's operand as 16-byte chunks (or, after
+// the last layer, the fp32 outputs to global memory).  Several 128-sample tiles ("chains") are in
+// flight per CTA, each with its own accumulator columns, operand buffer and four epilogue warps, so
+// that one chain's epilogue overlaps another chain's products and input loads: at small widths the
+// work per tile is tiny and only concurrency hides the hand-off latencies.
+//
+// Operand layout: rows of min(64, width) elements per panel with the swizzle whose span equals the
+// panel row (32, 64 or 128 bytes), which is exactly what a TMA tile load with that swizzle produces.
+//
+// What the reference does instead: one thread per sample with scalar loops (coopVecMatMulAdd's
+// fallback, source/slang/hlsl.meta.slang:32835-32912) or one warp per 32 samples on mma.sync with
+// shuffle-packed operands (source/standard-modules/neural/mma-tiled-cuda.slang:88-138).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <string>
+
+#include "launchers.h"
+#include "mlp_common.cuh"
+#include "tc_host.h"
+#include "tc_ptx.cuh"
+
+namespace mlpb200 {
+
+using namespace ptx;
+
+namespace fwd {
+
+enum : uint32_t { kStatusCtrlX = 0x100u, kStatusCtrlAcc = 0x200u, kStatusEpiAcc = 0x400u };
+
+// Panel geometry of a [rows][D] 16-bit operand.
+__host__ __device__ constexpr int panel_w(int d) { return d < 64 ? d : 64; }              // elements per panel row
+__host__ __device__ constexpr int row_bytes(int d) { return panel_w(d) * 2; }             // 32, 64 or 128
+__host__ __device__ constexpr int swz_shift(int d) { return d >= 64 ? 0 : d == 32 ? 1 : 2; }
+__host__ __device__ constexpr int swz_mask(int d) { return d >= 64 ? 7 : d == 32 ? 3 : 1; }
+__host__ __device__ constexpr uint32_t layout_type(int d) { return d >= 64 ? 2u : d == 32 ? 4u : 6u; }  // SW128 / SW64 / SW32
+__host__ __device__ constexpr int imax(int a, int b) { return a > b ? a : b; }
+__host__ __device__ constexpr uint32_t pow2_at_least_32(uint32_t n) { uint32_t p = 32; while (p < n) p <<= 1; return p; }
+
+// Byte offset of the 16-byte chunk j (8 elements) of row r in a [rows][D] operand buffer.
+template <int D>
+__device__ __forceinline__ uint32_t chunk_offset(int rows, int r, int j)
+{
+    constexpr int cpp = panel_w(D) / 8;  // chunks per panel row
+    const int panel = j / cpp, cj = j % cpp;
+    return (uint32_t)panel * (uint32_t)(rows * row_bytes(D)) + (uint32_t)r * row_bytes(D) +
+           (uint32_t)((cj ^ ((r >> swz_shift(D)) & swz_mask(D))) << 4);
+}
+
+struct Params {
+    const MlpLayerPointers* net;
+    float* out;
+    uint32_t* status;
+    uint32_t count;
+    uint32_t n_tiles;
+    float act_alpha;
+};
+
+template <int FMT> struct Cvt;
+template <> struct Cvt<MLP_BF16> {
+    __device__ static __forceinline__ float round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+    __device__ static __forceinline__ uint32_t pack2(float lo, float hi)
+    {
+        __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&t);
+    }
+};
+template <> struct Cvt<MLP_F16> {
+    __device__ static __forceinline__ float round(float v) { return __half2float(__float2half_rn(v)); }
+    __device__ static __forceinline__ uint32_t pack2(float lo, float hi)
+    {
+        __half2 t = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&t);
+    }
+};
+
+template <int DIN, int DH, int DOUT, int NL, int NCH>
+struct Geometry {
+    static constexpr int kThreads = 64 + 128 * NCH;
+    static constexpr int kAccCols = imax(DH, DOUT);
+    static constexpr uint32_t kTmemCols = pow2_at_least_32(NCH * kAccCols);
+    __host__ __device__ static constexpr int in_dim(int l) { return l == 0 ? DIN : DH; }
+    __host__ __device__ static constexpr int out_dim(int l) { return l == NL - 1 ? DOUT : DH; }
+    __host__ __device__ static constexpr uint32_t w_bytes(int l) { return (uint32_t)(in_dim(l) * out_dim(l) * 2); }
+    __host__ __device__ static constexpr uint32_t w_off(int l)
+    {
+        uint32_t o = 0;
+        for (int i = 0; i < l; ++i) o += (w_bytes(i) + 1023u) & ~1023u;
+        return o;
+    }
+    static constexpr uint32_t kActBytes = (uint32_t)(128 * imax(DIN, DH) * 2 + 1023) & ~1023u;
+    static constexpr uint32_t kAct = w_off(NL);
+    static constexpr uint32_t kBias = kAct + NCH * kActBytes;     // fp32 [NL][128]
+    static constexpr uint32_t kBars = kBias + NL * 128 * 4;       // x_full[NCH], acc_full[NCH], acc_free[NCH]
+    static constexpr uint32_t kTmemPtr = kBars + 3 * NCH * 8;
+    static constexpr uint32_t kAbort = kTmemPtr + 4;
+    static constexpr uint32_t kSmemBytes = kAbort + 4 + 1024;
+};
+
+template <int DIN, int DH, int DOUT, int NL, int FMT, int ACT, int OUT_ACT, int NCH>
+__global__ void __launch_bounds__(64 + 128 * NCH, 1)
+forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const Params p)
+{
+    using G = Geometry<DIN, DH, DOUT, NL, NCH>;
+    using C = Cvt<FMT>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const uint32_t sbase = smem_u32(smem);
+    uint64_t* x_full = (uint64_t*)(smem + G::kBars);
+    uint64_t* acc_full = x_full + NCH;
+    uint64_t* acc_free = acc_full + NCH;
+    uint32_t* tmem_ptr = (uint32_t*)(smem + G::kTmemPtr);
+    volatile uint32_t* abort_flag = (volatile uint32_t*)(smem + G::kAbort);
+    float* s_bias = (float*)(smem + G::kBias);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t n_my_tiles = (p.n_tiles > blockIdx.x) ? (p.n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    constexpr uint32_t kXBytes = 128u * DIN * 2u;
+
+    if (threadIdx.x == 0) {
+        for (int c = 0; c < NCH; ++c) {
+            mbar_init(&x_full[c], 1);
+            mbar_init(&acc_full[c], 1);
+            mbar_init(&acc_free[c], 4);
+        }
+        *abort_flag = 0u;
+        fence_mbar_init();
+        prefetch_tmap(&tmap_x);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_ptr, G::kTmemCols);
+        tmem_relinquish();
+    }
+    // Weights into shared memory, row-major rows re-cut into swizzled panels; biases as fp32.
+    for (int l = 0; l < NL; ++l) {
+        const int in = G::in_dim(l), out = G::out_dim(l);
+        const uint4* src = (const uint4*)p.net[l].weights;
+        const int cpr = in / 8;
+        for (int idx = threadIdx.x; idx < out * cpr; idx += G::kThreads) {
+            const int o = idx / cpr, j = idx % cpr;
+            const uint32_t off = (l == 0) ? chunk_offset<DIN>(out, o, j) : chunk_offset<DH>(out, o, j);
+            *(uint4*)(smem + G::w_off(l) + off) = src[idx];
+        }
+        for (int j = threadIdx.x; j < 128; j += G::kThreads)
+            s_bias[l * 128 + j] = j < out ? load_as_f32(FMT, (const void*)p.net[l].biases, j) : 0.0f;
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_ptr;
+
+    // The i-th tile of this CTA (global tile blockIdx.x + i * gridDim.x) runs on chain i % NCH.
+    if (warp == 0) {
+        // =================================== control warp ==========================================
+        if (n_my_tiles > 0) {
+            const bool leader = elect_one();
+            constexpr uint32_t F = FMT == MLP_BF16 ? 1u : 0u;
+            const uint32_t lo_base = (sbase & 0x3FFFFu) >> 4;
+            bool ok = true;
+            uint32_t steps[NCH];  // products issued so far per chain
+#pragma unroll
+            for (int c = 0; c < NCH; ++c) steps[c] = 0;
+            if (leader) {
+#pragma unroll
+                for (int c = 0; c < NCH; ++c) {
+                    if ((uint32_t)c < n_my_tiles) {
+                        const uint32_t tile = blockIdx.x + (uint32_t)c * gridDim.x;
+                        mbar_expect_tx(&x_full[c], kXBytes);
+#pragma unroll
+                        for (int pn = 0; pn < DIN / panel_w(DIN); ++pn)
+                            tma_load_2d(smem + G::kAct + c * G::kActBytes + pn * (128 * row_bytes(DIN)), &tmap_x, pn * panel_w(DIN),
+                                        (int32_t)(tile * 128u), &x_full[c]);
+                    }
+                }
+            }
+            const uint32_t rounds = (n_my_tiles + NCH - 1) / NCH;
+            for (uint32_t j = 0; j < rounds && ok; ++j) {
+#pragma unroll
+                for (int l = 0; l < NL; ++l) {
+#pragma unroll
+                    for (int c = 0; c < NCH; ++c) {
+                        if (j * NCH + c < n_my_tiles && ok) {
+                            // Every phase of the chain's barriers is observed in order.
+                            if (steps[c] > 0) ok = mbar_wait(&acc_free[c], (steps[c] - 1) & 1u, abort_flag, p.status, kStatusCtrlAcc);
+                            if (l == 0) ok = ok && mbar_wait(&x_full[c], j & 1u, abort_flag, p.status, kStatusCtrlX);
+                            tc_fence_after();
+                            if (ok) {
+                                const uint32_t acc = tmem_base + (uint32_t)(c * G::kAccCols);
+                                const uint32_t abuf = G::kAct + (uint32_t)c * G::kActBytes;
+                                if (leader) {
+                                    if (l == 0) {
+                                        constexpr uint32_t hi = (uint32_t)((8 * row_bytes(DIN)) >> 4) | (1u << 14) | (layout_type(DIN) << 29);
+                                        constexpr uint32_t idesc = umma_idesc(F, 0, 0, 128, G::out_dim(0));
+#pragma unroll
+                                        for (int k = 0; k < DIN / 16; ++k) {
+                                            constexpr int kpp = panel_w(DIN) / 16;  // K steps per panel
+                                            const uint32_t ka = (uint32_t)(k / kpp) * (uint32_t)(128 * row_bytes(DIN)) + (uint32_t)(k % kpp) * 32u;
+                                            const uint32_t kb = (uint32_t)(k / kpp) * (uint32_t)(G::out_dim(0) * row_bytes(DIN)) + (uint32_t)(k % kpp) * 32u;
+                                            const uint64_t da = ((uint64_t)hi << 32) | (lo_base + ((abuf + ka) >> 4) + (1u << 16));
+                                            const uint64_t db = ((uint64_t)hi << 32) | (lo_base + ((G::w_off(0) + kb) >> 4) + (1u << 16));
+                                            umma_f16(acc, da, db, idesc, k > 0);
+                                        }
+                                    } else {
+                                        constexpr uint32_t hi = (uint32_t)((8 * row_bytes(DH)) >> 4) | (1u << 14) | (layout_type(DH) << 29);
+                                        const uint32_t idesc = umma_idesc(F, 0, 0, 128, G::out_dim(l));
+#pragma unroll
+                                        for (int k = 0; k < DH / 16; ++k) {
+                                            constexpr int kpp = panel_w(DH) / 16;
+                                            const uint32_t ka = (uint32_t)(k / kpp) * (uint32_t)(128 * row_bytes(DH)) + (uint32_t)(k % kpp) * 32u;
+                                            const uint32_t kb = (uint32_t)(k / kpp) * (uint32_t)(G::out_dim(l) * row_bytes(DH)) + (uint32_t)(k % kpp) * 32u;
+                                            const uint64_t da = ((uint64_t)hi << 32) | (lo_base + ((abuf + ka) >> 4) + (1u << 16));
+                                            const uint64_t db = ((uint64_t)hi << 32) | (lo_base + ((G::w_off(l) + kb) >> 4) + (1u << 16));
+                                            umma_f16(acc, da, db, idesc, k > 0);
+                                        }
+                                    }
+                                    umma_commit(&acc_full[c]);
+                                }
+                                __syncwarp();
+                                ++steps[c];
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp >= 2) {
+        // =================================== epilogue warps ========================================
+        const int c = (warp - 2) >> 2;   // chain
+        const int q = warp & 3;          // TMEM lane quarter this warp may read
+        const int r = q * 32 + lane;     // the sample row this thread owns
+        const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * G::kAccCols);
+        uint8_t* abuf = smem + G::kAct + c * G::kActBytes;
+        uint32_t step = 0;
+        bool ok = true;
+        for (uint32_t i = (uint32_t)c; i < n_my_tiles && ok; i += NCH) {
+            const uint32_t tile = blockIdx.x + i * gridDim.x;
+#pragma unroll
+            for (int l = 0; l < NL; ++l) {
+                ok = ok && mbar_wait(&acc_full[c], step & 1u, abort_flag, p.status, kStatusEpiAcc);
+                ++step;
+                if (ok) {
+                    tc_fence_after();
+                    const bool last = (l == NL - 1);
+                    if (last && q == 0 && lane == 0 && i + NCH < n_my_tiles) {
+                        // The last product has read this chain's operand buffer: fetch the chain's next tile.
+                        const uint32_t next = blockIdx.x + (i + NCH) * gridDim.x;
+                        mbar_expect_tx(&x_full[c], kXBytes);
+#pragma unroll
+                        for (int pn = 0; pn < DIN / panel_w(DIN); ++pn)
+                            tma_load_2d(abuf + pn * (128 * row_bytes(DIN)), &tmap_x, pn * panel_w(DIN), (int32_t)(next * 128u), &x_full[c]);
+                    }
+                    const int out = G::out_dim(l);
+                    const float* bl = s_bias + l * 128;
+                    const uint64_t row_index = (uint64_t)tile * 128u + (uint64_t)r;
+#pragma unroll
+                    for (int c0 = 0; c0 < G::out_dim(l); c0 += 16) {
+                        uint32_t v[16];
+                        tmem_ld_32x16(t_acc + (uint32_t)c0, v);
+                        tmem_ld_wait();
+                        float z[16];
+#pragma unroll
+                        for (int k = 0; k < 16; k += 4) {
+                            const float4 b4 = *(const float4*)(bl + c0 + k);
+                            z[k + 0] = C::round(__uint_as_float(v[k + 0]) + b4.x);
+                            z[k + 1] = C::round(__uint_as_float(v[k + 1]) + b4.y);
+                            z[k + 2] = C::round(__uint_as_float(v[k + 2]) + b4.z);
+                            z[k + 3] = C::round(__uint_as_float(v[k + 3]) + b4.w);
+                        }
+                        if (!last) {
+                            uint32_t pk[8];
+#pragma unroll
+                            for (int k = 0; k < 16; k += 2)
+                                pk[k >> 1] = C::pack2(act_value(ACT, p.act_alpha, z[k]), act_value(ACT, p.act_alpha, z[k + 1]));
+                            // the next layer reads this buffer as a [128][DH] operand
+                            *(uint4*)(abuf + chunk_offset<DH>(128, r, c0 / 8)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                            *(uint4*)(abuf + chunk_offset<DH>(128, r, c0 / 8 + 1)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                        } else if (row_index < p.count) {
+                            float* dst = p.out + row_index * (uint64_t)out + c0;
+#pragma unroll
+                            for (int k = 0; k < 16; k += 4)
+                                *(float4*)(dst + k) = make_float4(act_value(OUT_ACT, p.act_alpha, z[k]), act_value(OUT_ACT, p.act_alpha, z[k + 1]),
+                                                                  act_value(OUT_ACT, p.act_alpha, z[k + 2]), act_value(OUT_ACT, p.act_alpha, z[k + 3]));
+                        }
+                    }
+                    tc_fence_before();
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&acc_free[c]);
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, G::kTmemCols);
+    }
+}
+
+}  // namespace fwd
+
+// ------------------------------------------------------------------------------------------------
+// Host side
+// ------------------------------------------------------------------------------------------------
+static bool width_ok(int d) { return d == 16 || d == 32 || d == 64 || d == 128; }
+
+bool tc_forward_supported(const MlpConfig& c)
+{
+    if (c.n_layers < 2 || c.n_layers > 5) return false;
+    if (c.dtype != MLP_BF16 && c.dtype != MLP_F16) return false;
+    if (c.input_dtype != c.dtype || c.encoding != MLP_ENC_NONE) return false;
+    const int din = c.dims[0], dh = c.dims[1], dout = c.dims[c.n_layers];
+    for (int l = 1; l < c.n_layers; ++l)
+        if (c.dims[l] != dh) return false;
+    if (!width_ok(din) || !width_ok(dh) || !width_ok(dout)) return false;
+    // shapes that are instantiated below
+    const bool constant_width = (din == dh && dh == dout && c.n_layers == 4);
+    const bool wide = (din == 64 && dh == 128 && dout == 64 && c.n_layers == 5);
+    if (!constant_width && !wide) return false;
+    if (constant_width && !(c.hidden_act == MLP_ACT_RELU && c.output_act == MLP_ACT_IDENTITY)) return false;
+    if (wide && !(c.hidden_act == MLP_ACT_GELU_TANH && c.output_act == MLP_ACT_IDENTITY)) return false;
+    return true;
+}
+
+template <int DIN, int DH, int DOUT, int NL, int FMT, int ACT, int OUT_ACT, int NCH>
+static cudaError_t launch_fwd(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const MlpForwardParams& a, std::string* err)
+{
+    using G = fwd::Geometry<DIN, DH, DOUT, NL, NCH>;
+    static_assert(G::kSmemBytes <= 227 * 1024, "shared memory budget");
+    static_assert(G::kTmemCols <= 512, "tensor memory budget");
+    CUtensorMap mx;
+    const CUtensorMapDataType dt = FMT == MLP_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const CUtensorMapSwizzle sw = DIN >= 64 ? CU_TENSOR_MAP_SWIZZLE_128B : DIN == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
+    if (!make_tile_map(ws, &mx, dt, 2, a.inputs, a.count, DIN, fwd::panel_w(DIN), 128, sw, err)) return cudaErrorInvalidValue;
+    if (a.outputs & 15u) { if (err) *err = "outputs must be 16-byte aligned"; return cudaErrorInvalidValue; }
+    fwd::Params p;
+    p.net = (const MlpLayerPointers*)a.networkBuffer;
+    p.out = (float*)a.outputs;
+    p.status = ws->status;
+    p.count = a.count;
+    p.n_tiles = (a.count + 127u) / 128u;
+    p.act_alpha = c.act_alpha;
+    auto kern = fwd::forward_tc_kernel<DIN, DH, DOUT, NL, FMT, ACT, OUT_ACT, NCH>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)G::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    const uint32_t grid = p.n_tiles < (uint32_t)ws->sm_count ? p.n_tiles : (uint32_t)ws->sm_count;
+    kern<<<grid, G::kThreads, G::kSmemBytes, st>>>(mx, p);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_forward_tc(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const MlpForwardParams& a, int* launches,
+                              std::string* err)
+{
+    if (!tc_forward_supported(c)) { if (err) *err = "shape not built for the tensor-core forward path"; return cudaErrorInvalidValue; }
+    if (a.count == 0) return cudaSuccess;
+    cudaError_t e = cudaErrorInvalidValue;
+    const int w = c.dims[1];
+    const bool wide = c.n_layers == 5;
+#define MLPB200_FWD(W_, FMT_, NCH_) \
+    if (!wide && w == W_ && c.dtype == FMT_) e = launch_fwd<W_, W_, W_, 4, FMT_, MLP_ACT_RELU, MLP_ACT_IDENTITY, NCH_>(st, ws, c, a, err);
+    MLPB200_FWD(16, MLP_F16, 6) MLPB200_FWD(32, MLP_F16, 6) MLPB200_FWD(64, MLP_F16, 6) MLPB200_FWD(128, MLP_F16, 2)
+    MLPB200_FWD(16, MLP_BF16, 6) MLPB200_FWD(32, MLP_BF16, 6) MLPB200_FWD(64, MLP_BF16, 6) MLPB200_FWD(128, MLP_BF16, 2)
+#undef MLPB200_FWD
+    if (wide && c.dtype == MLP_BF16) e = launch_fwd<64, 128, 64, 5, MLP_BF16, MLP_ACT_GELU_TANH, MLP_ACT_IDENTITY, 2>(st, ws, c, a, err);
+    if (wide && c.dtype == MLP_F16) e = launch_fwd<64, 128, 64, 5, MLP_F16, MLP_ACT_GELU_TANH, MLP_ACT_IDENTITY, 2>(st, ws, c, a, err);
+    *launches += 1;
+    return e;
+}
+
+}  // namespace mlpb200

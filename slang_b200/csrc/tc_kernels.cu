@@ -28,6 +28,7 @@
 
 #include "launchers.h"
 #include "mlp_common.cuh"
+#include "tc_host.h"
 #include "tc_ptx.cuh"
 
 namespace mlpb200 {
@@ -448,7 +449,6 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                     tmem_ld_cols(t_acc, v);
                     tmem_ld_wait();
                     uint8_t* dst = smem + kA1 + (uint32_t)l * 16384u;
-#pragma unroll
                     const float2 bias2 = make_float2(bias[l], bias[l]);
 #pragma unroll
                     for (int s = 0; s < CPT; s += 2) {
@@ -541,7 +541,6 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                     tmem_ld_cols(t_acc, v);
                     tmem_ld_wait();
                     uint8_t* dst = smem + kA1 + (uint32_t)(l - 1) * 16384u;
-#pragma unroll
                     float2 dbp = make_float2(0.0f, 0.0f);
 #pragma unroll
                     for (int s = 0; s < CPT; s += 2) {
@@ -627,21 +626,6 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
 // ------------------------------------------------------------------------------------------------
 // Host side
 // ------------------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-struct TcWorkspace {
-    int ordinal = 0;
-    int sm_count = 0;
-    uint32_t* status = nullptr;       // device word, set by kernels that give up on a wait
-    uint32_t* status_host = nullptr;  // pinned copy
-    unsigned long long* timing = nullptr;  // device, 8 words of kernel diagnostics
-    EncodeTiledFn encode = nullptr;
-};
-
-bool tc_forward_supported(const MlpConfig&) { return false; }
-
 bool tc_train_supported(const MlpConfig& c)
 {
     static const int dims[6] = {64, 128, 128, 128, 128, 64};
@@ -707,17 +691,15 @@ cudaError_t tc_read_status(cudaStream_t st, TcWorkspace* ws, uint32_t* status)
     return e;
 }
 
-// A [rows][cols] 16-bit row-major matrix viewed in boxes of box_rows x 64 columns with the 128-byte swizzle.
-static bool make_tile_map(TcWorkspace* ws, CUtensorMap* map, int dtype, uint64_t base, uint64_t rows, uint32_t cols,
-                          uint32_t box_rows, std::string* err)
+bool make_tile_map(TcWorkspace* ws, CUtensorMap* map, CUtensorMapDataType type, int elem_bytes, uint64_t base, uint64_t rows,
+                   uint32_t cols, uint32_t box_cols, uint32_t box_rows, CUtensorMapSwizzle swizzle, std::string* err)
 {
-    if (base & 15u) { if (err) *err = "inputs and targets must be 16-byte aligned for the TMA path"; return false; }
+    if (base & 15u) { if (err) *err = "inputs, targets and outputs must be 16-byte aligned for the TMA path"; return false; }
     const cuuint64_t gdim[2] = {cols, rows};
-    const cuuint64_t gstride[1] = {(cuuint64_t)cols * 2};
-    const cuuint32_t box[2] = {64, box_rows};
+    const cuuint64_t gstride[1] = {(cuuint64_t)cols * elem_bytes};
+    const cuuint32_t box[2] = {box_cols, box_rows};
     const cuuint32_t estr[2] = {1, 1};
-    CUresult r = ws->encode(map, dtype == MLP_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
-                            (void*)base, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+    CUresult r = ws->encode(map, type, 2, (void*)base, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { if (err) *err = "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r); return false; }
     return true;
@@ -741,8 +723,9 @@ cudaError_t launch_learn_gradient_tc(cudaStream_t st, TcWorkspace* ws, const Mlp
     if (!tc_train_supported(c)) { if (err) *err = "shape not built for the tensor-core path"; return cudaErrorInvalidValue; }
     if (a.count == 0) return cudaSuccess;
     CUtensorMap mx, mt;
-    if (!make_tile_map(ws, &mx, c.dtype, a.inputs, a.count, 64, wide::NS, err)) return cudaErrorInvalidValue;
-    if (!make_tile_map(ws, &mt, c.dtype, a.targets, a.count, 64, wide::NS, err)) return cudaErrorInvalidValue;
+    const CUtensorMapDataType dt = c.dtype == MLP_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    if (!make_tile_map(ws, &mx, dt, 2, a.inputs, a.count, 64, 64, wide::NS, CU_TENSOR_MAP_SWIZZLE_128B, err)) return cudaErrorInvalidValue;
+    if (!make_tile_map(ws, &mt, dt, 2, a.targets, a.count, 64, 64, wide::NS, CU_TENSOR_MAP_SWIZZLE_128B, err)) return cudaErrorInvalidValue;
     WideTrainParams p;
     p.net = (const MlpLayerPointers*)a.networkBuffer;
     p.loss_words = (uint32_t*)a.lossBuffer;
@@ -764,12 +747,6 @@ cudaError_t launch_learn_gradient_tc(cudaStream_t st, TcWorkspace* ws, const Mlp
 #undef MLPB200_DISPATCH
     *launches += 1;
     return e;
-}
-
-cudaError_t launch_forward_tc(cudaStream_t, TcWorkspace*, const MlpConfig&, const MlpForwardParams&, int*, std::string* err)
-{
-    if (err) *err = "no tensor-core forward kernel for this shape";
-    return cudaErrorInvalidValue;
 }
 
 }  // namespace mlpb200
