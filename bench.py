@@ -169,6 +169,64 @@ def teacher_targets(torch, cfg, x, seed):
     return out
 
 
+def sweep_forward(args):
+    """Forward-only inference sweep: depth-4 ReLU networks of constant width 16/32/64/128 (fp16 weights,
+    Kaiming-uniform, seed 7; inputs uniform in [-1, 1]; fp32 outputs), batch 2^20 .. 2^26 in powers of 4.
+    Each point: samples/s, achieved HBM GB/s over the algorithmic 6w bytes per sample against the
+    measured copy bandwidth, and TFLOP/s.  L2 is flushed between timed iterations."""
+    import torch
+    from slang_b200 import config as C
+    from slang_b200.api import Device, Trainer
+    torch.cuda.set_device(0)
+    dev_t = torch.device("cuda", 0)
+    stream = torch.cuda.Stream(device=dev_t)
+    torch.cuda.set_stream(stream)
+    device = Device(0, stream.cuda_stream)
+    peaks = measured_peaks()
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev_t)
+    points = []
+    for w in (16, 32, 64, 128):
+        cfg = C.named_config("c5_w%d" % w)
+        tr = Trainer(device, cfg, C.init_params(cfg, seed=7, scheme="kaiming"))
+        assert tr.k_forward.implementation == "tcgen05"
+        for lg in (20, 22, 24, 26):
+            n = 1 << lg
+            gen = torch.Generator(device=dev_t); gen.manual_seed(7)
+            x = torch.empty((n, w), dtype=torch.float16, device=dev_t)
+            piece = 1 << 22
+            for i0 in range(0, n, piece):
+                x[i0:i0 + piece] = (torch.rand((min(piece, n - i0), w), device=dev_t, generator=gen) * 2 - 1).to(torch.float16)
+            out = torch.empty((n, w), dtype=torch.float32, device=dev_t)
+            times = []
+            for it in range(args.warmup + args.steps):
+                flush.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                tr.forward(x.data_ptr(), out.data_ptr(), n)
+                e1.record()
+                torch.cuda.synchronize()
+                if it >= args.warmup:
+                    times.append(e0.elapsed_time(e1))
+            ms = float(np.median(times))
+            sps = n / (ms * 1e-3)
+            gbs = sps * 6 * w / 1e9
+            points.append({"width": w, "batch": n, "ms": ms, "samples_per_s": sps, "hbm_gbs": gbs,
+                           "hbm_frac": gbs / peaks["hbm_gbs"], "tflops": sps * 8 * w * w / 1e12})
+            del x, out
+    device.wait()
+    best = max(points, key=lambda p: p["hbm_frac"])
+    line = {"metric": "MLP forward samples/sec (depth-4 constant width)", "value": best["samples_per_s"], "unit": UNIT,
+            "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": best["ms"], "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "forward sweep, widths 16-128, batch 2^20-2^26; value is the point with the best HBM fraction",
+                       "l2": "512 MB written between timed iterations"},
+            "roofline": {"bound": "hbm", "achieved": best["hbm_gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": best["hbm_frac"], "traffic": None, "kernel": "forward_tc_kernel", "peak_source": peaks["source"]},
+            "gpu_launches": device.launch_count, "sweep": points}
+    print(json.dumps(line), flush=True)
+    device.destroy()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -188,6 +246,10 @@ def main():
 
     if args.impl == "reference":
         reference_arm(args, rank)
+        return
+    if args.config == "c5_sweep":
+        if rank == 0:
+            sweep_forward(args)
         return
 
     import torch

@@ -48,7 +48,10 @@ constexpr int NS = 64;            // samples per tile
 constexpr int CH = MLPB200_CH;    // samples per chain (MMA N of the forward / input-gradient products)
 constexpr int NCH = NS / CH;      // chains per tile
 constexpr int D0 = 64, H = 128, DOUT = 64, NL = 5;
-constexpr int CPT = 16;           // sample columns per epilogue thread
+#ifndef MLPB200_CPT
+#define MLPB200_CPT 16
+#endif
+constexpr int CPT = MLPB200_CPT;  // sample columns per epilogue thread
 constexpr int kEpiWarps = 4 * (NS / CPT);      // one warp per TMEM lane quarter and column group
 constexpr int kWarpsPerChain = 4 * (CH / CPT);
 constexpr int kThreads = 64 + 32 * kEpiWarps;  // warp 0: TMA + MMA issue, warp 1: TMEM owner, then the epilogue warps
@@ -405,13 +408,10 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
         const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16) + kColAcc + (uint32_t)col0;
         // Byte offset of (row col0, feature f) inside a [64 x W] operand buffer, minus the swizzled chunk.
         const uint32_t pbase = (uint32_t)(f >> 6) * 8192u + (uint32_t)col0 * 128u + (uint32_t)(f & 7) * 2u;
-        uint32_t xo[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) xo[j] = pbase + (uint32_t)(((((f & 63) >> 3) ^ j)) << 4);
+        // Row s of this thread's column group puts feature f in 16-byte chunk ((f & 63) >> 3) ^ (s & 7);
+        // bit 4..6 of the base are that chunk for row 0, so the other rows' chunks are an XOR away.
+        const uint32_t xo0 = pbase + (uint32_t)(((f & 63) >> 3) << 4);
 
-        float bias[NL];
-#pragma unroll
-        for (int l = 0; l < NL; ++l) bias[l] = s_bias[l * 128 + f];
         uint32_t dreg[NL - 1][CPT / 2];  // activation derivatives of the four hidden layers, two per register
         float dw0[CPT];                  // this thread's slice of dW_0 (row f, columns col0..), summed over tiles
         float db[NL];                    // bias-gradient partial sums
@@ -449,7 +449,8 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                     tmem_ld_cols(t_acc, v);
                     tmem_ld_wait();
                     uint8_t* dst = smem + kA1 + (uint32_t)l * 16384u;
-                    const float2 bias2 = make_float2(bias[l], bias[l]);
+                    const float bl = s_bias[l * 128 + f];
+                    const float2 bias2 = make_float2(bl, bl);
 #pragma unroll
                     for (int s = 0; s < CPT; s += 2) {
                         // bias, storage rounding of the pre-activation (one paired conversion), activation
@@ -458,8 +459,8 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                         float2 a, d;
                         act_pair2<ACT>(make_float2(E::unpack_lo(zr), E::unpack_hi(zr)), p.act_alpha, a, d);
                         const uint32_t ap = E::pack2(a.x, a.y);
-                        *(uint16_t*)(dst + xo[s & 7] + s * 128) = (uint16_t)(ap & 0xffffu);
-                        *(uint16_t*)(dst + xo[(s + 1) & 7] + (s + 1) * 128) = (uint16_t)(ap >> 16);
+                        *(uint16_t*)(dst + (xo0 ^ (uint32_t)((s & 7) << 4)) + s * 128) = (uint16_t)(ap & 0xffffu);
+                        *(uint16_t*)(dst + (xo0 ^ (uint32_t)(((s + 1) & 7) << 4)) + (s + 1) * 128) = (uint16_t)(ap >> 16);
                         dreg[l][s >> 1] = E::pack2(d.x, d.y);
                     }
                     release_acc();
@@ -477,12 +478,13 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                     tmem_ld_cols(t_acc, v);
                     tmem_ld_wait();
                     uint8_t* dst = smem + kDZ4;
+                    const float bias_out = s_bias[(NL - 1) * 128 + f];
                     float lsq[CPT];
 #pragma unroll
                     for (int s = 0; s < CPT; ++s) {
                         const bool valid = tile * NS + col0 + s < p.count;
-                        uint16_t* slot = (uint16_t*)(dst + xo[s & 7] + s * 128);
-                        const float out = E::round(__uint_as_float(v[s]) + bias[NL - 1]);
+                        uint16_t* slot = (uint16_t*)(dst + (xo0 ^ (uint32_t)((s & 7) << 4)) + s * 128);
+                        const float out = E::round(__uint_as_float(v[s]) + bias_out);
                         const float diff = out - E::unpack(*slot);
                         const float dz = valid ? E::round((2.0f * p.loss_scale) * diff) : 0.0f;
                         lsq[s] = valid ? (diff * p.loss_scale) * diff : 0.0f;
@@ -548,8 +550,8 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                         const float2 g = __fmul2_rn(make_float2(__uint_as_float(v[s]), __uint_as_float(v[s + 1])),
                                                     make_float2(E::unpack_lo(dd), E::unpack_hi(dd)));
                         const uint32_t zp = E::pack2(g.x, g.y);
-                        *(uint16_t*)(dst + xo[s & 7] + s * 128) = (uint16_t)(zp & 0xffffu);
-                        *(uint16_t*)(dst + xo[(s + 1) & 7] + (s + 1) * 128) = (uint16_t)(zp >> 16);
+                        *(uint16_t*)(dst + (xo0 ^ (uint32_t)((s & 7) << 4)) + s * 128) = (uint16_t)(zp & 0xffffu);
+                        *(uint16_t*)(dst + (xo0 ^ (uint32_t)(((s + 1) & 7) << 4)) + (s + 1) * 128) = (uint16_t)(zp >> 16);
                         dbp = __fadd2_rn(dbp, make_float2(E::unpack_lo(zp), E::unpack_hi(zp)));
                     }
                     db[l - 1] += dbp.x + dbp.y;
