@@ -27,6 +27,7 @@ UNITS = [
     ("simt_kernels.cu", ["-fmad=false"]),
     ("tc_kernels.cu", []),
     ("tc_forward.cu", []),
+    ("tc_train_narrow.cu", []),
 ]
 
 

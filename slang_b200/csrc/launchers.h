@@ -22,6 +22,7 @@ cudaError_t launch_adjust_parameters(cudaStream_t st, const MlpConfig& c, const 
 // Tensor-core kernels (tc_kernels.cu).  tc_supported() says whether the shape is one they are built for.
 bool tc_forward_supported(const MlpConfig& c);
 bool tc_train_supported(const MlpConfig& c);
+bool tc_train_narrow_supported(const MlpConfig& c);
 struct TcWorkspace;  // per-device state: status word, SM count, tensor maps cache
 TcWorkspace* tc_workspace_create(int device_ordinal, std::string* err);
 void tc_workspace_destroy(TcWorkspace* ws);
@@ -29,6 +30,8 @@ cudaError_t launch_forward_tc(cudaStream_t st, TcWorkspace* ws, const MlpConfig&
                               int* launches, std::string* err);
 cudaError_t launch_learn_gradient_tc(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c,
                                      const MlpLearnGradParamsEx& a, int* launches, std::string* err);
+cudaError_t launch_learn_gradient_narrow(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c,
+                                         const MlpLearnGradParamsEx& a, int* launches, std::string* err);
 // Cycle counts CTA 0 of the last tensor-core learnGradient recorded (diagnostics).
 cudaError_t tc_read_timing(cudaStream_t st, TcWorkspace* ws, unsigned long long* out8);
 // Reads and clears the device status word (0 = no kernel gave up on a bounded wait).

@@ -628,7 +628,11 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
 // ------------------------------------------------------------------------------------------------
 // Host side
 // ------------------------------------------------------------------------------------------------
-bool tc_train_supported(const MlpConfig& c)
+static bool wide_supported(const MlpConfig& c);
+
+bool tc_train_supported(const MlpConfig& c) { return wide_supported(c) || tc_train_narrow_supported(c); }
+
+static bool wide_supported(const MlpConfig& c)
 {
     static const int dims[6] = {64, 128, 128, 128, 128, 64};
     if (c.n_layers != 5) return false;
@@ -722,7 +726,7 @@ static cudaError_t launch_wide(cudaStream_t st, TcWorkspace* ws, const CUtensorM
 cudaError_t launch_learn_gradient_tc(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const MlpLearnGradParamsEx& a,
                                      int* launches, std::string* err)
 {
-    if (!tc_train_supported(c)) { if (err) *err = "shape not built for the tensor-core path"; return cudaErrorInvalidValue; }
+    if (!wide_supported(c)) return launch_learn_gradient_narrow(st, ws, c, a, launches, err);
     if (a.count == 0) return cudaSuccess;
     CUtensorMap mx, mt;
     const CUtensorMapDataType dt = c.dtype == MLP_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;

@@ -1,0 +1,468 @@
+// learnGradient on the tensor cores for narrow networks: every layer width <= 64 (the fp16 CoopVec-style
+// network 4-32-32-32-32-4 and the neural-texture network enc(2->32)-64-64-64-3).
+//
+// Every layer is padded to 64 x 64 in shared memory (zero rows and columns), so one kernel shape
+// serves all such networks: padded features stay exactly zero through the forward and backward pass.
+// Orientation: the 128 samples of a tile run along the TMEM lanes (the MMA's M), features along the
+// columns; an epilogue thread owns one sample.
+//   forward   Z_l [128 x 64]  = A_l [128 x 64] . W_l^T        A: A_l, K-major          B: W_l [out][in], K-major
+//   input     dA_l [128 x 64] = dZ_l [128 x 64] . W_l          A: dZ_l, K-major         B: W_l, MN-major
+//   weights   dW_l [64 x 64] += dZ_l^T . A_l                   A: dZ_l, MN-major        B: A_l, MN-major (K = 128 samples)
+//   biases    db_l [64]      += dZ_l^T . 1                      A: dZ_l, MN-major        B: a constant column of ones
+// The thread that owns a sample builds the sample's input row itself (conversion or the frequency
+// encoding), reads its targets straight from global memory, keeps the activation derivatives of its
+// row in shared memory and keeps the running loss in registers.  Weight and bias gradients
+// accumulate in tensor memory over all tiles of the CTA and leave through one atomic add per
+// parameter per CTA.
+//
+// What the reference does instead: one thread per sample with per-element global atomics
+// (examples/mlp-training/mlp_sw.slang:28-58) or CoopVec calls whose CPU/CUDA fallback is scalar loops
+// (examples/mlp-training-coopvec/fflayer.slang:16-58, source/slang/hlsl.meta.slang:32835-32912).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <string>
+
+#include "launchers.h"
+#include "mlp_common.cuh"
+#include "tc_host.h"
+#include "tc_layout.cuh"
+#include "tc_ptx.cuh"
+
+namespace mlpb200 {
+
+using namespace ptx;
+
+namespace narrow {
+
+using namespace layout;
+
+constexpr int H = 64;         // padded width of every layer
+constexpr int TS = 128;       // samples per tile
+constexpr int kThreads = 64 + 128;
+constexpr uint32_t kMat = 64 * 64 * 2;     // one padded weight matrix: 64 rows of 128 bytes
+constexpr uint32_t kTile = 128 * 64 * 2;   // one [128][64] operand tile: 128 rows of 128 bytes
+
+enum : uint32_t { kStatusCtrl = 0x1000u, kStatusEpi = 0x2000u };
+
+struct Params {
+    MlpConfig cfg;
+    const MlpLayerPointers* net;
+    uint32_t* loss_words;
+    uint32_t* status;
+    const void* inputs;
+    const void* targets;
+    uint32_t count;
+    uint32_t n_tiles;
+};
+
+template <int FMT> struct Cvt;
+template <> struct Cvt<MLP_BF16> {
+    static constexpr uint32_t kUmmaFmt = 1;
+    __device__ static __forceinline__ float round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+    __device__ static __forceinline__ uint32_t pack2(float lo, float hi)
+    {
+        __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&t);
+    }
+    __device__ static __forceinline__ float lo(uint32_t p) { return __uint_as_float(p << 16); }
+    __device__ static __forceinline__ float hi(uint32_t p) { return __uint_as_float(p & 0xffff0000u); }
+    __device__ static __forceinline__ uint16_t one() { return 0x3F80; }
+};
+template <> struct Cvt<MLP_F16> {
+    static constexpr uint32_t kUmmaFmt = 0;
+    __device__ static __forceinline__ float round(float v) { return __half2float(__float2half_rn(v)); }
+    __device__ static __forceinline__ uint32_t pack2(float lo, float hi)
+    {
+        __half2 t = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&t);
+    }
+    __device__ static __forceinline__ float lo(uint32_t p) { return __half2float(__ushort_as_half((uint16_t)(p & 0xffffu))); }
+    __device__ static __forceinline__ float hi(uint32_t p) { return __half2float(__ushort_as_half((uint16_t)(p >> 16))); }
+    __device__ static __forceinline__ uint16_t one() { return 0x3C00; }
+};
+
+// Shared-memory map for NL layers (bytes from a 1024-aligned base).
+template <int NL>
+struct Map {
+    static constexpr uint32_t kW = 0;                          // NL padded weight matrices
+    static constexpr uint32_t kA = kW + NL * kMat;             // A_0 .. A_{NL-1}: layer inputs; dZ_{l-1} later replaces A_l
+    static constexpr uint32_t kD = kA + NL * kTile;            // activation derivatives of layers 0 .. NL-2
+    static constexpr uint32_t kDZ = kD + (NL - 1) * kTile;     // dZ of the last layer
+    static constexpr uint32_t kOnes = kDZ + kTile;             // [128 rows][16 elements]: first column one, rest zero
+    static constexpr uint32_t kBias = kOnes + 128 * 32;        // fp32 [NL][64]
+    static constexpr uint32_t kBars = kBias + NL * 64 * 4;     // acc_full, acc_free, tile_done
+    static constexpr uint32_t kTmemPtr = kBars + 3 * 8;
+    static constexpr uint32_t kAbort = kTmemPtr + 4;
+    static constexpr uint32_t kSmemBytes = kAbort + 4 + 1024;
+    // tensor-memory columns
+    static constexpr uint32_t kColAcc = 0, kColDW = 64, kColDB = 64 + 64 * NL, kTmemCols = 512;
+    static_assert(kColDB + 16 * NL <= 512, "tensor memory budget");
+    static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
+};
+
+template <int NL, int FMT>
+__global__ void __launch_bounds__(kThreads, 1) learn_gradient_narrow_kernel(const Params p)
+{
+    using M = Map<NL>;
+    using C = Cvt<FMT>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const uint32_t sbase = smem_u32(smem);
+    uint64_t* acc_full = (uint64_t*)(smem + M::kBars);
+    uint64_t* acc_free = acc_full + 1;
+    uint64_t* tile_done = acc_full + 2;
+    uint32_t* tmem_ptr = (uint32_t*)(smem + M::kTmemPtr);
+    volatile uint32_t* abort_flag = (volatile uint32_t*)(smem + M::kAbort);
+    float* s_bias = (float*)(smem + M::kBias);
+    const MlpConfig& c = p.cfg;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t n_my_tiles = (p.n_tiles > blockIdx.x) ? (p.n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+
+    if (threadIdx.x == 0) {
+        mbar_init(acc_full, 1);
+        mbar_init(acc_free, 4);
+        mbar_init(tile_done, 1);
+        *abort_flag = 0u;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_ptr, M::kTmemCols);
+        tmem_relinquish();
+    }
+    // Padded weights (zero outside [out][in]), biases, and the ones column.
+    for (int l = 0; l < NL; ++l) {
+        const int in = c.dims[l], out = c.dims[l + 1];
+        const uint16_t* W = (const uint16_t*)p.net[l].weights;
+        for (int idx = threadIdx.x; idx < H * H; idx += kThreads) {
+            const int o = idx / H, i = idx % H;
+            const uint16_t v = (o < out && i < in) ? W[o * in + i] : (uint16_t)0;
+            *(uint16_t*)(smem + M::kW + l * kMat + chunk_offset<H>(H, o, i / 8) + (i % 8) * 2) = v;
+        }
+        for (int j = threadIdx.x; j < H; j += kThreads)
+            s_bias[l * H + j] = j < out ? load_as_f32(FMT, (const void*)p.net[l].biases, j) : 0.0f;
+    }
+    for (int idx = threadIdx.x; idx < 128 * 16; idx += kThreads) {
+        const int r = idx / 16, i = idx % 16;
+        *(uint16_t*)(smem + M::kOnes + chunk_offset<16>(128, r, i / 8) + (i % 8) * 2) = (i == 0) ? C::one() : (uint16_t)0;
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_ptr;
+
+    if (warp == 0) {
+        // =================================== control warp ==========================================
+        if (n_my_tiles > 0) {
+            const bool leader = elect_one();
+            constexpr uint32_t F = C::kUmmaFmt;
+            constexpr uint32_t kIdFwd = umma_idesc(F, 0, 0, 128, H);   // acts (K) x W (K)
+            constexpr uint32_t kIdDx = umma_idesc(F, 0, 1, 128, H);    // dZ (K) x W (MN)
+            constexpr uint32_t kIdDw = umma_idesc(F, 1, 1, 128, H);    // dZ^T (MN) x acts (MN)
+            constexpr uint32_t kIdDb = umma_idesc(F, 1, 1, 128, 16);   // dZ^T (MN) x ones (MN)
+            const uint32_t lo_base = (sbase & 0x3FFFFu) >> 4;
+            constexpr uint32_t kHi128 = (1024u >> 4) | (1u << 14) | (2u << 29);  // 128-byte rows and swizzle
+            constexpr uint32_t kHi32 = (256u >> 4) | (1u << 14) | (6u << 29);    // 32-byte rows and swizzle (ones column)
+            // K-major [rows][64]: a K step of 16 elements is 32 bytes inside the 128-byte row.
+            auto desc_k = [&](uint32_t buf, int k) -> uint64_t {
+                return ((uint64_t)kHi128 << 32) | (lo_base + ((buf + (uint32_t)k * 32u) >> 4) + (1u << 16));
+            };
+            // MN-major [K rows][64]: a K step of 16 rows is 2048 bytes; a second 64-element block, where the
+            // instruction asks for 128, starts 16 bytes further (its results are never read).
+            auto desc_mn = [&](uint32_t buf, int k) -> uint64_t {
+                return ((uint64_t)kHi128 << 32) | (lo_base + ((buf + (uint32_t)k * 2048u) >> 4) + (1u << 16));
+            };
+            auto desc_ones = [&](int k) -> uint64_t {
+                return ((uint64_t)kHi32 << 32) | (lo_base + ((M::kOnes + (uint32_t)k * 512u) >> 4) + (1u << 16));
+            };
+            const uint32_t acc = tmem_base + M::kColAcc;
+            uint32_t n_free = 0;  // acc_free phases observed
+            bool ok = true;
+            auto wait_free = [&]() {
+                ok = ok && mbar_wait(acc_free, n_free & 1u, abort_flag, p.status, kStatusCtrl);
+                ++n_free;
+                tc_fence_after();
+            };
+            // dW_l and db_l of the current tile; `first` is true only for the launch's first tile.
+            auto grads = [&](int l, uint32_t dzbuf, bool first) {
+#pragma unroll
+                for (int k = 0; k < TS / 16; ++k) {
+                    umma_f16(tmem_base + M::kColDW + (uint32_t)l * 64u, desc_mn(dzbuf, k), desc_mn(M::kA + (uint32_t)l * kTile, k), kIdDw,
+                             (first && k == 0) ? 0u : 1u);
+                    umma_f16(tmem_base + M::kColDB + (uint32_t)l * 16u, desc_mn(dzbuf, k), desc_ones(k), kIdDb, (first && k == 0) ? 0u : 1u);
+                }
+            };
+            for (uint32_t it = 0; it < n_my_tiles && ok; ++it) {
+                const bool first = it == 0;
+                // ---- forward ----
+#pragma unroll
+                for (int l = 0; l < NL; ++l) {
+                    wait_free();  // A_l is in shared memory (l = 0: the input rows) and the accumulator is drained
+                    if (ok) {
+                        if (leader) {
+#pragma unroll
+                            for (int k = 0; k < H / 16; ++k)
+                                umma_f16(acc, desc_k(M::kA + (uint32_t)l * kTile, k), desc_k(M::kW + (uint32_t)l * kMat, k), kIdFwd, k > 0);
+                            umma_commit(acc_full);
+                        }
+                        __syncwarp();
+                    }
+                }
+                // ---- backward ----
+#pragma unroll
+                for (int l = NL - 1; l >= 1; --l) {
+                    wait_free();  // dZ_l is in shared memory
+                    if (ok) {
+                        const uint32_t dzbuf = (l == NL - 1) ? M::kDZ : M::kA + (uint32_t)(l + 1) * kTile;
+                        if (leader) {
+#pragma unroll
+                            for (int k = 0; k < H / 16; ++k)
+                                umma_f16(acc, desc_k(dzbuf, k), desc_mn(M::kW + (uint32_t)l * kMat, k), kIdDx, k > 0);
+                            grads(l, dzbuf, first);
+                            umma_commit(acc_full);
+                        }
+                        __syncwarp();
+                    }
+                }
+                wait_free();  // dZ_0 is in shared memory (in A_1's buffer, or the last layer's own buffer)
+                if (ok) {
+                    if (leader) {
+                        grads(0, NL == 1 ? M::kDZ : M::kA + kTile, first);
+                        umma_commit(tile_done);
+                    }
+                    __syncwarp();
+                }
+            }
+        }
+    } else if (warp >= 2) {
+        // =================================== epilogue warps ========================================
+        const int q = warp & 3;
+        const int r = q * 32 + lane;  // the sample row (TMEM lane) this thread owns
+        const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16) + M::kColAcc;
+        const int od = c.dims[NL];
+        const float loss_scale = c.loss == MLP_LOSS_MSE_MEAN ? 1.0f / (float)od : 1.0f;
+        float run_max = 0.0f, run_sum = 0.0f;
+        uint32_t n_full = 0;
+        bool ok = true;
+        auto release = [&]() {
+            tc_fence_before();
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_free);
+        };
+        auto wait_full = [&]() {
+            ok = ok && mbar_wait(acc_full, n_full & 1u, abort_flag, p.status, kStatusEpi);
+            ++n_full;
+            tc_fence_after();
+        };
+        auto row_chunk = [&](uint32_t buf, int j) -> uint4* { return (uint4*)(smem + buf + chunk_offset<H>(128, r, j)); };
+
+        for (uint32_t it = 0; it < n_my_tiles && ok; ++it) {
+            const uint64_t sample = ((uint64_t)blockIdx.x + (uint64_t)it * gridDim.x) * TS + (uint64_t)r;
+            const bool valid = sample < p.count;
+            // ---- the input row: conversion (and zero padding) or the frequency encoding ----
+            if (it > 0) ok = ok && mbar_wait(tile_done, (it - 1) & 1u, abort_flag, p.status, kStatusEpi);
+            if (!ok) break;
+            {
+                float x[H];
+#pragma unroll
+                for (int i = 0; i < H; ++i) x[i] = 0.0f;
+                if (valid) {
+                    if (c.encoding == MLP_ENC_FREQ2D) {
+#pragma unroll
+                        for (int u = 0; u < 2; ++u) {
+                            const float v = load_as_f32(c.input_dtype, p.inputs, sample * 2 + u);
+#pragma unroll
+                            for (int k = 0; k < 8; ++k) {
+                                const float arg = ldexpf(3.14159265358979323846f, k) * v;
+                                x[u * 16 + k * 2 + 0] = sinf(arg);
+                                x[u * 16 + k * 2 + 1] = cosf(arg);
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < H; ++i)
+                            if (i < c.dims[0]) x[i] = load_as_f32(c.input_dtype, p.inputs, sample * c.dims[0] + i);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < H / 8; ++j)
+                    *row_chunk(M::kA, j) = make_uint4(C::pack2(x[8 * j], x[8 * j + 1]), C::pack2(x[8 * j + 2], x[8 * j + 3]),
+                                                      C::pack2(x[8 * j + 4], x[8 * j + 5]), C::pack2(x[8 * j + 6], x[8 * j + 7]));
+                release();
+            }
+            // ---- forward ----
+#pragma unroll
+            for (int l = 0; l < NL; ++l) {
+                wait_full();
+                if (ok) {
+                    const bool last = (l == NL - 1);
+                    float loss = 0.0f;
+#pragma unroll
+                    for (int c0 = 0; c0 < H; c0 += 16) {
+                        uint32_t v[16];
+                        tmem_ld_32x16(t_acc + (uint32_t)c0, v);
+                        tmem_ld_wait();
+                        uint32_t pa[8], pd[8];
+#pragma unroll
+                        for (int k = 0; k < 16; k += 2) {
+                            float a2[2], d2[2];
+#pragma unroll
+                            for (int e = 0; e < 2; ++e) {
+                                const int j = c0 + k + e;
+                                const float z = C::round(__uint_as_float(v[k + e]) + s_bias[l * H + j]);
+                                if (!last) {
+                                    a2[e] = act_value(c.hidden_act, c.act_alpha, z);
+                                    d2[e] = act_deriv(c.hidden_act, c.act_alpha, z);
+                                } else {
+                                    // loss and dZ of the last layer; padded outputs and rows past the batch give zero
+                                    float dz = 0.0f;
+                                    if (valid && j < od) {
+                                        const float o = act_value(c.output_act, c.act_alpha, z);
+                                        const float diff = o - load_as_f32(c.target_dtype, p.targets, sample * od + j);
+                                        loss = fmaf(diff * loss_scale, diff, loss);
+                                        dz = ((2.0f * loss_scale) * diff) * act_deriv(c.output_act, c.act_alpha, z);
+                                    }
+                                    a2[e] = dz;
+                                    d2[e] = 0.0f;
+                                }
+                            }
+                            pa[k >> 1] = C::pack2(a2[0], a2[1]);
+                            pd[k >> 1] = C::pack2(d2[0], d2[1]);
+                        }
+                        const uint32_t abuf = last ? M::kDZ : M::kA + (uint32_t)(l + 1) * kTile;
+                        *row_chunk(abuf, c0 / 8) = make_uint4(pa[0], pa[1], pa[2], pa[3]);
+                        *row_chunk(abuf, c0 / 8 + 1) = make_uint4(pa[4], pa[5], pa[6], pa[7]);
+                        if (!last) {
+                            *row_chunk(M::kD + (uint32_t)l * kTile, c0 / 8) = make_uint4(pd[0], pd[1], pd[2], pd[3]);
+                            *row_chunk(M::kD + (uint32_t)l * kTile, c0 / 8 + 1) = make_uint4(pd[4], pd[5], pd[6], pd[7]);
+                        }
+                    }
+                    if (last) {
+                        run_max = fmaxf(run_max, loss);
+                        run_sum += loss;
+                    }
+                    release();
+                }
+            }
+            // ---- backward: dA_l in the accumulator times the stored derivative gives dZ_{l-1}, written over A_l ----
+#pragma unroll
+            for (int l = NL - 1; l >= 1; --l) {
+                wait_full();
+                if (ok) {
+#pragma unroll
+                    for (int c0 = 0; c0 < H; c0 += 16) {
+                        uint32_t v[16];
+                        tmem_ld_32x16(t_acc + (uint32_t)c0, v);
+                        tmem_ld_wait();
+                        const uint4 d0 = *row_chunk(M::kD + (uint32_t)(l - 1) * kTile, c0 / 8);
+                        const uint4 d1 = *row_chunk(M::kD + (uint32_t)(l - 1) * kTile, c0 / 8 + 1);
+                        const uint32_t dd[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+                        uint32_t pz[8];
+#pragma unroll
+                        for (int k = 0; k < 8; ++k)
+                            pz[k] = C::pack2(__uint_as_float(v[2 * k]) * C::lo(dd[k]), __uint_as_float(v[2 * k + 1]) * C::hi(dd[k]));
+                        *row_chunk(M::kA + (uint32_t)l * kTile, c0 / 8) = make_uint4(pz[0], pz[1], pz[2], pz[3]);
+                        *row_chunk(M::kA + (uint32_t)l * kTile, c0 / 8 + 1) = make_uint4(pz[4], pz[5], pz[6], pz[7]);
+                    }
+                    release();
+                }
+            }
+        }
+
+        // ---- one add per parameter per CTA: lane = output feature, column = input feature ----
+        if (ok && n_my_tiles > 0) ok = mbar_wait(tile_done, (n_my_tiles - 1) & 1u, abort_flag, p.status, kStatusEpi);
+        if (ok && !*abort_flag && n_my_tiles > 0) {
+            tc_fence_after();
+            const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
+            for (int l = 0; l < NL; ++l) {
+                const int in = c.dims[l], out = c.dims[l + 1];
+                float* dW = (float*)p.net[l].weightsGrad;
+                float* dB = (float*)p.net[l].biasesGrad;
+                for (int c0 = 0; c0 < H; c0 += 16) {
+                    uint32_t v[16];
+                    tmem_ld_32x16(lane_base + M::kColDW + (uint32_t)l * 64u + (uint32_t)c0, v);
+                    tmem_ld_wait();
+                    if (r < out) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            if (c0 + i < in) atomicAdd(dW + (size_t)r * in + c0 + i, __uint_as_float(v[i]));
+                    }
+                }
+                uint32_t b[16];
+                tmem_ld_32x16(lane_base + M::kColDB + (uint32_t)l * 16u, b);
+                tmem_ld_wait();
+                if (r < out) atomicAdd(dB + r, __uint_as_float(b[0]));
+            }
+            float mx = run_max, sm = run_sum;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+                sm += __shfl_xor_sync(0xffffffffu, sm, o);
+            }
+            if (lane == 0) {
+                atomicMax(p.loss_words, __float_as_uint(mx));
+                atomicAdd((float*)(p.loss_words + 1), sm);
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Map<NL>::kTmemCols);
+    }
+}
+
+}  // namespace narrow
+
+bool tc_train_narrow_supported(const MlpConfig& c)
+{
+    if (c.n_layers < 2 || c.n_layers > 5) return false;
+    if (c.dtype != MLP_BF16 && c.dtype != MLP_F16) return false;
+    for (int l = 0; l <= c.n_layers; ++l)
+        if (c.dims[l] > narrow::H) return false;
+    if (c.encoding == MLP_ENC_FREQ2D && c.dims[0] != 32) return false;
+    return true;
+}
+
+template <int NL, int FMT>
+static cudaError_t launch_narrow(cudaStream_t st, TcWorkspace* ws, const narrow::Params& p)
+{
+    auto kern = narrow::learn_gradient_narrow_kernel<NL, FMT>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)narrow::Map<NL>::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    const uint32_t grid = p.n_tiles < (uint32_t)ws->sm_count ? p.n_tiles : (uint32_t)ws->sm_count;
+    kern<<<grid, narrow::kThreads, narrow::Map<NL>::kSmemBytes, st>>>(p);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_learn_gradient_narrow(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const MlpLearnGradParamsEx& a,
+                                         int* launches, std::string* err)
+{
+    if (!tc_train_narrow_supported(c)) { if (err) *err = "shape not built for the narrow tensor-core path"; return cudaErrorInvalidValue; }
+    if (a.count == 0) return cudaSuccess;
+    narrow::Params p;
+    p.cfg = c;
+    p.net = (const MlpLayerPointers*)a.networkBuffer;
+    p.loss_words = (uint32_t*)a.lossBuffer;
+    p.status = ws->status;
+    p.inputs = (const void*)a.inputs;
+    p.targets = (const void*)a.targets;
+    p.count = a.count;
+    p.n_tiles = (a.count + narrow::TS - 1) / narrow::TS;
+    cudaError_t e = cudaErrorInvalidValue;
+#define MLPB200_NARROW(NL_) \
+    if (c.n_layers == NL_) e = c.dtype == MLP_BF16 ? launch_narrow<NL_, MLP_BF16>(st, ws, p) : launch_narrow<NL_, MLP_F16>(st, ws, p);
+    MLPB200_NARROW(2) MLPB200_NARROW(3) MLPB200_NARROW(4) MLPB200_NARROW(5)
+#undef MLPB200_NARROW
+    *launches += 1;
+    return e;
+}
+
+}  // namespace mlpb200

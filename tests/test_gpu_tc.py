@@ -101,3 +101,32 @@ def test_c4_tensor_core_matches_simt_on_large_batch(device):
         tr_tc.network.address, tr_tc.loss.address, xb.address + half * 128, tb.address + half * 128, half, 0), (half + 255) // 256)
     g_split = tr_tc.read_grads()
     assert _grad_layer_errs(cfg, g_split, g_tc) < 1e-4
+
+
+@pytest.mark.parametrize("name", ["c2", "c3"])
+@pytest.mark.parametrize("count", [1, 127, 129, 1024, 128 * 148 * 2 + 5])
+def test_narrow_networks_on_tensor_cores(device, name, count):
+    """fp16 4-32-32-32-32-4 (LeakyReLU) and enc(2->32)-64-64-64-3 (ReLU, sigmoid output, L2) through the
+    padded 64-wide tensor-core kernel: gradients per tensor within 1e-2, loss words within 1e-2."""
+    cfg, p0, batches = make_problem(name, count, seed=17, steps=1)
+    _, l_ref, g_ref, _ = oracle_trajectory(cfg, p0, batches, n_threads=8)
+    _, l_gpu, g_gpu, _, tr = gpu_trajectory(device, cfg, p0, batches)
+    assert tr.k_learn.implementation == "tcgen05"
+    err = _grad_layer_errs(cfg, g_gpu, g_ref)
+    print("%s count=%d worst per-tensor gradient rel err %.3g; loss gpu %s ref %s" % (name, count, err, l_gpu[0], l_ref[0]))
+    assert err < 1e-2
+    assert abs(l_gpu[0][1] - l_ref[0][1]) <= 1e-2 * abs(l_ref[0][1])
+    assert abs(l_gpu[0][0] - l_ref[0][0]) <= 1e-2 * abs(l_ref[0][0])
+
+
+@pytest.mark.parametrize("name,count,steps", [("c2", 2048, 10), ("c3", 1024, 10)])
+def test_narrow_network_trajectories(device, name, count, steps):
+    cfg, p0, batches = make_problem(name, count, seed=3, steps=steps)
+    p_ref, l_ref, _, _ = oracle_trajectory(cfg, p0, batches)
+    p_gpu, l_gpu, _, _, tr = gpu_trajectory(device, cfg, p0, batches)
+    assert tr.k_learn.implementation == "tcgen05"
+    for (mg, sg), (mr, sr) in zip(l_gpu, l_ref):
+        assert abs(sg - sr) <= 1e-2 * abs(sr)
+    errs = per_layer_rel_errs(cfg, C.from_storage(p_gpu, cfg.dtype), C.from_storage(p_ref, cfg.dtype))
+    print(name, "trajectory: worst per-layer parameter rel err %.3g" % max(errs))
+    assert max(errs) < 2e-2
