@@ -227,6 +227,80 @@ def sweep_forward(args):
     device.destroy()
 
 
+def bench_narrow(args):
+    """Configurations 2 and 3 at their stated sizes on one GPU (resident inputs, CUDA events)."""
+    import torch
+    from slang_b200 import config as C
+    from slang_b200.api import Device, Trainer
+    torch.cuda.set_device(0)
+    dev_t = torch.device("cuda", 0)
+    stream = torch.cuda.Stream(device=dev_t)
+    torch.cuda.set_stream(stream)
+    device = Device(0, stream.cuda_stream)
+    name = args.config
+    cfg = C.named_config(name)
+    count = args.batch if args.batch != (1 << 26) else (1 << 20 if name == "c2" else 1 << 24)
+    gen = torch.Generator(device=dev_t); gen.manual_seed(11)
+    if name == "c2":
+        x = torch.rand((count, 4), device=dev_t, generator=gen)
+        w = torch.from_numpy(C.unit_vectors(1234, 4, 4)).to(dev_t)
+        t = torch.sin(2 * np.pi * (x @ w.t())).contiguous()
+        workload = "fp16 MLP 4-32-32-32-32-4 LeakyReLU(0.01), MSE, Adam lr 1e-3"
+    else:
+        side = int(round(count ** 0.5))
+        assert side * side == count
+        idx = torch.arange(count, device=dev_t)
+        x = torch.stack([((idx % side) + 0.5) / side, ((idx // side) + 0.5) / side], dim=1).float().contiguous()
+        centres, sigma = C.gaussian_blobs(4321)
+        t = torch.zeros((count, 3), device=dev_t)
+        for ch in range(3):
+            for b in range(centres.shape[1]):
+                cx, cy, sg = float(centres[ch, b, 0]), float(centres[ch, b, 1]), float(sigma[ch, b])
+                t[:, ch] += torch.exp(-((x[:, 0] - cx) ** 2 + (x[:, 1] - cy) ** 2) / (2 * sg * sg))
+        t = t.clamp(0, 1).to(torch.float16).contiguous()
+        workload = "fp16 MLP enc(2->32)-64-64-64-3 ReLU, sigmoid out, L2, Adam lr 1e-2, 4096x4096 grid"
+    tr = Trainer(device, cfg, C.init_params(cfg, seed=1, scheme="xavier" if name == "c2" else "kaiming"))
+    impl = tr.k_learn.implementation
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev_t)
+
+    def step():
+        tr.learn_gradient(x.data_ptr(), t.data_ptr(), count)
+        tr.adjust_parameters()
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    times, ktimes = [], []
+    launches0 = device.launch_count
+    for _ in range(args.steps):
+        flush.zero_()
+        e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        e0.record()
+        tr.learn_gradient(x.data_ptr(), t.data_ptr(), count)
+        e1.record()
+        tr.adjust_parameters()
+        e2.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e2)); ktimes.append(e0.elapsed_time(e1))
+    launches = device.launch_count - launches0
+    device.wait()
+    ms, kms = float(np.mean(times)), float(np.mean(ktimes))
+    mx, sm = tr.read_loss()
+    peaks = measured_peaks()
+    flops = C.flops_per_sample(cfg, training=True)
+    achieved = flops * count / (kms * 1e-3) / 1e12
+    line = {"metric": METRIC, "value": count / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": workload, "global_batch": count, "l2": "512 MB written between timed steps"},
+            "gpu_launches": launches, "implementation": impl,
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_burst"], "unit": "TFLOP/s",
+                         "frac": achieved / peaks["bf16_burst"], "traffic": None, "kernel": "learn_gradient_narrow_kernel",
+                         "kernel_ms": kms, "flop_per_sample": flops, "peak_source": peaks["source"] + " (burst; kernel timed alone)"},
+            "loss": {"max": mx, "mean": sm / count}}
+    print(json.dumps(line), flush=True)
+    device.destroy()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -246,6 +320,10 @@ def main():
 
     if args.impl == "reference":
         reference_arm(args, rank)
+        return
+    if args.config in ("c2", "c3"):
+        if rank == 0:
+            bench_narrow(args)
         return
     if args.config == "c5_sweep":
         if rank == 0:

@@ -103,7 +103,9 @@ struct Map {
     static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 };
 
-template <int NL, int FMT>
+// HACT / OACT: the hidden and output activation as compile-time constants, or -1 to read them from
+// the configuration at run time (slower: every element goes through a switch).
+template <int NL, int FMT, int HACT, int OACT>
 __global__ void __launch_bounds__(kThreads, 1) learn_gradient_narrow_kernel(const Params p)
 {
     using M = Map<NL>;
@@ -244,6 +246,8 @@ __global__ void __launch_bounds__(kThreads, 1) learn_gradient_narrow_kernel(cons
         const int r = q * 32 + lane;  // the sample row (TMEM lane) this thread owns
         const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16) + M::kColAcc;
         const int od = c.dims[NL];
+        const int hact = HACT >= 0 ? HACT : c.hidden_act;
+        const int oact = OACT >= 0 ? OACT : c.output_act;
         const float loss_scale = c.loss == MLP_LOSS_MSE_MEAN ? 1.0f / (float)od : 1.0f;
         float run_max = 0.0f, run_sum = 0.0f;
         uint32_t n_full = 0;
@@ -279,8 +283,7 @@ __global__ void __launch_bounds__(kThreads, 1) learn_gradient_narrow_kernel(cons
 #pragma unroll
                             for (int k = 0; k < 8; ++k) {
                                 const float arg = ldexpf(3.14159265358979323846f, k) * v;
-                                x[u * 16 + k * 2 + 0] = sinf(arg);
-                                x[u * 16 + k * 2 + 1] = cosf(arg);
+                                sincosf(arg, &x[u * 16 + k * 2 + 0], &x[u * 16 + k * 2 + 1]);
                             }
                         }
                     } else {
@@ -302,39 +305,49 @@ __global__ void __launch_bounds__(kThreads, 1) learn_gradient_narrow_kernel(cons
                 if (ok) {
                     const bool last = (l == NL - 1);
                     float loss = 0.0f;
+                    const int width = c.dims[l + 1];  // real features of this layer; the padding beyond stays zero
 #pragma unroll
                     for (int c0 = 0; c0 < H; c0 += 16) {
+                        const uint32_t abuf = last ? M::kDZ : M::kA + (uint32_t)(l + 1) * kTile;
+                        if (c0 >= width) {
+                            *row_chunk(abuf, c0 / 8) = make_uint4(0u, 0u, 0u, 0u);
+                            *row_chunk(abuf, c0 / 8 + 1) = make_uint4(0u, 0u, 0u, 0u);
+                            continue;
+                        }
                         uint32_t v[16];
                         tmem_ld_32x16(t_acc + (uint32_t)c0, v);
                         tmem_ld_wait();
                         uint32_t pa[8], pd[8];
 #pragma unroll
-                        for (int k = 0; k < 16; k += 2) {
-                            float a2[2], d2[2];
+                        for (int k = 0; k < 16; k += 4) {
+                            const float4 b4 = *(const float4*)(s_bias + l * H + c0 + k);
+                            const float bb[4] = {b4.x, b4.y, b4.z, b4.w};
+                            float a4[4], d4[4];
 #pragma unroll
-                            for (int e = 0; e < 2; ++e) {
+                            for (int e = 0; e < 4; ++e) {
                                 const int j = c0 + k + e;
-                                const float z = C::round(__uint_as_float(v[k + e]) + s_bias[l * H + j]);
+                                const float z = C::round(__uint_as_float(v[k + e]) + bb[e]);
                                 if (!last) {
-                                    a2[e] = act_value(c.hidden_act, c.act_alpha, z);
-                                    d2[e] = act_deriv(c.hidden_act, c.act_alpha, z);
+                                    a4[e] = act_value(hact, c.act_alpha, z);
+                                    d4[e] = act_deriv(hact, c.act_alpha, z);
                                 } else {
                                     // loss and dZ of the last layer; padded outputs and rows past the batch give zero
                                     float dz = 0.0f;
                                     if (valid && j < od) {
-                                        const float o = act_value(c.output_act, c.act_alpha, z);
+                                        const float o = act_value(oact, c.act_alpha, z);
                                         const float diff = o - load_as_f32(c.target_dtype, p.targets, sample * od + j);
                                         loss = fmaf(diff * loss_scale, diff, loss);
-                                        dz = ((2.0f * loss_scale) * diff) * act_deriv(c.output_act, c.act_alpha, z);
+                                        dz = ((2.0f * loss_scale) * diff) * act_deriv(oact, c.act_alpha, z);
                                     }
-                                    a2[e] = dz;
-                                    d2[e] = 0.0f;
+                                    a4[e] = dz;
+                                    d4[e] = 0.0f;
                                 }
                             }
-                            pa[k >> 1] = C::pack2(a2[0], a2[1]);
-                            pd[k >> 1] = C::pack2(d2[0], d2[1]);
+                            pa[k >> 1] = C::pack2(a4[0], a4[1]);
+                            pa[(k >> 1) + 1] = C::pack2(a4[2], a4[3]);
+                            pd[k >> 1] = C::pack2(d4[0], d4[1]);
+                            pd[(k >> 1) + 1] = C::pack2(d4[2], d4[3]);
                         }
-                        const uint32_t abuf = last ? M::kDZ : M::kA + (uint32_t)(l + 1) * kTile;
                         *row_chunk(abuf, c0 / 8) = make_uint4(pa[0], pa[1], pa[2], pa[3]);
                         *row_chunk(abuf, c0 / 8 + 1) = make_uint4(pa[4], pa[5], pa[6], pa[7]);
                         if (!last) {
@@ -354,8 +367,14 @@ __global__ void __launch_bounds__(kThreads, 1) learn_gradient_narrow_kernel(cons
             for (int l = NL - 1; l >= 1; --l) {
                 wait_full();
                 if (ok) {
+                    const int width = c.dims[l];  // real features of dZ_{l-1}
 #pragma unroll
                     for (int c0 = 0; c0 < H; c0 += 16) {
+                        if (c0 >= width) {
+                            *row_chunk(M::kA + (uint32_t)l * kTile, c0 / 8) = make_uint4(0u, 0u, 0u, 0u);
+                            *row_chunk(M::kA + (uint32_t)l * kTile, c0 / 8 + 1) = make_uint4(0u, 0u, 0u, 0u);
+                            continue;
+                        }
                         uint32_t v[16];
                         tmem_ld_32x16(t_acc + (uint32_t)c0, v);
                         tmem_ld_wait();
@@ -431,10 +450,10 @@ bool tc_train_narrow_supported(const MlpConfig& c)
     return true;
 }
 
-template <int NL, int FMT>
+template <int NL, int FMT, int HACT, int OACT>
 static cudaError_t launch_narrow(cudaStream_t st, TcWorkspace* ws, const narrow::Params& p)
 {
-    auto kern = narrow::learn_gradient_narrow_kernel<NL, FMT>;
+    auto kern = narrow::learn_gradient_narrow_kernel<NL, FMT, HACT, OACT>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)narrow::Map<NL>::kSmemBytes);
     if (e != cudaSuccess) return e;
     const uint32_t grid = p.n_tiles < (uint32_t)ws->sm_count ? p.n_tiles : (uint32_t)ws->sm_count;
@@ -457,10 +476,17 @@ cudaError_t launch_learn_gradient_narrow(cudaStream_t st, TcWorkspace* ws, const
     p.count = a.count;
     p.n_tiles = (a.count + narrow::TS - 1) / narrow::TS;
     cudaError_t e = cudaErrorInvalidValue;
+    // the two benchmark shapes get their activations as compile-time constants
+    if (c.n_layers == 5 && c.dtype == MLP_F16 && c.hidden_act == MLP_ACT_LEAKY_RELU && c.output_act == MLP_ACT_IDENTITY)
+        e = launch_narrow<5, MLP_F16, MLP_ACT_LEAKY_RELU, MLP_ACT_IDENTITY>(st, ws, p);
+    else if (c.n_layers == 4 && c.dtype == MLP_F16 && c.hidden_act == MLP_ACT_RELU && c.output_act == MLP_ACT_SIGMOID)
+        e = launch_narrow<4, MLP_F16, MLP_ACT_RELU, MLP_ACT_SIGMOID>(st, ws, p);
+    else {
 #define MLPB200_NARROW(NL_) \
-    if (c.n_layers == NL_) e = c.dtype == MLP_BF16 ? launch_narrow<NL_, MLP_BF16>(st, ws, p) : launch_narrow<NL_, MLP_F16>(st, ws, p);
-    MLPB200_NARROW(2) MLPB200_NARROW(3) MLPB200_NARROW(4) MLPB200_NARROW(5)
+    if (c.n_layers == NL_) e = c.dtype == MLP_BF16 ? launch_narrow<NL_, MLP_BF16, -1, -1>(st, ws, p) : launch_narrow<NL_, MLP_F16, -1, -1>(st, ws, p);
+        MLPB200_NARROW(2) MLPB200_NARROW(3) MLPB200_NARROW(4) MLPB200_NARROW(5)
 #undef MLPB200_NARROW
+    }
     *launches += 1;
     return e;
 }
