@@ -134,6 +134,27 @@ int32_t mlp_dispatch(MlpDevice* device, MlpKernel* kernel, const void* args, siz
 /* Number of CUDA kernels launched through this device handle since it was created. */
 uint64_t mlp_device_launch_count(const MlpDevice* device);
 
+/* ---- parameter layout conversion --------------------------------------------------------------- */
+
+/* A network as the neural module's NetworkParameterLayoutConverter<T, BiasMask, In, Out, Rest...> sees
+ * it (source/standard-modules/neural/network-parameter-layout-converter.slang:469-478): layer widths
+ * and one bias bit per layer. */
+typedef struct MlpNetworkShape {
+    int32_t n_layers;
+    int32_t dims[MLP_MAX_LAYERS + 1];
+    uint64_t bias_mask;  /* bit l set: layer l has a bias */
+    int32_t elem_bytes;  /* 4 (float) or 2 (half / bfloat16: a pure permutation of 16-bit patterns) */
+    int32_t reserved;
+} MlpNetworkShape;
+
+/* ElementCountLogical / ElementCountPhysical of the converter (:480-483). */
+int32_t mlp_layout_sizes(const MlpNetworkShape* shape, int64_t* logical_elements, int64_t* physical_elements);
+/* toOptimalLayout (:492-520): portable row-major -> 16x16 tiles in tensor-core B-fragment order, padded
+ * with zeros, bias slot reserved for every layer.  Device addresses; stream ordered. */
+int32_t mlp_layout_to_optimal(MlpDevice* device, const MlpNetworkShape* shape, uint64_t portable, uint64_t optimal);
+/* toPortableLayout (:529-554): the inverse. */
+int32_t mlp_layout_to_portable(MlpDevice* device, const MlpNetworkShape* shape, uint64_t optimal, uint64_t portable);
+
 /* ---- learnGradient without any allocation ------------------------------------------------- */
 
 /* No counterpart in the reference.  For hosts that must not touch the CUDA allocator while they

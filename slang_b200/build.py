@@ -25,6 +25,7 @@ COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
 UNITS = [
     ("abi.cu", []),
     ("simt_kernels.cu", ["-fmad=false"]),
+    ("layout_convert.cu", []),
     ("tc_kernels.cu", []),
     ("tc_forward.cu", []),
     ("tc_train_narrow.cu", []),

@@ -55,6 +55,21 @@ class MlpConfig(ctypes.Structure):
         return int(self.dims[self.n_layers])
 
 
+class MlpNetworkShape(ctypes.Structure):
+    """Mirrors struct MlpNetworkShape: layer widths and one bias bit per layer."""
+    _fields_ = [("n_layers", ctypes.c_int32), ("dims", ctypes.c_int32 * (MLP_MAX_LAYERS + 1)),
+                ("bias_mask", ctypes.c_uint64), ("elem_bytes", ctypes.c_int32), ("reserved", ctypes.c_int32)]
+
+
+def network_shape(dims, bias_mask, elem_bytes):
+    s = MlpNetworkShape()
+    s.n_layers = len(dims) - 1
+    for i, d in enumerate(dims):
+        s.dims[i] = d
+    s.bias_mask, s.elem_bytes = bias_mask, elem_bytes
+    return s
+
+
 class MlpAdamState(ctypes.Structure):
     _fields_ = [("mean", ctypes.c_float), ("variance", ctypes.c_float),
                 ("iteration", ctypes.c_int32), ("master", ctypes.c_float)]

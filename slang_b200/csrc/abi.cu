@@ -336,6 +336,42 @@ int32_t mlp_dispatch(MlpDevice* d, MlpKernel* k, const void* args, size_t args_s
     return MLP_OK;
 }
 
+int32_t mlp_layout_sizes(const MlpNetworkShape* shape, int64_t* logical_elements, int64_t* physical_elements)
+{
+    if (!shape || !logical_elements || !physical_elements) return fail(MLP_E_INVALID_ARG, "null argument");
+    std::string err;
+    long long lo = 0, po = 0;
+    if (!layout_sizes(*shape, &lo, &po, &err)) return fail(MLP_E_INVALID_ARG, "bad network shape: %s", err.c_str());
+    *logical_elements = lo;
+    *physical_elements = po;
+    return MLP_OK;
+}
+
+static int32_t layout_convert(MlpDevice* d, const MlpNetworkShape* shape, bool to_optimal, uint64_t src, uint64_t dst)
+{
+    if (!d || !shape || !src || !dst) return fail(MLP_E_INVALID_ARG, "null argument");
+    CUDA_TRY(cudaSetDevice(d->ordinal));
+    std::string err;
+    int launches = 0;
+    cudaError_t e = launch_layout_convert(d->stream, *shape, to_optimal, (const void*)src, (void*)dst, &launches, &err);
+    d->launches += (uint64_t)launches;
+    if (e != cudaSuccess) {
+        if (!err.empty()) return fail(MLP_E_INVALID_ARG, "bad network shape: %s", err.c_str());
+        return fail(MLP_E_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
+    }
+    return MLP_OK;
+}
+
+int32_t mlp_layout_to_optimal(MlpDevice* d, const MlpNetworkShape* shape, uint64_t portable, uint64_t optimal)
+{
+    return layout_convert(d, shape, true, portable, optimal);
+}
+
+int32_t mlp_layout_to_portable(MlpDevice* d, const MlpNetworkShape* shape, uint64_t optimal, uint64_t portable)
+{
+    return layout_convert(d, shape, false, optimal, portable);
+}
+
 // Diagnostics, not part of the public header: cycle counts recorded by CTA 0 of the last
 // tensor-core learnGradient (control thread total / waiting, tiles, epilogue warp total / waiting).
 int32_t mlpb200_debug_tc_timing(MlpDevice* d, unsigned long long* out8)

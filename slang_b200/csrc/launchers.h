@@ -19,6 +19,11 @@ cudaError_t launch_learn_gradient_simt(cudaStream_t st, const MlpConfig& c, cons
 size_t sequential_scratch_floats_per_sample(const MlpConfig& c);
 cudaError_t launch_adjust_parameters(cudaStream_t st, const MlpConfig& c, const MlpAdjustParamsParams& a, int* launches);
 
+// Parameter layout conversion (layout_convert.cu).
+bool layout_sizes(const MlpNetworkShape& n, long long* logical, long long* physical, std::string* err);
+cudaError_t launch_layout_convert(cudaStream_t st, const MlpNetworkShape& n, bool to_optimal, const void* src, void* dst,
+                                  int* launches, std::string* err);
+
 // Tensor-core kernels (tc_kernels.cu).  tc_supported() says whether the shape is one they are built for.
 bool tc_forward_supported(const MlpConfig& c);
 bool tc_train_supported(const MlpConfig& c);

@@ -19,6 +19,7 @@ EXPORTS = [
     "mlp_kernel_get", "mlp_kernel_get_for_config", "mlp_kernel_destroy", "mlp_kernel_implementation",
     "mlp_dispatch", "mlp_device_launch_count", "mlp_param_layout", "mlp_last_error_string",
     "mlp_learn_gradient_ordered_noalloc",
+    "mlp_layout_sizes", "mlp_layout_to_optimal", "mlp_layout_to_portable",
 ]
 
 _lib = None
@@ -62,6 +63,9 @@ def load():
     L.mlp_param_layout.argtypes = [ctypes.POINTER(MlpConfig), ctypes.POINTER(ctypes.c_int64),
                                    ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64)]
     L.mlp_last_error_string.restype = ctypes.c_char_p
+    L.mlp_layout_sizes.argtypes = [vp, ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64)]
+    L.mlp_layout_to_optimal.argtypes = [vp, vp, u64, u64]
+    L.mlp_layout_to_portable.argtypes = [vp, vp, u64, u64]
     L.mlp_learn_gradient_ordered_noalloc.argtypes = [i32, vp, ctypes.POINTER(MlpConfig), vp]
     for name in EXPORTS:
         fn = getattr(L, name)
