@@ -430,12 +430,15 @@ def main():
     # ---- end to end: pinned host inputs, copies inside the timed region ----
     e2e = None
     if not args.no_e2e:
-        stepper = HostStepper(trainer, chunk_samples=min(count, 1 << 21), allreduce=allreduce if world > 1 else None)
+        # The targets are the frozen teacher's outputs: only the inputs cross the host-device link, the
+        # teacher's forward kernel produces each piece's targets on the device inside the timed region.
+        teacher = Trainer(device, cfg, C.init_params(cfg, seed=2, scheme="xavier"))
+        assert teacher.k_forward.implementation == "tcgen05"
+        stepper = HostStepper(trainer, chunk_samples=min(count, 1 << 21), allreduce=allreduce if world > 1 else None, teacher=teacher)
         xh = torch.empty((count, 64), dtype=torch.bfloat16, pin_memory=True)
-        th = torch.empty((count, 64), dtype=torch.bfloat16, pin_memory=True)
-        xh.copy_(xs[0]); th.copy_(ts[0])
+        xh.copy_(xs[0])
         torch.cuda.synchronize()
-        stepper.step(xh, th)  # warm-up
+        stepper.step(xh)  # warm-up
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
@@ -443,7 +446,7 @@ def main():
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(args.e2e_steps):
-            stepper.step(xh, th)
+            stepper.step(xh)
         e1.record()
         torch.cuda.synchronize()
         e2e_ms = e0.elapsed_time(e1)
@@ -455,8 +458,9 @@ def main():
         e2e = {"value": args.batch * args.e2e_steps / (e2e_ms * 1e-3), "unit": UNIT,
                "h2d_bytes_per_step": int(stepper.h2d_bytes) * world, "d2h_bytes_per_step": int(stepper.d2h_bytes) * world,
                "steps": args.e2e_steps, "wall_ms_per_step": wall_ms / args.e2e_steps,
-               "api": "slang_b200.host_step.HostStepper.step (pinned host inputs and targets, chunked copies overlapped with learnGradient)"}
-        del xh, th
+               "api": "slang_b200.host_step.HostStepper.step (pinned host inputs, chunked copies overlapped with the "
+                      "teacher's forward kernel and learnGradient; targets computed on the device)"}
+        del xh
 
     if rank == 0:
         peaks = measured_peaks()

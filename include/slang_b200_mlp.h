@@ -68,7 +68,8 @@ typedef struct MlpLearnGradParamsEx {
     uint32_t flags; /* MLP_FLAG_* */
 } MlpLearnGradParamsEx;
 
-/* forward only: outputs are fp32 [count][dims[n_layers]]. */
+/* forward only: outputs are fp32 [count][dims[n_layers]], or the network's storage type with
+ * MLP_FLAG_OUTPUT_STORAGE_TYPE (for feeding another network's targets). */
 typedef struct MlpForwardParams {
     uint64_t networkBuffer;
     uint64_t inputs;
@@ -80,6 +81,8 @@ typedef struct MlpForwardParams {
 /* Gradient sums in ascending sample order, one add at a time, as the reference's CPU target runs
  * them (source/slang/slang-emit-cpp.cpp:2210-2284): bit-identical to a sequential machine, slow. */
 #define MLP_FLAG_SEQUENTIAL_SUM 1u
+/* forward: write the outputs rounded to the network's storage type (tensor-core path only). */
+#define MLP_FLAG_OUTPUT_STORAGE_TYPE 2u
 
 /* ---- device ------------------------------------------------------------------------------- */
 

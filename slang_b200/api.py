@@ -36,6 +36,7 @@ class ForwardParams(ctypes.Structure):
 
 
 FLAG_SEQUENTIAL_SUM = 1
+FLAG_OUTPUT_STORAGE_TYPE = 2
 
 
 class Buffer:
@@ -180,8 +181,8 @@ class Trainer:
         args = AdjustParamsParams(self.states.address, self.params.address, self.grads.address, self.total)
         self.k_adjust.dispatch(args, groups_for(self.total))
 
-    def forward(self, inputs_address, outputs_address, count):
-        args = ForwardParams(self.network.address, inputs_address, outputs_address, count, 0)
+    def forward(self, inputs_address, outputs_address, count, flags=0):
+        args = ForwardParams(self.network.address, inputs_address, outputs_address, count, flags)
         self.k_forward.dispatch(args, groups_for(count))
 
     def read_loss(self):

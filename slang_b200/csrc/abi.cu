@@ -323,6 +323,8 @@ int32_t mlp_dispatch(MlpDevice* d, MlpKernel* k, const void* args, size_t args_s
         MlpForwardParams a; std::memcpy(&a, args, sizeof a);
         if ((uint64_t)gx * 256 < a.count) return fail(MLP_E_INVALID_ARG, "grid of %u groups does not cover %u samples", gx, a.count);
         if (!a.networkBuffer || (a.count && (!a.inputs || !a.outputs))) return fail(MLP_E_INVALID_ARG, "null device address in the argument struct");
+        if ((a.flags & MLP_FLAG_OUTPUT_STORAGE_TYPE) && k->entry != Entry::Forward)
+            return fail(MLP_E_NOT_AVAILABLE, "MLP_FLAG_OUTPUT_STORAGE_TYPE needs the tensor-core forward kernel");
         if (k->entry == Entry::Forward) e = launch_forward_tc(d->stream, d->tc, k->cfg, a, &launches, &err);
         else e = launch_forward_simt(d->stream, k->cfg, a, &launches, &err);
         break;

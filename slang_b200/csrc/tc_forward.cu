@@ -47,6 +47,7 @@ struct Params {
     uint32_t count;
     uint32_t n_tiles;
     float act_alpha;
+    uint32_t out_storage;  // 1: outputs are written in the network's 16-bit storage type instead of fp32
 };
 
 template <int FMT> struct Cvt;
@@ -269,11 +270,21 @@ forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const Params p)
                             *(uint4*)(abuf + chunk_offset<DH>(128, r, c0 / 8)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
                             *(uint4*)(abuf + chunk_offset<DH>(128, r, c0 / 8 + 1)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
                         } else if (row_index < p.count) {
-                            float* dst = p.out + row_index * (uint64_t)out + c0;
+                            if (p.out_storage) {
+                                uint32_t pk[8];
 #pragma unroll
-                            for (int k = 0; k < 16; k += 4)
-                                *(float4*)(dst + k) = make_float4(act_value(OUT_ACT, p.act_alpha, z[k]), act_value(OUT_ACT, p.act_alpha, z[k + 1]),
-                                                                  act_value(OUT_ACT, p.act_alpha, z[k + 2]), act_value(OUT_ACT, p.act_alpha, z[k + 3]));
+                                for (int k = 0; k < 16; k += 2)
+                                    pk[k >> 1] = C::pack2(act_value(OUT_ACT, p.act_alpha, z[k]), act_value(OUT_ACT, p.act_alpha, z[k + 1]));
+                                uint4* dst = (uint4*)((uint16_t*)p.out + row_index * (uint64_t)out + c0);
+                                dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                                dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                            } else {
+                                float* dst = p.out + row_index * (uint64_t)out + c0;
+#pragma unroll
+                                for (int k = 0; k < 16; k += 4)
+                                    *(float4*)(dst + k) = make_float4(act_value(OUT_ACT, p.act_alpha, z[k]), act_value(OUT_ACT, p.act_alpha, z[k + 1]),
+                                                                      act_value(OUT_ACT, p.act_alpha, z[k + 2]), act_value(OUT_ACT, p.act_alpha, z[k + 3]));
+                            }
                         }
                     }
                     tc_fence_before();
@@ -336,6 +347,7 @@ static cudaError_t launch_fwd(cudaStream_t st, TcWorkspace* ws, const MlpConfig&
     p.count = a.count;
     p.n_tiles = (a.count + 127u) / 128u;
     p.act_alpha = c.act_alpha;
+    p.out_storage = (a.flags & MLP_FLAG_OUTPUT_STORAGE_TYPE) ? 1u : 0u;
     auto kern = fwd::forward_tc_kernel<DIN, DH, DOUT, NL, FMT, ACT, OUT_ACT, NCH>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)G::kSmemBytes);
     if (e != cudaSuccess) return e;

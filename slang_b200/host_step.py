@@ -15,8 +15,13 @@ _TORCH_DTYPE = {C.F32: torch.float32, C.F16: torch.float16, C.BF16: torch.bfloat
 
 
 class HostStepper:
-    def __init__(self, trainer, chunk_samples=1 << 21, allreduce=None):
+    """trainer: the network being trained.  teacher: optional Trainer of a frozen network whose
+    outputs are the targets; when given, only the inputs cross the host-device link and the targets
+    are computed on the device, piece by piece, with the teacher's forward kernel."""
+
+    def __init__(self, trainer, chunk_samples=1 << 21, allreduce=None, teacher=None):
         self.tr = trainer
+        self.teacher = teacher
         cfg = trainer.cfg
         self.chunk = chunk_samples
         self.allreduce = allreduce
@@ -29,11 +34,15 @@ class HostStepper:
         self.h2d_bytes = 0
         self.d2h_bytes = 0
 
-    def step(self, x_host, t_host):
-        """x_host, t_host: pinned CPU tensors [count, width].  Returns (max loss, mean loss) of this rank's samples."""
+    def step(self, x_host, t_host=None):
+        """x_host, t_host: pinned CPU tensors [count, width] (t_host is None with a teacher).
+        Returns (max loss, mean loss) of this rank's samples."""
+        from .api import FLAG_OUTPUT_STORAGE_TYPE
         count = x_host.shape[0]
         compute = torch.cuda.current_stream()
-        self.h2d_bytes = x_host.numel() * x_host.element_size() + t_host.numel() * t_host.element_size()
+        self.h2d_bytes = x_host.numel() * x_host.element_size()
+        if self.teacher is None:
+            self.h2d_bytes += t_host.numel() * t_host.element_size()
         n_chunks = (count + self.chunk - 1) // self.chunk
         for i in range(n_chunks):
             b = i & 1
@@ -43,9 +52,12 @@ class HostStepper:
                 self.copy_stream.wait_event(self.compute_done[b])
             with torch.cuda.stream(self.copy_stream):
                 self.x_dev[b][:n].copy_(x_host[i0:i1], non_blocking=True)
-                self.t_dev[b][:n].copy_(t_host[i0:i1], non_blocking=True)
+                if self.teacher is None:
+                    self.t_dev[b][:n].copy_(t_host[i0:i1], non_blocking=True)
                 self.copy_done[b].record(self.copy_stream)
             compute.wait_event(self.copy_done[b])
+            if self.teacher is not None:
+                self.teacher.forward(self.x_dev[b].data_ptr(), self.t_dev[b].data_ptr(), n, FLAG_OUTPUT_STORAGE_TYPE)
             self.tr.learn_gradient(self.x_dev[b].data_ptr(), self.t_dev[b].data_ptr(), n, clear_loss=(i == 0))
             self.compute_done[b].record(compute)
         if self.allreduce is not None:

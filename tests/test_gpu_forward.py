@@ -73,3 +73,22 @@ def test_wide_network_forward(device, count):
     err = float(np.max(np.abs(out - ref))) / scale
     print("wide forward count %d: max err / max|out| = %.3g" % (count, err))
     assert err < 1e-2
+
+
+def test_forward_output_in_storage_type(device):
+    """MLP_FLAG_OUTPUT_STORAGE_TYPE: the same outputs rounded to bf16, as another network's targets."""
+    from slang_b200.api import FLAG_OUTPUT_STORAGE_TYPE, Trainer
+    cfg = C.named_config("c4")
+    params = C.init_params(cfg, seed=5, scheme="xavier")
+    count = 777
+    x = C.to_storage(np.random.default_rng(2).normal(size=(count, 64)).astype(np.float32), C.BF16)
+    tr = Trainer(device, cfg, params)
+    xb = device.create_buffer(x.nbytes, x)
+    o32 = device.create_buffer(count * 64 * 4)
+    o16 = device.create_buffer(count * 64 * 2)
+    tr.forward(xb.address, o32.address, count)
+    tr.forward(xb.address, o16.address, count, FLAG_OUTPUT_STORAGE_TYPE)
+    device.wait()
+    a = o32.read(np.float32)
+    b = o16.read(np.uint16)
+    assert np.array_equal(C.f32_to_bf16_bits(a), b)
