@@ -240,6 +240,16 @@ void encode_input(const MlpConfig& c, const void* inputs, int64_t s, float* a0)
     }
 }
 
+// The parameters widened to float once per call (exact: every storage type embeds in float), so
+// that the inner loops do not convert on every multiply.
+struct FloatParams {
+    std::vector<float> v;
+    FloatParams(const MlpConfig& c, const Layout& L, const void* params) : v(size_t(L.total))
+    {
+        for (int64_t i = 0; i < L.total; ++i) v[size_t(i)] = load_as_f32(c.dtype, params, i);
+    }
+};
+
 struct Scratch {
     std::vector<float> a[MLP_MAX_LAYERS + 1];  // a[l]: vector entering layer l (storage-rounded)
     std::vector<float> z[MLP_MAX_LAYERS];      // z[l]: pre-activation of layer l (storage-rounded)
@@ -256,7 +266,7 @@ struct Scratch {
 // Forward pass of one sample.  On return sc.a[n_layers] holds the network output in fp32
 // (output activation applied, not rounded to the storage type).
 template <typename Acc>
-void forward_sample(const MlpConfig& c, const Layout& L, const void* params, const void* inputs, int64_t s,
+void forward_sample(const MlpConfig& c, const Layout& L, const float* params, const void* inputs, int64_t s,
                     Scratch& sc, int acc_mode)
 {
     encode_input(c, inputs, s, sc.a[0].data());
@@ -264,19 +274,20 @@ void forward_sample(const MlpConfig& c, const Layout& L, const void* params, con
         const int in = c.dims[l], out = c.dims[l + 1];
         const bool last = (l == c.n_layers - 1);
         for (int j = 0; j < out; ++j) {
-            float bias = load_as_f32(c.dtype, params, L.b[l] + j);
+            float bias = params[L.b[l] + j];
+            const float* wrow = params + L.w[l] + int64_t(j) * in;
+            const float* ain = sc.a[l].data();
             float zf;
             if (acc_mode == 2) {
                 float r = bias;
                 for (int i = 0; i < in; ++i) {
-                    float prod = round_to(c.dtype, load_as_f32(c.dtype, params, L.w[l] + int64_t(j) * in + i) * sc.a[l][i]);
+                    float prod = round_to(c.dtype, wrow[i] * ain[i]);
                     r = round_to(c.dtype, r + prod);
                 }
                 zf = r;
             } else {
                 Acc r = Acc(bias);
-                for (int i = 0; i < in; ++i)
-                    r = AccOps<Acc>::mac(r, load_as_f32(c.dtype, params, L.w[l] + int64_t(j) * in + i), sc.a[l][i]);
+                for (int i = 0; i < in; ++i) r = AccOps<Acc>::mac(r, wrow[i], ain[i]);
                 zf = float(r);
             }
             float zs = round_to(c.dtype, zf);
@@ -288,7 +299,7 @@ void forward_sample(const MlpConfig& c, const Layout& L, const void* params, con
 }
 
 template <typename Acc>
-float learn_sample(const MlpConfig& c, const Layout& L, const void* params, float* grads, const void* inputs,
+float learn_sample(const MlpConfig& c, const Layout& L, const float* params, float* grads, const void* inputs,
                    const void* targets, int64_t s, Scratch& sc, int acc_mode)
 {
     forward_sample<Acc>(c, L, params, inputs, s, sc, acc_mode);
@@ -321,14 +332,14 @@ float learn_sample(const MlpConfig& c, const Layout& L, const void* params, floa
             if (acc_mode == 2) {
                 float r = 0.0f;
                 for (int j = 0; j < out; ++j) {
-                    float prod = round_to(c.dtype, load_as_f32(c.dtype, params, L.w[l] + int64_t(j) * in + i) * sc.dz[j]);
+                    float prod = round_to(c.dtype, params[L.w[l] + int64_t(j) * in + i] * sc.dz[j]);
                     r = round_to(c.dtype, r + prod);
                 }
                 v = r;
             } else {
                 Acc r = Acc(0);
-                for (int j = 0; j < out; ++j)
-                    r = AccOps<Acc>::mac(r, load_as_f32(c.dtype, params, L.w[l] + int64_t(j) * in + i), sc.dz[j]);
+                const float* wcol = params + L.w[l] + i;
+                for (int j = 0; j < out; ++j) r = AccOps<Acc>::mac(r, wcol[int64_t(j) * in], sc.dz[j]);
                 v = float(r);
             }
             float d = round_to(c.dtype, act_deriv(c.hidden_act, c.act_alpha, sc.z[l - 1][i]));
@@ -340,7 +351,7 @@ float learn_sample(const MlpConfig& c, const Layout& L, const void* params, floa
 }
 
 template <typename Acc>
-void learn_range(const MlpConfig& c, const Layout& L, const void* params, float* grads, const void* inputs,
+void learn_range(const MlpConfig& c, const Layout& L, const float* params, float* grads, const void* inputs,
                  const void* targets, int64_t s0, int64_t s1, int acc_mode, float* max_loss, double* sum_loss)
 {
     Scratch sc(c);
@@ -389,10 +400,11 @@ int mlp_oracle_forward(const MlpConfig* c, const void* params, const void* input
     if (!config_ok(c)) return -1;
     Layout L = make_layout(*c);
     Scratch sc(*c);
+    FloatParams fp(*c, L, params);
     const int od = c->dims[c->n_layers];
     for (int64_t s = 0; s < count; ++s) {
-        if (acc_mode == 1) forward_sample<double>(*c, L, params, inputs, s, sc, acc_mode);
-        else forward_sample<float>(*c, L, params, inputs, s, sc, acc_mode);
+        if (acc_mode == 1) forward_sample<double>(*c, L, fp.v.data(), inputs, s, sc, acc_mode);
+        else forward_sample<float>(*c, L, fp.v.data(), inputs, s, sc, acc_mode);
         std::memcpy(out + s * od, sc.a[c->n_layers].data(), sizeof(float) * od);
     }
     return 0;
@@ -409,11 +421,13 @@ int mlp_oracle_learn_gradient(const MlpConfig* c, const void* params, float* gra
 {
     if (!config_ok(c)) return -1;
     Layout L = make_layout(*c);
+    FloatParams fpar(*c, L, params);
+    const float* pf = fpar.v.data();
     float mx = 0.0f;
     double sum = 0.0;
     if (n_threads <= 1) {
-        if (acc_mode == 1) learn_range<double>(*c, L, params, grads, inputs, targets, 0, count, acc_mode, &mx, &sum);
-        else learn_range<float>(*c, L, params, grads, inputs, targets, 0, count, acc_mode, &mx, &sum);
+        if (acc_mode == 1) learn_range<double>(*c, L, pf, grads, inputs, targets, 0, count, acc_mode, &mx, &sum);
+        else learn_range<float>(*c, L, pf, grads, inputs, targets, 0, count, acc_mode, &mx, &sum);
     } else {
         std::vector<std::vector<float>> priv(n_threads, std::vector<float>(size_t(L.total), 0.0f));
         std::vector<float> mxs(n_threads, 0.0f);
@@ -423,9 +437,9 @@ int mlp_oracle_learn_gradient(const MlpConfig* c, const void* params, float* gra
             int64_t s0 = count * t / n_threads, s1 = count * (t + 1) / n_threads;
             th.emplace_back([&, t, s0, s1]() {
                 if (acc_mode == 1)
-                    learn_range<double>(*c, L, params, priv[t].data(), inputs, targets, s0, s1, acc_mode, &mxs[t], &sums[t]);
+                    learn_range<double>(*c, L, pf, priv[t].data(), inputs, targets, s0, s1, acc_mode, &mxs[t], &sums[t]);
                 else
-                    learn_range<float>(*c, L, params, priv[t].data(), inputs, targets, s0, s1, acc_mode, &mxs[t], &sums[t]);
+                    learn_range<float>(*c, L, pf, priv[t].data(), inputs, targets, s0, s1, acc_mode, &mxs[t], &sums[t]);
             });
         }
         for (auto& t : th) t.join();

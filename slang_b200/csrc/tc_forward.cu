@@ -52,6 +52,15 @@ struct Params {
 
 template <int FMT> struct Cvt;
 template <> struct Cvt<MLP_BF16> {
+    __device__ static __forceinline__ float lo(uint32_t p) { return __uint_as_float(p << 16); }
+    __device__ static __forceinline__ float hi(uint32_t p) { return __uint_as_float(p & 0xffff0000u); }
+    // max(x, 0) on both halves of a packed pair (exact: rounding is monotonic and zero is representable)
+    __device__ static __forceinline__ uint32_t relu2(uint32_t p)
+    {
+        __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&p);
+        v = __hmax2(v, __float2bfloat162_rn(0.0f));
+        return *reinterpret_cast<uint32_t*>(&v);
+    }
     __device__ static __forceinline__ float round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
     __device__ static __forceinline__ uint32_t pack2(float lo, float hi)
     {
@@ -60,6 +69,14 @@ template <> struct Cvt<MLP_BF16> {
     }
 };
 template <> struct Cvt<MLP_F16> {
+    __device__ static __forceinline__ float lo(uint32_t p) { return __half2float(__ushort_as_half((uint16_t)(p & 0xffffu))); }
+    __device__ static __forceinline__ float hi(uint32_t p) { return __half2float(__ushort_as_half((uint16_t)(p >> 16))); }
+    __device__ static __forceinline__ uint32_t relu2(uint32_t p)
+    {
+        __half2 v = *reinterpret_cast<__half2*>(&p);
+        v = __hmax2(v, __float2half2_rn(0.0f));
+        return *reinterpret_cast<uint32_t*>(&v);
+    }
     __device__ static __forceinline__ float round(float v) { return __half2float(__float2half_rn(v)); }
     __device__ static __forceinline__ uint32_t pack2(float lo, float hi)
     {
@@ -252,20 +269,26 @@ forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const Params p)
                         uint32_t v[16];
                         tmem_ld_32x16(t_acc + (uint32_t)c0, v);
                         tmem_ld_wait();
-                        float z[16];
+                        // bias (packed fp32 adds) and rounding to the storage type, two values per register
+                        uint32_t zp[8];
 #pragma unroll
                         for (int k = 0; k < 16; k += 4) {
                             const float4 b4 = *(const float4*)(bl + c0 + k);
-                            z[k + 0] = C::round(__uint_as_float(v[k + 0]) + b4.x);
-                            z[k + 1] = C::round(__uint_as_float(v[k + 1]) + b4.y);
-                            z[k + 2] = C::round(__uint_as_float(v[k + 2]) + b4.z);
-                            z[k + 3] = C::round(__uint_as_float(v[k + 3]) + b4.w);
+                            const float2 s0 = __fadd2_rn(make_float2(__uint_as_float(v[k]), __uint_as_float(v[k + 1])), make_float2(b4.x, b4.y));
+                            const float2 s1 = __fadd2_rn(make_float2(__uint_as_float(v[k + 2]), __uint_as_float(v[k + 3])), make_float2(b4.z, b4.w));
+                            zp[k >> 1] = C::pack2(s0.x, s0.y);
+                            zp[(k >> 1) + 1] = C::pack2(s1.x, s1.y);
                         }
                         if (!last) {
                             uint32_t pk[8];
+                            if constexpr (ACT == MLP_ACT_RELU) {
 #pragma unroll
-                            for (int k = 0; k < 16; k += 2)
-                                pk[k >> 1] = C::pack2(act_value(ACT, p.act_alpha, z[k]), act_value(ACT, p.act_alpha, z[k + 1]));
+                                for (int k = 0; k < 8; ++k) pk[k] = C::relu2(zp[k]);
+                            } else {
+#pragma unroll
+                                for (int k = 0; k < 8; ++k)
+                                    pk[k] = C::pack2(act_value(ACT, p.act_alpha, C::lo(zp[k])), act_value(ACT, p.act_alpha, C::hi(zp[k])));
+                            }
                             // the next layer reads this buffer as a [128][DH] operand
                             *(uint4*)(abuf + chunk_offset<DH>(128, r, c0 / 8)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
                             *(uint4*)(abuf + chunk_offset<DH>(128, r, c0 / 8 + 1)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
@@ -273,17 +296,18 @@ forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const Params p)
                             if (p.out_storage) {
                                 uint32_t pk[8];
 #pragma unroll
-                                for (int k = 0; k < 16; k += 2)
-                                    pk[k >> 1] = C::pack2(act_value(OUT_ACT, p.act_alpha, z[k]), act_value(OUT_ACT, p.act_alpha, z[k + 1]));
+                                for (int k = 0; k < 8; ++k)
+                                    pk[k] = (OUT_ACT == MLP_ACT_IDENTITY) ? zp[k]
+                                            : C::pack2(act_value(OUT_ACT, p.act_alpha, C::lo(zp[k])), act_value(OUT_ACT, p.act_alpha, C::hi(zp[k])));
                                 uint4* dst = (uint4*)((uint16_t*)p.out + row_index * (uint64_t)out + c0);
                                 dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
                                 dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
                             } else {
                                 float* dst = p.out + row_index * (uint64_t)out + c0;
 #pragma unroll
-                                for (int k = 0; k < 16; k += 4)
-                                    *(float4*)(dst + k) = make_float4(act_value(OUT_ACT, p.act_alpha, z[k]), act_value(OUT_ACT, p.act_alpha, z[k + 1]),
-                                                                      act_value(OUT_ACT, p.act_alpha, z[k + 2]), act_value(OUT_ACT, p.act_alpha, z[k + 3]));
+                                for (int k = 0; k < 8; k += 2)
+                                    *(float4*)(dst + 2 * k) = make_float4(act_value(OUT_ACT, p.act_alpha, C::lo(zp[k])), act_value(OUT_ACT, p.act_alpha, C::hi(zp[k])),
+                                                                          act_value(OUT_ACT, p.act_alpha, C::lo(zp[k + 1])), act_value(OUT_ACT, p.act_alpha, C::hi(zp[k + 1])));
                             }
                         }
                     }
