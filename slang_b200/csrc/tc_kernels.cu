@@ -40,6 +40,12 @@ enum : uint32_t {
     kStatusCtrlAcc = 1u, kStatusCtrlX = 2u, kStatusEpiAcc = 4u, kStatusEpiTarget = 8u, kStatusEpiLoss = 16u,
 };
 
+#ifdef MLPB200_SPIN
+#define MLPB200_CTRL_WAIT mbar_wait_spin
+#else
+#define MLPB200_CTRL_WAIT mbar_wait
+#endif
+
 namespace wide {
 constexpr int NS = 64;            // samples per tile
 #ifndef MLPB200_CH
@@ -257,7 +263,7 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
             // the waiter has seen all earlier phases complete.
             auto chain_wait = [&](int h) {
                 const long long t0 = clock64();
-                if (step > 0) ok = ok && mbar_wait(&acc_free[h], (step - 1) & 1u, abort_flag, p.status, kStatusCtrlAcc);
+                if (step > 0) ok = ok && MLPB200_CTRL_WAIT(&acc_free[h], (step - 1) & 1u, abort_flag, p.status, kStatusCtrlAcc);
                 tc_fence_after();
                 t_wait += clock64() - t0;
             };

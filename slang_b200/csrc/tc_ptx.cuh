@@ -44,6 +44,33 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
     return ok != 0;
 }
 
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded spinning wait without the hardware's suspended polling: lower wake-up latency, for a
+// single control warp whose reaction time is on the critical path.
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                               uint32_t* status, uint32_t code)
+{
+    for (uint32_t i = 0; i < 8u * kMaxPolls; ++i) {
+        if (mbar_test_wait(bar, parity)) return true;
+        if ((i & 255u) == 255u && *abort_flag) return false;
+    }
+    *abort_flag = 1u;
+    atomicOr(status, code);
+    return false;
+}
+
 // Bounded wait.  Returns false when the CTA is aborting (this waiter timed out, or another did).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           uint32_t* status, uint32_t code)
