@@ -130,3 +130,42 @@ def test_narrow_network_trajectories(device, name, count, steps):
     errs = per_layer_rel_errs(cfg, C.from_storage(p_gpu, cfg.dtype), C.from_storage(p_ref, cfg.dtype))
     print(name, "trajectory: worst per-layer parameter rel err %.3g" % max(errs))
     assert max(errs) < 2e-2
+
+
+def test_c4_large_batch_properties(device):
+    """2^22 samples (one sixteenth of the benchmark batch; the kernel walks 443 tiles per CTA):
+    size-independent properties instead of an oracle run.  (1) Additivity: the gradient of the batch
+    equals the sum of the gradients of its four quarters, and so does the loss sum.  (2) A zero
+    residual gives a zero gradient: when the targets are the network's own outputs (rounded to bf16 by
+    the forward kernel), every output difference is at most one rounding step of the output layer."""
+    import torch
+    from slang_b200.api import FLAG_OUTPUT_STORAGE_TYPE
+    from slang_b200.torch_api import TorchTrainer
+    count = 1 << 22
+    cfg = C.named_config("c4")
+    p0 = C.init_params(cfg, seed=33, scheme="xavier")
+    gen = torch.Generator(device="cuda"); gen.manual_seed(5)
+    x = torch.randn((count, 64), device="cuda", generator=gen).to(torch.bfloat16)
+    t = (torch.randn((count, 64), device="cuda", generator=gen) * 0.3).to(torch.bfloat16)
+    tt = TorchTrainer(cfg, p0)
+    tt.learn_gradient(x, t)
+    whole = tt.grads.clone()
+    loss_whole = tt.loss()
+    tt.grads.zero_()
+    q = count // 4
+    sums, mx = 0.0, 0.0
+    for i in range(4):
+        tt.learn_gradient(x[i * q:(i + 1) * q], t[i * q:(i + 1) * q])
+        l = tt.loss()
+        sums += l[1]; mx = max(mx, l[0])
+    parts = tt.grads.clone()
+    scale = whole.abs().max().item()
+    assert (parts - whole).abs().max().item() <= 1e-4 * scale
+    assert abs(sums - loss_whole[1]) <= 1e-4 * abs(loss_whole[1]) and mx == loss_whole[0]
+    # zero residual
+    own = torch.empty((count, 64), dtype=torch.bfloat16, device="cuda")
+    tt.trainer.forward(x.data_ptr(), own.data_ptr(), count, FLAG_OUTPUT_STORAGE_TYPE)
+    tt.grads.zero_()
+    tt.learn_gradient(x, own)
+    assert tt.grads.abs().max().item() <= 2e-3 * scale
+    assert tt.loss()[0] < 1e-4
