@@ -303,13 +303,10 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                     if (h == 0) ok = ok && mbar_wait(&x_full[b], (it >> 1) & 1u, abort_flag, p.status, kStatusCtrlX);
                     if (ok) {
                         const uint32_t acc = tmem_base + kColAcc + (uint32_t)(h * CH);
-                        if (leader) {
 #pragma unroll
-                            for (int k = 0; k < D0 / 16; ++k)
-                                umma_f16(acc, desc_k(kW0, 16384u, k), desc_k(xbuf + (uint32_t)h * (uint32_t)(CH * 128), 8192u, k), kIdescFwd, k > 0);
-                            umma_commit(&acc_full[h]);
-                        }
-                        __syncwarp();
+                        for (int k = 0; k < D0 / 16; ++k)
+                            umma_f16_warp(acc, desc_k(kW0, 16384u, k), desc_k(xbuf + (uint32_t)h * (uint32_t)(CH * 128), 8192u, k), kIdescFwd, k > 0);
+                        umma_commit_warp(&acc_full[h]);
                     }
                 }
                 ++step;
@@ -323,13 +320,10 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                         chain_wait(h);
                         if (ok) {
                             const uint32_t acc = tmem_base + kColAcc + (uint32_t)(h * CH);
-                            if (leader) {
 #pragma unroll
-                                for (int k = 0; k < H / 16; ++k)
-                                    umma_f16(acc, desc_k(w_off(l), wpanel, k), desc_k(abuf + (uint32_t)h * (uint32_t)(CH * 128), 8192u, k), kIdescFwd, k > 0);
-                                umma_commit(&acc_full[h]);
-                            }
-                            __syncwarp();
+                            for (int k = 0; k < H / 16; ++k)
+                                umma_f16_warp(acc, desc_k(w_off(l), wpanel, k), desc_k(abuf + (uint32_t)h * (uint32_t)(CH * 128), 8192u, k), kIdescFwd, k > 0);
+                            umma_commit_warp(&acc_full[h]);
                         }
                     }
                     ++step;
@@ -347,24 +341,23 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                             const uint32_t acc = tmem_base + kColAcc + (uint32_t)(h * CH);
                             const uint32_t row = (uint32_t)h * (uint32_t)(CH * 128);  // 32 rows of 128 bytes
                             const uint32_t prior = (it > 0 || h > 0) ? 1u : 0u;  // the launch's first product overwrites
-                            if (leader) {
+                            {
 #pragma unroll
                                 for (int k = 0; k < out_dim(l) / 16; ++k)
-                                    umma_f16(acc, desc_mn(w_off(l), wpanel, k), desc_k(dzbuf + row, 8192u, k), kIdescDx, k > 0);
+                                    umma_f16_warp(acc, desc_mn(w_off(l), wpanel, k), desc_k(dzbuf + row, 8192u, k), kIdescDx, k > 0);
                                 if (l == NL - 1) {
 #pragma unroll
                                     for (int k = 0; k < CH / 16; ++k)
-                                        umma_f16(tmem_base + kColDW4T, desc_mn(abuf + row, 8192u, k), desc_mn(dzbuf + row, 8192u, k),
+                                        umma_f16_warp(tmem_base + kColDW4T, desc_mn(abuf + row, 8192u, k), desc_mn(dzbuf + row, 8192u, k),
                                                  kIdescDw64, prior | (uint32_t)(k > 0));
                                 } else {
 #pragma unroll
                                     for (int k = 0; k < CH / 16; ++k)
-                                        umma_f16(tmem_base + kColDW1 + (uint32_t)(l - 1) * 128u, desc_mn(dzbuf + row, 8192u, k),
+                                        umma_f16_warp(tmem_base + kColDW1 + (uint32_t)(l - 1) * 128u, desc_mn(dzbuf + row, 8192u, k),
                                                  desc_mn(abuf + row, 8192u, k), kIdescDw, prior | (uint32_t)(k > 0));
                                 }
-                                umma_commit(&acc_full[h]);
+                                umma_commit_warp(&acc_full[h]);
                             }
-                            __syncwarp();
                         }
                     }
                     ++step;
@@ -374,12 +367,12 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
 #pragma unroll
                 for (int h = 0; h < NCH; ++h) chain_wait(h);
                 if (ok) {
+#pragma unroll
+                    for (int k = 0; k < NS / 16; ++k)
+                        umma_f16_warp(tmem_base + kColAcc, desc_mn(kA1, 8192u, k), desc_mn(xbuf, 8192u, k), kIdescDw64, k > 0);
+#pragma unroll
+                    for (int h = 0; h < NCH; ++h) umma_commit_warp(&acc_full[h]);
                     if (leader) {
-#pragma unroll
-                        for (int k = 0; k < NS / 16; ++k)
-                            umma_f16(tmem_base + kColAcc, desc_mn(kA1, 8192u, k), desc_mn(xbuf, 8192u, k), kIdescDw64, k > 0);
-#pragma unroll
-                        for (int h = 0; h < NCH; ++h) umma_commit(&acc_full[h]);
                         if (has_next) {
                             // Both chains are past every product that read the other X buffer and dZ_4.
                             mbar_expect_tx(&x_full[b ^ 1u], 8192);
