@@ -101,16 +101,20 @@ struct Geometry {
     }
     static constexpr uint32_t kActBytes = (uint32_t)(128 * imax(DIN, DH) * 2 + 1023) & ~1023u;
     static constexpr uint32_t kAct = w_off(NL);
-    static constexpr uint32_t kBias = kAct + NCH * kActBytes;     // fp32 [NL][128]
-    static constexpr uint32_t kBars = kBias + NL * 128 * 4;       // x_full[NCH], acc_full[NCH], acc_free[NCH]
-    static constexpr uint32_t kTmemPtr = kBars + 3 * NCH * 8;
+    // fp32 output staging per chain: slabs of [128 rows][kSlabCols floats] in the layout of a swizzled TMA store
+    static constexpr int kSlabCols = DOUT < 32 ? DOUT : (DH >= 128 ? 16 : 32);  // narrower slabs where the weights fill shared memory
+    static constexpr uint32_t kStageBytes = 128u * kSlabCols * 4u;
+    static constexpr uint32_t kStage = kAct + NCH * kActBytes;
+    static constexpr uint32_t kBias = kStage + NCH * kStageBytes;  // fp32 [NL][128]
+    static constexpr uint32_t kBars = kBias + NL * 128 * 4;        // x_full, acc_full, acc_free, stg_full, stg_free (NCH each)
+    static constexpr uint32_t kTmemPtr = kBars + 5 * NCH * 8;
     static constexpr uint32_t kAbort = kTmemPtr + 4;
     static constexpr uint32_t kSmemBytes = kAbort + 4 + 1024;
 };
 
 template <int DIN, int DH, int DOUT, int NL, int FMT, int ACT, int OUT_ACT, int NCH>
 __global__ void __launch_bounds__(64 + 128 * NCH, 1)
-forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const Params p)
+forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_out, const Params p)
 {
     using G = Geometry<DIN, DH, DOUT, NL, NCH>;
     using C = Cvt<FMT>;
@@ -120,6 +124,8 @@ forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const Params p)
     uint64_t* x_full = (uint64_t*)(smem + G::kBars);
     uint64_t* acc_full = x_full + NCH;
     uint64_t* acc_free = acc_full + NCH;
+    uint64_t* stg_full = acc_free + NCH;   // the chain's four warps have written the output slab
+    uint64_t* stg_free = stg_full + NCH;   // the slab's TMA store has finished reading shared memory
     uint32_t* tmem_ptr = (uint32_t*)(smem + G::kTmemPtr);
     volatile uint32_t* abort_flag = (volatile uint32_t*)(smem + G::kAbort);
     float* s_bias = (float*)(smem + G::kBias);
@@ -133,10 +139,13 @@ forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const Params p)
             mbar_init(&x_full[c], 1);
             mbar_init(&acc_full[c], 1);
             mbar_init(&acc_free[c], 4);
+            mbar_init(&stg_full[c], 4);
+            mbar_init(&stg_free[c], 1);
         }
         *abort_flag = 0u;
         fence_mbar_init();
         prefetch_tmap(&tmap_x);
+        prefetch_tmap(&tmap_out);
     }
     if (warp == 1) {
         tmem_alloc(tmem_ptr, G::kTmemCols);
@@ -242,7 +251,8 @@ forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const Params p)
         const int r = q * 32 + lane;     // the sample row this thread owns
         const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * G::kAccCols);
         uint8_t* abuf = smem + G::kAct + c * G::kActBytes;
-        uint32_t step = 0;
+        uint8_t* stage = smem + G::kStage + c * G::kStageBytes;
+        uint32_t step = 0, slabs = 0;  // slabs: output slabs this chain has handed to TMA stores so far
         bool ok = true;
         for (uint32_t i = (uint32_t)c; i < n_my_tiles && ok; i += NCH) {
             const uint32_t tile = blockIdx.x + i * gridDim.x;
@@ -292,8 +302,9 @@ forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const Params p)
                             // the next layer reads this buffer as a [128][DH] operand
                             *(uint4*)(abuf + chunk_offset<DH>(128, r, c0 / 8)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
                             *(uint4*)(abuf + chunk_offset<DH>(128, r, c0 / 8 + 1)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-                        } else if (row_index < p.count) {
+                        } else {
                             if (p.out_storage) {
+                              if (row_index < p.count) {
                                 uint32_t pk[8];
 #pragma unroll
                                 for (int k = 0; k < 8; ++k)
@@ -302,12 +313,40 @@ forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const Params p)
                                 uint4* dst = (uint4*)((uint16_t*)p.out + row_index * (uint64_t)out + c0);
                                 dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
                                 dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                              }
                             } else {
-                                float* dst = p.out + row_index * (uint64_t)out + c0;
+                                // fp32 outputs go through a staging slab and a TMA store: every 128-byte line
+                                // of the output is written once, whole (rows past the batch are clipped by the copy)
+                                constexpr int SC = G::kSlabCols;          // columns per slab
+                                constexpr int CPR = SC / 4;               // 16-byte chunks per slab row
+                                const int cs = c0 % SC;                   // first column of this 16-column piece inside the slab
+                                if (cs == 0) {
+                                    if (slabs > 0) ok = ok && mbar_wait(&stg_free[c], (slabs - 1) & 1u, abort_flag, p.status, kStatusEpiAcc);
+                                }
 #pragma unroll
-                                for (int k = 0; k < 8; k += 2)
-                                    *(float4*)(dst + 2 * k) = make_float4(act_value(OUT_ACT, p.act_alpha, C::lo(zp[k])), act_value(OUT_ACT, p.act_alpha, C::hi(zp[k])),
-                                                                          act_value(OUT_ACT, p.act_alpha, C::lo(zp[k + 1])), act_value(OUT_ACT, p.act_alpha, C::hi(zp[k + 1])));
+                                for (int k = 0; k < 8; k += 2) {
+                                    const int chunk = (cs + 2 * k) / 4;
+                                    const int sw = SC == 32 ? (r & 7) : SC == 16 ? ((r >> 1) & 3) : 0;
+                                    *(float4*)(stage + (uint32_t)r * (SC * 4) + (uint32_t)(((chunk ^ sw) % CPR) << 4)) =
+                                        make_float4(act_value(OUT_ACT, p.act_alpha, C::lo(zp[k])), act_value(OUT_ACT, p.act_alpha, C::hi(zp[k])),
+                                                    act_value(OUT_ACT, p.act_alpha, C::lo(zp[k + 1])), act_value(OUT_ACT, p.act_alpha, C::hi(zp[k + 1])));
+                                }
+                                if (cs + 16 >= SC) {
+                                    // the slab is complete in this warp: hand it over, one lane of the chain stores it
+                                    fence_async_smem();
+                                    __syncwarp();
+                                    if (lane == 0) mbar_arrive(&stg_full[c]);
+                                    if (q == 0 && lane == 0) {
+                                        ok = ok && mbar_wait(&stg_full[c], slabs & 1u, abort_flag, p.status, kStatusEpiAcc);
+                                        if (ok) {
+                                            tma_store_2d(&tmap_out, (c0 / SC) * SC, (int32_t)(tile * 128u), stage);
+                                            tma_store_commit();
+                                            tma_store_wait_read();
+                                            mbar_arrive(&stg_free[c]);
+                                        }
+                                    }
+                                    ++slabs;
+                                }
                             }
                         }
                     }
@@ -320,6 +359,7 @@ forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const Params p)
         }
     }
 
+    if (warp >= 2 && (warp & 3) == 0 && lane == 0) tma_store_wait_all();  // this thread's output stores have landed
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -364,6 +404,15 @@ static cudaError_t launch_fwd(cudaStream_t st, TcWorkspace* ws, const MlpConfig&
     const CUtensorMapSwizzle sw = DIN >= 64 ? CU_TENSOR_MAP_SWIZZLE_128B : DIN == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
     if (!make_tile_map(ws, &mx, dt, 2, a.inputs, a.count, DIN, fwd::panel_w(DIN), 128, sw, err)) return cudaErrorInvalidValue;
     if (a.outputs & 15u) { if (err) *err = "outputs must be 16-byte aligned"; return cudaErrorInvalidValue; }
+    CUtensorMap mo;
+    {
+        constexpr int SC = G::kSlabCols;
+        const CUtensorMapSwizzle so = SC == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : SC == 16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE;
+        // with storage-type outputs the map is not used; describe the same memory as fp32 of half the width
+        const uint32_t cols = (a.flags & MLP_FLAG_OUTPUT_STORAGE_TYPE) ? DOUT / 2 : DOUT;
+        if (!make_tile_map(ws, &mo, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a.outputs, a.count, cols, SC <= (int)cols ? SC : cols, 128, so, err))
+            return cudaErrorInvalidValue;
+    }
     fwd::Params p;
     p.net = (const MlpLayerPointers*)a.networkBuffer;
     p.out = (float*)a.outputs;
@@ -376,7 +425,7 @@ static cudaError_t launch_fwd(cudaStream_t st, TcWorkspace* ws, const MlpConfig&
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)G::kSmemBytes);
     if (e != cudaSuccess) return e;
     const uint32_t grid = p.n_tiles < (uint32_t)ws->sm_count ? p.n_tiles : (uint32_t)ws->sm_count;
-    kern<<<grid, G::kThreads, G::kSmemBytes, st>>>(mx, p);
+    kern<<<grid, G::kThreads, G::kSmemBytes, st>>>(mx, mo, p);
     return cudaGetLastError();
 }
 
@@ -390,8 +439,8 @@ cudaError_t launch_forward_tc(cudaStream_t st, TcWorkspace* ws, const MlpConfig&
     const bool wide = c.n_layers == 5;
 #define MLPB200_FWD(W_, FMT_, NCH_) \
     if (!wide && w == W_ && c.dtype == FMT_) e = launch_fwd<W_, W_, W_, 4, FMT_, MLP_ACT_RELU, MLP_ACT_IDENTITY, NCH_>(st, ws, c, a, err);
-    MLPB200_FWD(16, MLP_F16, 6) MLPB200_FWD(32, MLP_F16, 6) MLPB200_FWD(64, MLP_F16, 6) MLPB200_FWD(128, MLP_F16, 2)
-    MLPB200_FWD(16, MLP_BF16, 6) MLPB200_FWD(32, MLP_BF16, 6) MLPB200_FWD(64, MLP_BF16, 6) MLPB200_FWD(128, MLP_BF16, 2)
+    MLPB200_FWD(16, MLP_F16, 6) MLPB200_FWD(32, MLP_F16, 6) MLPB200_FWD(64, MLP_F16, 5) MLPB200_FWD(128, MLP_F16, 2)
+    MLPB200_FWD(16, MLP_BF16, 6) MLPB200_FWD(32, MLP_BF16, 6) MLPB200_FWD(64, MLP_BF16, 5) MLPB200_FWD(128, MLP_BF16, 2)
 #undef MLPB200_FWD
     if (wide && c.dtype == MLP_BF16) e = launch_fwd<64, 128, 64, 5, MLP_BF16, MLP_ACT_GELU_TANH, MLP_ACT_IDENTITY, 2>(st, ws, c, a, err);
     if (wide && c.dtype == MLP_F16) e = launch_fwd<64, 128, 64, 5, MLP_F16, MLP_ACT_GELU_TANH, MLP_ACT_IDENTITY, 2>(st, ws, c, a, err);

@@ -102,6 +102,18 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
         ::"r"(smem_u32(smem_dst)), "l"((uint64_t)map), "r"(c0), "r"(c1), "r"(smem_u32(bar))
         : "memory");
 }
+// 2-D tiled TMA store from this CTA's shared memory (bulk async group of the issuing thread).
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int32_t c0, int32_t c1, const void* smem_src)
+{
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"((uint64_t)map), "r"(c0), "r"(c1), "r"(smem_u32(smem_src))
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Returns when the committed stores of this thread have finished READING shared memory.
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map)
 {
     asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)map) : "memory");
