@@ -38,7 +38,7 @@ namespace fwd {
 
 using namespace layout;
 
-enum : uint32_t { kStatusCtrlX = 0x100u, kStatusCtrlAcc = 0x200u, kStatusEpiAcc = 0x400u };
+enum : uint32_t { kStatusCtrlX = 0x100u, kStatusCtrlAcc = 0x200u, kStatusEpiAcc = 0x400u, kStatusAlign = 0x800u };
 
 struct Params {
     const MlpLayerPointers* net;
@@ -85,9 +85,9 @@ template <> struct Cvt<MLP_F16> {
     }
 };
 
-template <int DIN, int DH, int DOUT, int NL, int NCH>
+template <int DIN, int DH, int DOUT, int NL, int NCH, int CS>
 struct Geometry {
-    static constexpr int kThreads = 64 + 128 * NCH;
+    static constexpr int kThreads = 64 + 128 * NCH * CS;  // CS: warps sharing a lane quarter split the columns
     static constexpr int kAccCols = imax(DH, DOUT);
     static constexpr uint32_t kTmemCols = pow2_at_least_32(NCH * kAccCols);
     __host__ __device__ static constexpr int in_dim(int l) { return l == 0 ? DIN : DH; }
@@ -105,27 +105,32 @@ struct Geometry {
     static constexpr int kSlabCols = DOUT < 32 ? DOUT : (DH >= 128 ? 16 : 32);  // narrower slabs where the weights fill shared memory
     static constexpr uint32_t kStageBytes = 128u * kSlabCols * 4u;
     static constexpr uint32_t kStage = kAct + NCH * kActBytes;
-    static constexpr uint32_t kBias = kStage + NCH * kStageBytes;  // fp32 [NL][128]
+    static constexpr uint32_t kBias = kStage + NCH * CS * kStageBytes;  // fp32 [NL][128]
     static constexpr uint32_t kBars = kBias + NL * 128 * 4;        // x_full, acc_full, acc_free, stg_full, stg_free (NCH each)
-    static constexpr uint32_t kTmemPtr = kBars + 5 * NCH * 8;
+    static constexpr uint32_t kTmemPtr = kBars + (3 + 2 * CS) * NCH * 8;
     static constexpr uint32_t kAbort = kTmemPtr + 4;
-    static constexpr uint32_t kSmemBytes = kAbort + 4 + 1024;
+    static constexpr uint32_t kSmemBytes = kAbort + 4;  // the dynamic shared-memory base must be 1024-byte aligned (checked at run time)
+    static_assert((DH / CS) % 16 == 0 && (DOUT / CS) % 16 == 0, "column split");
 };
 
-template <int DIN, int DH, int DOUT, int NL, int FMT, int ACT, int OUT_ACT, int NCH>
-__global__ void __launch_bounds__(64 + 128 * NCH, 1)
+template <int DIN, int DH, int DOUT, int NL, int FMT, int ACT, int OUT_ACT, int NCH, int CS>
+__global__ void __launch_bounds__(64 + 128 * NCH * CS, 1)
 forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_out, const Params p)
 {
-    using G = Geometry<DIN, DH, DOUT, NL, NCH>;
+    using G = Geometry<DIN, DH, DOUT, NL, NCH, CS>;
     using C = Cvt<FMT>;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = smem_raw;
     const uint32_t sbase = smem_u32(smem);
+    if (sbase & 1023u) {  // the swizzled operand layouts need a 1024-byte aligned base
+        if (threadIdx.x == 0) atomicOr(p.status, kStatusAlign);
+        return;
+    }
     uint64_t* x_full = (uint64_t*)(smem + G::kBars);
     uint64_t* acc_full = x_full + NCH;
     uint64_t* acc_free = acc_full + NCH;
     uint64_t* stg_full = acc_free + NCH;   // the chain's four warps have written the output slab
-    uint64_t* stg_free = stg_full + NCH;   // the slab's TMA store has finished reading shared memory
+    uint64_t* stg_free = stg_full + NCH * CS;  // the slab's TMA store has finished reading shared memory
     uint32_t* tmem_ptr = (uint32_t*)(smem + G::kTmemPtr);
     volatile uint32_t* abort_flag = (volatile uint32_t*)(smem + G::kAbort);
     float* s_bias = (float*)(smem + G::kBias);
@@ -138,7 +143,9 @@ forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
         for (int c = 0; c < NCH; ++c) {
             mbar_init(&x_full[c], 1);
             mbar_init(&acc_full[c], 1);
-            mbar_init(&acc_free[c], 4);
+            mbar_init(&acc_free[c], 4 * CS);
+        }
+        for (int c = 0; c < NCH * CS; ++c) {
             mbar_init(&stg_full[c], 4);
             mbar_init(&stg_free[c], 1);
         }
@@ -246,12 +253,14 @@ forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
         }
     } else if (warp >= 2) {
         // =================================== epilogue warps ========================================
-        const int c = (warp - 2) >> 2;   // chain
+        const int g = (warp - 2) >> 2;   // group of four warps: one chain's share of the columns
+        const int c = g / CS;            // chain
+        const int sub = g % CS;          // which part of the layer's columns
         const int q = warp & 3;          // TMEM lane quarter this warp may read
         const int r = q * 32 + lane;     // the sample row this thread owns
         const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * G::kAccCols);
         uint8_t* abuf = smem + G::kAct + c * G::kActBytes;
-        uint8_t* stage = smem + G::kStage + c * G::kStageBytes;
+        uint8_t* stage = smem + G::kStage + g * G::kStageBytes;
         uint32_t step = 0, slabs = 0;  // slabs: output slabs this chain has handed to TMA stores so far
         bool ok = true;
         for (uint32_t i = (uint32_t)c; i < n_my_tiles && ok; i += NCH) {
@@ -263,7 +272,7 @@ forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
                 if (ok) {
                     tc_fence_after();
                     const bool last = (l == NL - 1);
-                    if (last && q == 0 && lane == 0 && i + NCH < n_my_tiles) {
+                    if (last && sub == 0 && q == 0 && lane == 0 && i + NCH < n_my_tiles) {
                         // The last product has read this chain's operand buffer: fetch the chain's next tile.
                         const uint32_t next = blockIdx.x + (i + NCH) * gridDim.x;
                         mbar_expect_tx(&x_full[c], kXBytes);
@@ -275,7 +284,8 @@ forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
                     const float* bl = s_bias + l * 128;
                     const uint64_t row_index = (uint64_t)tile * 128u + (uint64_t)r;
 #pragma unroll
-                    for (int c0 = 0; c0 < G::out_dim(l); c0 += 16) {
+                    for (int cc = 0; cc < G::out_dim(l) / CS; cc += 16) {
+                        const int c0 = sub * (G::out_dim(l) / CS) + cc;  // this warp's share of the columns
                         uint32_t v[16];
                         tmem_ld_32x16(t_acc + (uint32_t)c0, v);
                         tmem_ld_wait();
@@ -321,7 +331,7 @@ forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
                                 constexpr int CPR = SC / 4;               // 16-byte chunks per slab row
                                 const int cs = c0 % SC;                   // first column of this 16-column piece inside the slab
                                 if (cs == 0) {
-                                    if (slabs > 0) ok = ok && mbar_wait(&stg_free[c], (slabs - 1) & 1u, abort_flag, p.status, kStatusEpiAcc);
+                                    if (slabs > 0) ok = ok && mbar_wait(&stg_free[g], (slabs - 1) & 1u, abort_flag, p.status, kStatusEpiAcc);
                                 }
 #pragma unroll
                                 for (int k = 0; k < 8; k += 2) {
@@ -335,14 +345,14 @@ forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
                                     // the slab is complete in this warp: hand it over, one lane of the chain stores it
                                     fence_async_smem();
                                     __syncwarp();
-                                    if (lane == 0) mbar_arrive(&stg_full[c]);
+                                    if (lane == 0) mbar_arrive(&stg_full[g]);
                                     if (q == 0 && lane == 0) {
-                                        ok = ok && mbar_wait(&stg_full[c], slabs & 1u, abort_flag, p.status, kStatusEpiAcc);
+                                        ok = ok && mbar_wait(&stg_full[g], slabs & 1u, abort_flag, p.status, kStatusEpiAcc);
                                         if (ok) {
                                             tma_store_2d(&tmap_out, (c0 / SC) * SC, (int32_t)(tile * 128u), stage);
                                             tma_store_commit();
                                             tma_store_wait_read();
-                                            mbar_arrive(&stg_free[c]);
+                                            mbar_arrive(&stg_free[g]);
                                         }
                                     }
                                     ++slabs;
@@ -393,10 +403,10 @@ bool tc_forward_supported(const MlpConfig& c)
     return true;
 }
 
-template <int DIN, int DH, int DOUT, int NL, int FMT, int ACT, int OUT_ACT, int NCH>
+template <int DIN, int DH, int DOUT, int NL, int FMT, int ACT, int OUT_ACT, int NCH, int CS>
 static cudaError_t launch_fwd(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const MlpForwardParams& a, std::string* err)
 {
-    using G = fwd::Geometry<DIN, DH, DOUT, NL, NCH>;
+    using G = fwd::Geometry<DIN, DH, DOUT, NL, NCH, CS>;
     static_assert(G::kSmemBytes <= 227 * 1024, "shared memory budget");
     static_assert(G::kTmemCols <= 512, "tensor memory budget");
     CUtensorMap mx;
@@ -421,7 +431,7 @@ static cudaError_t launch_fwd(cudaStream_t st, TcWorkspace* ws, const MlpConfig&
     p.n_tiles = (a.count + 127u) / 128u;
     p.act_alpha = c.act_alpha;
     p.out_storage = (a.flags & MLP_FLAG_OUTPUT_STORAGE_TYPE) ? 1u : 0u;
-    auto kern = fwd::forward_tc_kernel<DIN, DH, DOUT, NL, FMT, ACT, OUT_ACT, NCH>;
+    auto kern = fwd::forward_tc_kernel<DIN, DH, DOUT, NL, FMT, ACT, OUT_ACT, NCH, CS>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)G::kSmemBytes);
     if (e != cudaSuccess) return e;
     const uint32_t grid = p.n_tiles < (uint32_t)ws->sm_count ? p.n_tiles : (uint32_t)ws->sm_count;
@@ -437,13 +447,13 @@ cudaError_t launch_forward_tc(cudaStream_t st, TcWorkspace* ws, const MlpConfig&
     cudaError_t e = cudaErrorInvalidValue;
     const int w = c.dims[1];
     const bool wide = c.n_layers == 5;
-#define MLPB200_FWD(W_, FMT_, NCH_) \
-    if (!wide && w == W_ && c.dtype == FMT_) e = launch_fwd<W_, W_, W_, 4, FMT_, MLP_ACT_RELU, MLP_ACT_IDENTITY, NCH_>(st, ws, c, a, err);
-    MLPB200_FWD(16, MLP_F16, 6) MLPB200_FWD(32, MLP_F16, 6) MLPB200_FWD(64, MLP_F16, 5) MLPB200_FWD(128, MLP_F16, 2)
-    MLPB200_FWD(16, MLP_BF16, 6) MLPB200_FWD(32, MLP_BF16, 6) MLPB200_FWD(64, MLP_BF16, 5) MLPB200_FWD(128, MLP_BF16, 2)
+#define MLPB200_FWD(W_, FMT_, NCH_, CS_) \
+    if (!wide && w == W_ && c.dtype == FMT_) e = launch_fwd<W_, W_, W_, 4, FMT_, MLP_ACT_RELU, MLP_ACT_IDENTITY, NCH_, CS_>(st, ws, c, a, err);
+    MLPB200_FWD(16, MLP_F16, 6, 1) MLPB200_FWD(32, MLP_F16, 6, 1) MLPB200_FWD(64, MLP_F16, 6, 1) MLPB200_FWD(128, MLP_F16, 2, 2)
+    MLPB200_FWD(16, MLP_BF16, 6, 1) MLPB200_FWD(32, MLP_BF16, 6, 1) MLPB200_FWD(64, MLP_BF16, 6, 1) MLPB200_FWD(128, MLP_BF16, 2, 2)
 #undef MLPB200_FWD
-    if (wide && c.dtype == MLP_BF16) e = launch_fwd<64, 128, 64, 5, MLP_BF16, MLP_ACT_GELU_TANH, MLP_ACT_IDENTITY, 2>(st, ws, c, a, err);
-    if (wide && c.dtype == MLP_F16) e = launch_fwd<64, 128, 64, 5, MLP_F16, MLP_ACT_GELU_TANH, MLP_ACT_IDENTITY, 2>(st, ws, c, a, err);
+    if (wide && c.dtype == MLP_BF16) e = launch_fwd<64, 128, 64, 5, MLP_BF16, MLP_ACT_GELU_TANH, MLP_ACT_IDENTITY, 2, 2>(st, ws, c, a, err);
+    if (wide && c.dtype == MLP_F16) e = launch_fwd<64, 128, 64, 5, MLP_F16, MLP_ACT_GELU_TANH, MLP_ACT_IDENTITY, 2, 2>(st, ws, c, a, err);
     *launches += 1;
     return e;
 }
