@@ -185,12 +185,13 @@ def sweep_forward(args):
     peaks = measured_peaks()
     flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev_t)
     points = []
-    for w in (16, 32, 64, 128):
+    single = args.config.startswith("c5_w")  # one point: --config c5_w64 --batch N
+    widths = (int(args.config[4:]),) if single else (16, 32, 64, 128)
+    for w in widths:
         cfg = C.named_config("c5_w%d" % w)
         tr = Trainer(device, cfg, C.init_params(cfg, seed=7, scheme="kaiming"))
         assert tr.k_forward.implementation == "tcgen05"
-        for lg in (20, 22, 24, 26):
-            n = 1 << lg
+        for n in ((args.batch,) if single else (1 << 20, 1 << 22, 1 << 24, 1 << 26)):
             gen = torch.Generator(device=dev_t); gen.manual_seed(7)
             x = torch.empty((n, w), dtype=torch.float16, device=dev_t)
             piece = 1 << 22
@@ -325,7 +326,7 @@ def main():
         if rank == 0:
             bench_narrow(args)
         return
-    if args.config == "c5_sweep":
+    if args.config == "c5_sweep" or args.config.startswith("c5_w"):
         if rank == 0:
             sweep_forward(args)
         return
