@@ -37,7 +37,7 @@ using namespace ptx;
 
 // Status-word codes (which wait gave up).
 enum : uint32_t {
-    kStatusCtrlAcc = 1u, kStatusCtrlX = 2u, kStatusEpiAcc = 4u, kStatusEpiTarget = 8u, kStatusEpiLoss = 16u,
+    kStatusCtrlAcc = 1u, kStatusCtrlX = 2u, kStatusEpiAcc = 4u, kStatusEpiTarget = 8u, kStatusEpiLoss = 16u, kStatusAlign = 32u,
 };
 
 #ifdef MLPB200_SPIN
@@ -77,7 +77,7 @@ constexpr uint32_t kLossPart = kBias + 5 * 128 * 4;  // fp32 [2][64]
 constexpr uint32_t kBars = kLossPart + 2 * 64 * 4;   // mbarriers: x_full[2], t_full, acc_full[2], acc_free[2], loss_bar[2]
 constexpr uint32_t kTmemPtr = kBars + 14 * 8;
 constexpr uint32_t kAbort = kTmemPtr + 4;
-constexpr uint32_t kSmemBytes = kAbort + 4 + 1024;   // + slack for aligning the base
+constexpr uint32_t kSmemBytes = kAbort + 4;   // the dynamic shared-memory base must be 1024-byte aligned (checked at run time)
 
 // Tensor-memory columns.
 constexpr uint32_t kColDW1 = 0, kColDW4T = 384, kColAcc = 448, kTmemCols = 512;
@@ -183,9 +183,13 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
 {
     using namespace wide;
     using E = Elem<FMT>;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = smem_raw;
     const uint32_t sbase = smem_u32(smem);
+    if (sbase & 1023u) {  // the swizzled operand layouts need a 1024-byte aligned base
+        if (threadIdx.x == 0) atomicOr(p.status, kStatusAlign);
+        return;
+    }
     uint64_t* bars = (uint64_t*)(smem + kBars);
     uint64_t* x_full = bars;        // [2]
     uint64_t* t_full = bars + 2;
