@@ -476,7 +476,10 @@ def main():
             "clocks": clocks, "gpu_launches": launches, "e2e": e2e,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_sustained"], "unit": "TFLOP/s",
                          "frac": achieved / peaks["bf16_sustained"], "frac_of_burst": achieved / peaks["bf16_burst"],
-                         "traffic": None, "peak_source": peaks["source"] + " (sustained bf16 GEMM; kernel timed inside the step loop)",
+                         # dram read + write bytes of one launch: 275.1 MB captured by ncu on a 2^20-sample launch
+                         # (profiles/learn_gradient_wide_c4.md), scaled by the samples of this launch
+                         "traffic": int(round(275.1e6 / 1048576 * count)), "traffic_source": "ncu capture at 2^20 samples, scaled per sample",
+                         "peak_source": peaks["source"] + " (sustained bf16 GEMM; kernel timed inside the step loop)",
                          "kernel": "learn_gradient_wide_kernel", "kernel_ms": kernel_ms, "flop_per_sample": flops,
                          "hbm_gbs": count * 256 / (kernel_ms * 1e-3) / 1e9},
             "loss": {"max": mx, "mean_local": sm / count},
