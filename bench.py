@@ -313,6 +313,8 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=2)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--deterministic-sum", action="store_true",
+                    help="N>1: gather every rank's gradient segment and add in rank order instead of an all-reduce")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -379,7 +381,8 @@ def main():
 
     def allreduce():
         if world > 1:
-            allreduce_gradients(grads_t)  # fp32 sum of the flat gradient segment (NCCL over NVLink)
+            # fp32 sum of the flat gradient segment (NCCL over NVLink)
+            allreduce_gradients(grads_t, deterministic=args.deterministic_sum)
 
     def step(i):
         b = i % n_batches
@@ -472,7 +475,7 @@ def main():
             "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": workload_name(args), "global_batch": args.batch, "per_gpu_batch": count,
-                       "parallelism": "dp%d" % world, "l2": "inputs (%.1f GB per step per GPU) larger than L2; two batches alternate" % (count * 256 / 1e9)},
+                       "parallelism": "dp%d" % world, "gradient_sum": "rank-ordered gather" if args.deterministic_sum else "all-reduce", "l2": "inputs (%.1f GB per step per GPU) larger than L2; two batches alternate" % (count * 256 / 1e9)},
             "clocks": clocks, "gpu_launches": launches, "e2e": e2e,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_sustained"], "unit": "TFLOP/s",
                          "frac": achieved / peaks["bf16_sustained"], "frac_of_burst": achieved / peaks["bf16_burst"],

@@ -116,6 +116,15 @@ int32_t mlp_buffer_write(MlpDevice* device, MlpBuffer* buffer, size_t offset, si
 /* loadComputeProgram / findEntryPointByName (mlp-training.cpp:291-312): the literal example's entry
  * points "learnGradient" and "adjustParameters" (examples/mlp-training/kernels.slang:8-41). */
 int32_t mlp_kernel_get(MlpDevice* device, const char* entry_point, MlpKernel** out_kernel);
+/* createShaderProgram / createComputePipeline for precompiled device code (mlp-training.cpp:341-377;
+ * the CUDA backend loads the module it gets with cuModuleLoadData and looks the entry point up by
+ * name).  image is a cubin or PTX module, for example this library's own mlp_training_kernels.cubin
+ * or a module built by nvcc from the CUDA source the reference compiler emits for kernels.slang.
+ * mlp_dispatch on such a kernel passes the argument bytes unchanged as the kernel's packed parameter
+ * buffer and launches block (256,1,1), grid (gx,gy,gz), as tools/gfx/cuda/cuda-command-queue.cpp:122-147
+ * does.  mlp_kernel_implementation reports "module". */
+int32_t mlp_kernel_load(MlpDevice* device, const void* image, size_t image_size, const char* entry_point,
+                        MlpKernel** out_kernel);
 /* The same entry points specialised for a problem description, the way the reference specialises
  * FeedForwardLayer<In, Out> at compile time.  entry_point is one of
  *   "learnGradient"      args MlpLearnGradParamsEx   (fastest implementation for the shape)

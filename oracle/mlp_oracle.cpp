@@ -550,54 +550,118 @@ extern "C" {
 
 // learnGradient of the example over `count` samples; network points at two MlpLayerPointers with
 // host addresses; inputs is count float2.
+static void ex_learn_thread(uint32_t tid, const MlpLayerPointers* network, uint32_t* loss_word, const float* inputs,
+                            uint32_t count)
+{
+    if (tid >= count) return;
+    hf x = (hf)inputs[2 * tid], y = (hf)inputs[2 * tid + 1];
+    hf enc[4] = {x, y, x * x, y * y};
+    hf h1[16], out[4], gt[4], diff[4];
+    ex_layer_eval<4, 16>(network[0], enc, h1);
+    ex_layer_eval<16, 4>(network[1], h1, out);
+    ex_groundtruth(x, y, gt);
+    for (int k = 0; k < 4; ++k) diff[k] = out[k] - gt[k];
+    // d dot(diff, diff) with dOut = 1: each factor contributes diff * dOut (diff.meta.slang:1608-1621).
+    hf g2[4];
+    for (int k = 0; k < 4; ++k) g2[k] = diff[k] * (hf)1.0f + diff[k] * (hf)1.0f;
+    hf g1[16], dead[4];
+    ex_layer_bwd<16, 4>(network[1], h1, g2, g1);
+    ex_layer_bwd<4, 16>(network[0], enc, g1, dead);
+    hf l = (hf)0.0f;
+    for (int k = 0; k < 4; ++k) l += diff[k] * diff[k];
+    uint32_t bits = f2u((float)l);
+    if (bits > *loss_word) *loss_word = bits;
+}
+
 int mlp_oracle_example_learn_gradient(const MlpLayerPointers* network, uint32_t* loss_word, const float* inputs,
                                       uint32_t count)
 {
-    for (uint32_t tid = 0; tid < count; ++tid) {
-        hf x = (hf)inputs[2 * tid], y = (hf)inputs[2 * tid + 1];
-        hf enc[4] = {x, y, x * x, y * y};
-        hf h1[16], out[4], gt[4], diff[4];
-        ex_layer_eval<4, 16>(network[0], enc, h1);
-        ex_layer_eval<16, 4>(network[1], h1, out);
-        ex_groundtruth(x, y, gt);
-        for (int k = 0; k < 4; ++k) diff[k] = out[k] - gt[k];
-        // d dot(diff, diff) with dOut = 1: each factor contributes diff * dOut (diff.meta.slang:1608-1621).
-        hf g2[4];
-        for (int k = 0; k < 4; ++k) g2[k] = diff[k] * (hf)1.0f + diff[k] * (hf)1.0f;
-        hf g1[16], dead[4];
-        ex_layer_bwd<16, 4>(network[1], h1, g2, g1);
-        ex_layer_bwd<4, 16>(network[0], enc, g1, dead);
-        hf l = (hf)0.0f;
-        for (int k = 0; k < 4; ++k) l += diff[k] * diff[k];
-        uint32_t bits = f2u((float)l);
-        if (bits > *loss_word) *loss_word = bits;
-    }
+    for (uint32_t tid = 0; tid < count; ++tid) ex_learn_thread(tid, network, loss_word, inputs, count);
     return 0;
+}
+
+static void ex_adjust_thread(uint32_t i, MlpExampleAdamState* states, uint16_t* params, uint16_t* grads, uint32_t count)
+{
+    if (i >= count) return;
+    const hf beta1 = (hf)0.9f, beta2 = (hf)0.999f, eps = (hf)1e-7f, lr = (hf)0.01f;
+    hf g; std::memcpy(&g, &grads[i], 2);
+    if (g != g) { grads[i] = 0; return; }
+    hf p; std::memcpy(&p, &params[i], 2);
+    hf m, v; std::memcpy(&m, &states[i].mean, 2); std::memcpy(&v, &states[i].variance, 2);
+    states[i].iteration++;
+    if (std::isinf((float)g)) g = g > (hf)0.0f ? (hf)10000.0f : (hf)-10000.0f;
+    m = beta1 * m + ((hf)1.0f - beta1) * g;
+    v = beta2 * v + ((hf)1.0f - beta2) * g * g;
+    hf it = (hf)(float)states[i].iteration;
+    hf mean_hat = m / ((hf)1.0f - (hf)std::pow((float)beta1, (float)it));
+    hf var_hat = v / ((hf)1.0f - (hf)std::pow((float)beta2, (float)it));
+    hf mx = var_hat > (hf)0.0f ? var_hat : (hf)0.0f;
+    hf den = (hf)std::sqrt((float)(hf)(mx + eps));
+    p -= lr * mean_hat / den;
+    std::memcpy(&params[i], &p, 2);
+    std::memcpy(&states[i].mean, &m, 2); std::memcpy(&states[i].variance, &v, 2);
+    grads[i] = 0;
 }
 
 int mlp_oracle_example_adjust_parameters(MlpExampleAdamState* states, uint16_t* params, uint16_t* grads, uint32_t count)
 {
-    const hf beta1 = (hf)0.9f, beta2 = (hf)0.999f, eps = (hf)1e-7f, lr = (hf)0.01f;
-    for (uint32_t i = 0; i < count; ++i) {
-        hf g; std::memcpy(&g, &grads[i], 2);
-        if (g != g) { grads[i] = 0; continue; }
-        hf p; std::memcpy(&p, &params[i], 2);
-        hf m, v; std::memcpy(&m, &states[i].mean, 2); std::memcpy(&v, &states[i].variance, 2);
-        states[i].iteration++;
-        if (std::isinf((float)g)) g = g > (hf)0.0f ? (hf)10000.0f : (hf)-10000.0f;
-        m = beta1 * m + ((hf)1.0f - beta1) * g;
-        v = beta2 * v + ((hf)1.0f - beta2) * g * g;
-        hf it = (hf)(float)states[i].iteration;
-        hf mean_hat = m / ((hf)1.0f - (hf)std::pow((float)beta1, (float)it));
-        hf var_hat = v / ((hf)1.0f - (hf)std::pow((float)beta2, (float)it));
-        hf mx = var_hat > (hf)0.0f ? var_hat : (hf)0.0f;
-        hf den = (hf)std::sqrt((float)(hf)(mx + eps));
-        p -= lr * mean_hat / den;
-        std::memcpy(&params[i], &p, 2);
-        std::memcpy(&states[i].mean, &m, 2); std::memcpy(&states[i].variance, &v, 2);
-        grads[i] = 0;
-    }
+    for (uint32_t i = 0; i < count; ++i) ex_adjust_thread(i, states, params, grads, count);
     return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// The two example kernels behind the calling convention of a compute entry point compiled for the
+// CPU (docs/cpu-target.md:363-424, prelude/slang-cpp-types.h:1336-1358): per entry point three
+// exported functions.  `name` runs the groups of [startGroupID, endGroupID), `name_Group` runs the one
+// group startGroupID, `name_Thread` runs one thread; groups in ascending order and the 256 threads of
+// a group in ascending order (source/slang/slang-emit-cpp.cpp:2210-2284).  entryPointParams is the
+// packed uniform parameter struct (pointers at 0/8/16, count at 24, examples/mlp-training/
+// mlp-training.cpp:55-69) holding host addresses; globalParams is unused.  The kernels are
+// one-dimensional: the y and z ranges must be [0,1).
+// ---------------------------------------------------------------------------------------------
+struct OracleUint3 { uint32_t x, y, z; };
+struct OracleComputeVaryingInput { OracleUint3 startGroupID, endGroupID; };
+struct OracleComputeThreadVaryingInput { OracleUint3 groupID, groupThreadID; };
+struct OracleEntryParams { uint64_t p0, p1, p2; uint32_t count; };
+
+static const uint32_t kGroupThreads = 256;  // [numthreads(256,1,1)], examples/mlp-training/kernels.slang:7,29
+
+static void learn_run_thread(uint32_t tid, const void* ep)
+{
+    OracleEntryParams a; std::memcpy(&a, ep, 28);
+    ex_learn_thread(tid, (const MlpLayerPointers*)(uintptr_t)a.p0, (uint32_t*)(uintptr_t)a.p1, (const float*)(uintptr_t)a.p2, a.count);
+}
+static void adjust_run_thread(uint32_t tid, const void* ep)
+{
+    OracleEntryParams a; std::memcpy(&a, ep, 28);
+    ex_adjust_thread(tid, (MlpExampleAdamState*)(uintptr_t)a.p0, (uint16_t*)(uintptr_t)a.p1, (uint16_t*)(uintptr_t)a.p2, a.count);
+}
+
+void learnGradient_Thread(OracleComputeThreadVaryingInput* v, void* entryPointParams, void*)
+{
+    learn_run_thread(v->groupID.x * kGroupThreads + v->groupThreadID.x, entryPointParams);
+}
+void learnGradient_Group(OracleComputeVaryingInput* v, void* entryPointParams, void*)
+{
+    for (uint32_t t = 0; t < kGroupThreads; ++t) learn_run_thread(v->startGroupID.x * kGroupThreads + t, entryPointParams);
+}
+void learnGradient(OracleComputeVaryingInput* v, void* entryPointParams, void*)
+{
+    for (uint32_t g = v->startGroupID.x; g < v->endGroupID.x; ++g)
+        for (uint32_t t = 0; t < kGroupThreads; ++t) learn_run_thread(g * kGroupThreads + t, entryPointParams);
+}
+void adjustParameters_Thread(OracleComputeThreadVaryingInput* v, void* entryPointParams, void*)
+{
+    adjust_run_thread(v->groupID.x * kGroupThreads + v->groupThreadID.x, entryPointParams);
+}
+void adjustParameters_Group(OracleComputeVaryingInput* v, void* entryPointParams, void*)
+{
+    for (uint32_t t = 0; t < kGroupThreads; ++t) adjust_run_thread(v->startGroupID.x * kGroupThreads + t, entryPointParams);
+}
+void adjustParameters(OracleComputeVaryingInput* v, void* entryPointParams, void*)
+{
+    for (uint32_t g = v->startGroupID.x; g < v->endGroupID.x; ++g)
+        for (uint32_t t = 0; t < kGroupThreads; ++t) adjust_run_thread(g * kGroupThreads + t, entryPointParams);
 }
 
 // The host's float -> half conversion that initialises the example's parameters

@@ -96,3 +96,39 @@ def example_learn_gradient(network_ptrs, loss_word, inputs, count):
 def example_adjust_parameters(states, params, grads, count):
     rc = lib().mlp_oracle_example_adjust_parameters(_p(states), _p(params), _p(grads), ctypes.c_uint32(count))
     assert rc == 0
+
+
+# ---- the example kernels behind the CPU compute entry-point calling convention ------------------
+class _Uint3(ctypes.Structure):
+    _fields_ = [("x", ctypes.c_uint32), ("y", ctypes.c_uint32), ("z", ctypes.c_uint32)]
+
+
+class ComputeVaryingInput(ctypes.Structure):
+    """prelude/slang-cpp-types.h:1343-1347"""
+    _fields_ = [("startGroupID", _Uint3), ("endGroupID", _Uint3)]
+
+
+class ComputeThreadVaryingInput(ctypes.Structure):
+    """prelude/slang-cpp-types.h:1337-1341"""
+    _fields_ = [("groupID", _Uint3), ("groupThreadID", _Uint3)]
+
+
+class EntryParams(ctypes.Structure):
+    """Packed uniform parameters of either example kernel: three addresses and a count (28 bytes used)."""
+    _fields_ = [("p0", ctypes.c_uint64), ("p1", ctypes.c_uint64), ("p2", ctypes.c_uint64), ("count", ctypes.c_uint32)]
+
+
+def cpu_entry_range(name, params, start_group, end_group):
+    """Calls `name` (learnGradient / adjustParameters) over the groups [start_group, end_group)."""
+    v = ComputeVaryingInput(_Uint3(start_group, 0, 0), _Uint3(end_group, 1, 1))
+    getattr(lib(), name)(ctypes.byref(v), ctypes.byref(params), None)
+
+
+def cpu_entry_group(name, params, group):
+    v = ComputeVaryingInput(_Uint3(group, 0, 0), _Uint3(group + 1, 1, 1))
+    getattr(lib(), name + "_Group")(ctypes.byref(v), ctypes.byref(params), None)
+
+
+def cpu_entry_thread(name, params, group, thread):
+    v = ComputeThreadVaryingInput(_Uint3(group, 0, 0), _Uint3(thread, 0, 0))
+    getattr(lib(), name + "_Thread")(ctypes.byref(v), ctypes.byref(params), None)

@@ -111,6 +111,13 @@ class Device:
             check(load().mlp_kernel_get_for_config(self.handle, ctypes.byref(cfg), entry_point.encode(), ctypes.byref(h)))
         return Kernel(self, h)
 
+    def load_kernel(self, image, entry_point):
+        """A kernel from a caller-supplied device module (cubin or PTX bytes); dispatch passes the argument
+        bytes as the packed parameter buffer, block (256,1,1)."""
+        h = ctypes.c_void_p()
+        check(load().mlp_kernel_load(self.handle, image, len(image), entry_point.encode(), ctypes.byref(h)))
+        return Kernel(self, h)
+
     def wait(self):
         check(load().mlp_wait(self.handle))
 

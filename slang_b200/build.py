@@ -3,7 +3,8 @@
     python -m slang_b200.build [--force] [--verbose]
 
 Each translation unit is compiled to an object with its own flags and the objects are linked into
-slang_b200/libslang_b200_mlp.so.  The CUDA runtime is linked statically so the library has no
+slang_b200/libslang_b200_mlp.so; the literal example entry points are also built into a stand-alone
+device module, slang_b200/mlp_training_kernels.cubin.  The CUDA runtime is linked statically so the library has no
 dependency beyond the driver.
 """
 import os
@@ -15,6 +16,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libslang_b200_mlp.so")
 OBJDIR = os.path.join(HERE, "build")
+# Stand-alone device module holding the literal example entry points (for cuModuleLoadData hosts).
+CUBIN = os.path.join(HERE, "mlp_training_kernels.cubin")
+CUBIN_SRC = "example_module.cu"
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
@@ -63,6 +67,12 @@ def build(force=False, verbose=False):
                 print(" ".join(cmd), flush=True)
             subprocess.check_call(cmd)
             rebuilt = True
+    cs = os.path.join(CSRC, CUBIN_SRC)
+    if force or not os.path.exists(CUBIN) or os.path.getmtime(CUBIN) < max(os.path.getmtime(cs), newest_header):
+        cmd = [nvcc, "-arch=sm_100a", "-cubin", "-O3", "-std=c++17", "-lineinfo", "-fmad=false", cs, "-o", CUBIN]
+        if verbose:
+            print(" ".join(cmd), flush=True)
+        subprocess.check_call(cmd)
     if rebuilt or not os.path.exists(OUT):
         cmd = [nvcc] + ARCH + ["-shared", "-cudart", "static", "-o", OUT] + objs
         if verbose:

@@ -1,6 +1,7 @@
 // The C ABI: devices, buffers, kernel handles and dispatch over the CUDA runtime.
 // One function per call the reference's example host loop makes through slang-rhi
 // (examples/mlp-training/mlp-training.cpp:92-312); see include/slang_b200_mlp.h.
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include <cstdarg>
@@ -34,7 +35,42 @@ int32_t fail(int32_t code, const char* fmt, ...)
         if (e_ != cudaSuccess) return fail(MLP_E_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e_)); \
     } while (0)
 
-enum class Entry { ExampleLearn, ExampleAdjust, Learn, LearnSimt, Adjust, Forward, ForwardSimt };
+enum class Entry { ExampleLearn, ExampleAdjust, Learn, LearnSimt, Adjust, Forward, ForwardSimt, Module };
+
+// Driver entry points for caller-supplied device modules, resolved through the runtime so that the
+// library carries no link-time dependency on the driver library.
+struct DriverApi {
+    CUresult (*moduleLoadData)(CUmodule*, const void*) = nullptr;
+    CUresult (*moduleUnload)(CUmodule) = nullptr;
+    CUresult (*moduleGetFunction)(CUfunction*, CUmodule, const char*) = nullptr;
+    CUresult (*launchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream,
+                             void**, void**) = nullptr;
+    CUresult (*getErrorString)(CUresult, const char**) = nullptr;
+    bool ok = false;
+};
+
+const DriverApi& driver_api()
+{
+    static DriverApi api = [] {
+        DriverApi a;
+        auto get = [](const char* name, void** fn) {
+            cudaDriverEntryPointQueryResult q;
+            return cudaGetDriverEntryPoint(name, fn, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess && *fn;
+        };
+        a.ok = get("cuModuleLoadData", (void**)&a.moduleLoadData) && get("cuModuleUnload", (void**)&a.moduleUnload) &&
+               get("cuModuleGetFunction", (void**)&a.moduleGetFunction) && get("cuLaunchKernel", (void**)&a.launchKernel) &&
+               get("cuGetErrorString", (void**)&a.getErrorString);
+        return a;
+    }();
+    return api;
+}
+
+const char* cu_error(CUresult r)
+{
+    const char* s = nullptr;
+    if (driver_api().getErrorString && driver_api().getErrorString(r, &s) == CUDA_SUCCESS && s) return s;
+    return "unknown driver error";
+}
 
 bool config_ok(const MlpConfig* c, std::string* why)
 {
@@ -80,6 +116,9 @@ struct MlpKernel {
     Entry entry;
     MlpConfig cfg;
     const char* impl;
+    int ordinal = 0;
+    CUmodule module = nullptr;     // Entry::Module only
+    CUfunction function = nullptr;
 };
 
 extern "C" {
@@ -257,12 +296,65 @@ int32_t mlp_kernel_get_for_config(MlpDevice* d, const MlpConfig* config, const c
     return MLP_OK;
 }
 
-int32_t mlp_kernel_destroy(MlpKernel* k) { delete k; return MLP_OK; }
+int32_t mlp_kernel_load(MlpDevice* d, const void* image, size_t image_size, const char* entry_point, MlpKernel** out_kernel)
+{
+    if (!d || !image || !entry_point || !out_kernel) return fail(MLP_E_INVALID_ARG, "null argument");
+    *out_kernel = nullptr;
+    if (image_size < 4) return fail(MLP_E_INVALID_ARG, "device module image of %zu bytes is too small", image_size);
+    const DriverApi& api = driver_api();
+    if (!api.ok) return fail(MLP_E_NOT_AVAILABLE, "the CUDA driver's module entry points could not be resolved");
+    CUDA_TRY(cudaSetDevice(d->ordinal));
+    CUDA_TRY(cudaFree(nullptr));  // makes the device's primary context current for the driver calls
+    // cuModuleLoadData reads a cubin by its header and PTX up to its terminating zero; copy the image so
+    // that a text image is terminated whatever the caller passed.
+    std::string copy((const char*)image, image_size);
+    CUmodule mod = nullptr;
+    CUresult r = api.moduleLoadData(&mod, copy.c_str());
+    if (r != CUDA_SUCCESS) return fail(MLP_E_CUDA, "cuModuleLoadData failed: %s", cu_error(r));
+    CUfunction fn = nullptr;
+    r = api.moduleGetFunction(&fn, mod, entry_point);
+    if (r != CUDA_SUCCESS) {
+        api.moduleUnload(mod);
+        return fail(MLP_E_NOT_AVAILABLE, "no entry point named '%s' in the module: %s", entry_point, cu_error(r));
+    }
+    MlpKernel* k = new MlpKernel();
+    std::memset(&k->cfg, 0, sizeof k->cfg);
+    k->entry = Entry::Module;
+    k->impl = "module";
+    k->ordinal = d->ordinal;
+    k->module = mod;
+    k->function = fn;
+    *out_kernel = k;
+    return MLP_OK;
+}
+
+int32_t mlp_kernel_destroy(MlpKernel* k)
+{
+    if (k && k->module) {
+        cudaSetDevice(k->ordinal);
+        driver_api().moduleUnload(k->module);
+    }
+    delete k;
+    return MLP_OK;
+}
 const char* mlp_kernel_implementation(const MlpKernel* k) { return k ? k->impl : ""; }
 
 int32_t mlp_dispatch(MlpDevice* d, MlpKernel* k, const void* args, size_t args_size, uint32_t gx, uint32_t gy, uint32_t gz)
 {
     if (!d || !k || !args) return fail(MLP_E_INVALID_ARG, "null argument");
+    if (k->entry == Entry::Module) {
+        // A loaded module's entry point: the packed argument bytes are the kernel's parameter buffer,
+        // block (256,1,1) as [numthreads(256,1,1)] declares (tools/gfx/cuda/cuda-command-queue.cpp:122-147).
+        if (k->ordinal != d->ordinal) return fail(MLP_E_INVALID_ARG, "the kernel was loaded on device %d, not %d", k->ordinal, d->ordinal);
+        if (gx == 0 || gy == 0 || gz == 0) return MLP_OK;
+        CUDA_TRY(cudaSetDevice(d->ordinal));
+        size_t size = args_size;
+        void* extra[] = {CU_LAUNCH_PARAM_BUFFER_POINTER, const_cast<void*>(args), CU_LAUNCH_PARAM_BUFFER_SIZE, &size, CU_LAUNCH_PARAM_END};
+        CUresult r = driver_api().launchKernel(k->function, gx, gy, gz, 256, 1, 1, 0, (CUstream)d->stream, nullptr, extra);
+        if (r != CUDA_SUCCESS) return fail(MLP_E_CUDA, "cuLaunchKernel failed: %s", cu_error(r));
+        d->launches += 1;
+        return MLP_OK;
+    }
     if (gy != 1 || gz != 1) return fail(MLP_E_INVALID_ARG, "the entry points are one-dimensional: grid must be (n,1,1)");
     CUDA_TRY(cudaSetDevice(d->ordinal));
     int launches = 0;
@@ -329,6 +421,7 @@ int32_t mlp_dispatch(MlpDevice* d, MlpKernel* k, const void* args, size_t args_s
         else e = launch_forward_simt(d->stream, k->cfg, a, &launches, &err);
         break;
     }
+    case Entry::Module: break;  // handled above
     }
     d->launches += (uint64_t)launches;
     if (e != cudaSuccess) {

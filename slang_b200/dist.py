@@ -19,12 +19,26 @@ def shard_range(global_count, rank, world):
     return global_count * rank // world, global_count * (rank + 1) // world
 
 
-def allreduce_gradients(grads, loss_words=None, group=None):
+def allreduce_gradients(grads, loss_words=None, group=None, deterministic=False):
     """In-place sum of the flat gradient segment over the ranks; the loss words combine as
-    (max of word 0 as float, sum of word 1 as float).  Tensors live wherever the backend needs them."""
+    (max of word 0 as float, sum of word 1 as float).  Tensors live wherever the backend needs them.
+
+    The order in which a collective library adds the ranks' terms depends on its algorithm (ring, tree,
+    in-switch), so the summed bits can differ from run to run and from N to N.  With
+    deterministic=True every rank gathers all ranks' segments and adds them itself in ascending rank
+    order: the result is the same on every rank and for every library, at N times the traffic (the
+    segment is a few hundred KB at most)."""
     if not dist.is_initialized() or dist.get_world_size(group) == 1:
         return
-    dist.all_reduce(grads, op=dist.ReduceOp.SUM, group=group)
+    if deterministic:
+        world = dist.get_world_size(group)
+        parts = [torch.empty_like(grads) for _ in range(world)]
+        dist.all_gather(parts, grads, group=group)
+        grads.copy_(parts[0])
+        for r in range(1, world):
+            grads.add_(parts[r])
+    else:
+        dist.all_reduce(grads, op=dist.ReduceOp.SUM, group=group)
     if loss_words is not None:
         mx = loss_words[0:1].clone()
         dist.all_reduce(mx, op=dist.ReduceOp.MAX, group=group)

@@ -16,11 +16,14 @@ EXPORTS = [
     "mlp_device_create", "mlp_device_create_on_stream", "mlp_device_destroy", "mlp_wait",
     "mlp_buffer_create", "mlp_buffer_wrap", "mlp_buffer_destroy", "mlp_buffer_address", "mlp_buffer_clear",
     "mlp_buffer_read", "mlp_buffer_write",
-    "mlp_kernel_get", "mlp_kernel_get_for_config", "mlp_kernel_destroy", "mlp_kernel_implementation",
+    "mlp_kernel_get", "mlp_kernel_load", "mlp_kernel_get_for_config", "mlp_kernel_destroy", "mlp_kernel_implementation",
     "mlp_dispatch", "mlp_device_launch_count", "mlp_param_layout", "mlp_last_error_string",
     "mlp_learn_gradient_ordered_noalloc",
     "mlp_layout_sizes", "mlp_layout_to_optimal", "mlp_layout_to_portable",
 ]
+
+# Stand-alone device module with the literal example entry points (built next to the library).
+CUBIN_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "mlp_training_kernels.cubin")
 
 _lib = None
 
@@ -53,6 +56,7 @@ def load():
     L.mlp_buffer_read.argtypes = [vp, vp, sz, sz, vp]
     L.mlp_buffer_write.argtypes = [vp, vp, sz, sz, vp]
     L.mlp_kernel_get.argtypes = [vp, ctypes.c_char_p, pp]
+    L.mlp_kernel_load.argtypes = [vp, ctypes.c_char_p, sz, ctypes.c_char_p, pp]
     L.mlp_kernel_get_for_config.argtypes = [vp, ctypes.POINTER(MlpConfig), ctypes.c_char_p, pp]
     L.mlp_kernel_destroy.argtypes = [vp]
     L.mlp_kernel_implementation.argtypes = [vp]

@@ -21,7 +21,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, out_dir):
+def _worker(rank, world, port, out_dir, deterministic=False):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import torch.distributed as dist
@@ -44,7 +44,7 @@ def _worker(rank, world, port, out_dir):
         oracle.learn_gradient(cfg, params, grads, x[b:e].copy(), t[b:e].copy(), e - b, words)
         g_t = torch.from_numpy(grads)
         w_t = torch.from_numpy(words.view(np.float32))
-        allreduce_gradients(g_t, w_t)
+        allreduce_gradients(g_t, w_t, deterministic=deterministic)
         oracle.adjust_parameters(cfg, states, params, grads)
     np.save(os.path.join(out_dir, "params_%d.npy" % rank), params)
     np.save(os.path.join(out_dir, "loss_%d.npy" % rank), words.view(np.float32))
@@ -66,6 +66,34 @@ def test_two_rank_step_matches_single_process(tmp_path):
     loss = np.load(tmp_path / "loss_0.npy")
     assert abs(loss[0] - l_ref[-1][0]) <= 1e-6 * abs(l_ref[-1][0])
     assert abs(loss[1] / 1000 - l_ref[-1][1]) <= 1e-5 * abs(l_ref[-1][1])
+
+
+def test_deterministic_sum_is_rank_ordered(tmp_path):
+    """deterministic=True: every rank adds the ranks' segments in ascending rank order, so the result is
+    bit-identical to one process that forms the per-shard sums and adds them in that order."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from oracle import oracle
+    from slang_b200 import config as C
+    from slang_b200.dist import shard_range
+    from mlp_testlib import make_problem
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path), True), nprocs=world, join=True)
+    p = [np.load(tmp_path / ("params_%d.npy" % r)) for r in range(world)]
+    assert np.array_equal(p[0].view(np.uint32), p[1].view(np.uint32)), "replicas diverged"
+    cfg, p0, batches = make_problem("c1", 1000, seed=4, steps=3)
+    _, _, total = C.param_layout(cfg)
+    params = p0.copy()
+    states = np.zeros(total, dtype=C.ADAM_STATE_DTYPE)
+    states["master"] = p0
+    for x, t in batches:
+        acc = None
+        for r in range(world):
+            b, e = shard_range(x.shape[0], r, world)
+            g = np.zeros(total, dtype=np.float32)
+            oracle.learn_gradient(cfg, params, g, x[b:e].copy(), t[b:e].copy(), e - b, np.zeros(2, dtype=np.uint32))
+            acc = g if acc is None else acc + g
+        oracle.adjust_parameters(cfg, states, params, acc)
+    assert np.array_equal(p[0].view(np.uint32), params.view(np.uint32))
 
 
 def test_shard_ranges_cover_the_batch():

@@ -144,9 +144,12 @@ def test_adam_guards(device):
     assert np.array_equal(s_gpu["mean"].view(np.uint32), states["mean"].view(np.uint32))
 
 
-def test_example_entry_points_match_oracle(device):
+@pytest.mark.parametrize("via", ["library", "module"])
+def test_example_entry_points_match_oracle(device, via):
     """The literal example (examples/mlp-training/mlp-training.cpp:106-212): srand(1072), parameters
-    uniform in [-1,1] through the host's floatToHalf, 16 samples, learnGradient then adjustParameters."""
+    uniform in [-1,1] through the host's floatToHalf, 16 samples, learnGradient then adjustParameters.
+    "module" loads the stand-alone cubin the way a CUDA host loads a compiled shader module
+    (cuModuleLoadData + one packed parameter buffer per launch)."""
     from slang_b200.api import AdjustParamsParams, LearnGradParams
     libc = ctypes.CDLL("libc.so.6")
     libc.srand(1072)
@@ -178,7 +181,13 @@ def test_example_entry_points_match_oracle(device):
     netb = device.create_buffer(netd.nbytes, netd)
     inb = device.create_buffer(inputs.nbytes, inputs)
     lossb = device.create_buffer(8)
-    k_learn, k_adjust = device.kernel("learnGradient"), device.kernel("adjustParameters")
+    if via == "library":
+        k_learn, k_adjust = device.kernel("learnGradient"), device.kernel("adjustParameters")
+    else:
+        from slang_b200.lib import CUBIN_PATH
+        image = open(CUBIN_PATH, "rb").read()
+        k_learn, k_adjust = device.load_kernel(image, "learnGradient"), device.load_kernel(image, "adjustParameters")
+        assert k_learn.implementation == "module"
     gpu_losses = []
     for k in range(steps):
         lossb.clear()
@@ -195,6 +204,47 @@ def test_example_entry_points_match_oracle(device):
     assert first_loss_mismatch >= 20
     a = got[:192].view(np.float16).astype(np.float32); b = host[:192].view(np.float16).astype(np.float32)
     assert np.max(np.abs(a - b)) <= 2e-2 * np.max(np.abs(b))
+
+
+def test_module_matches_library_bit_for_bit(device):
+    """The cubin and the library hold the same two kernels: a 300-sample, two-block step through either
+    leaves identical bytes."""
+    from slang_b200.api import AdjustParamsParams, LearnGradParams
+    from slang_b200.lib import CUBIN_PATH, MlpError
+    rng = np.random.default_rng(5)
+    init = np.zeros(384, dtype=np.uint16)
+    init[:192] = rng.uniform(-1, 1, 192).astype(np.float16).view(np.uint16)
+    inputs = rng.uniform(0, 1, 600).astype(np.float32)
+    offs = [(0, 128), (192, 320)]
+    image = open(CUBIN_PATH, "rb").read()
+    results = []
+    for via in ("library", "module"):
+        buf = device.create_buffer(init.nbytes, init)
+        states = device.create_buffer(192 * 8)
+        netd = np.array([[buf.address + w, buf.address + 384 + w, buf.address + b, buf.address + 384 + b] for w, b in offs], dtype=np.uint64)
+        netb = device.create_buffer(netd.nbytes, netd)
+        inb = device.create_buffer(inputs.nbytes, inputs)
+        lossb = device.create_buffer(8)
+        if via == "library":
+            kl, ka = device.kernel("learnGradient"), device.kernel("adjustParameters")
+        else:
+            kl, ka = device.load_kernel(image, "learnGradient"), device.load_kernel(image, "adjustParameters")
+        before = device.launch_count
+        for _ in range(3):
+            lossb.clear()
+            kl.dispatch(LearnGradParams(netb.address, lossb.address, inb.address, 300), 2)
+            ka.dispatch(AdjustParamsParams(states.address, buf.address, buf.address + 384, 192), 1)
+        assert device.launch_count - before == 6
+        results.append((buf.read(np.uint16).copy(), states.read(np.uint8).copy(), lossb.read(np.uint32).copy()))
+    # two blocks add their sums with atomics, so the order of the two adds is the only freedom; the
+    # parameters agree to within that (identical when the adds commute, which they do for two terms)
+    assert np.array_equal(results[0][0], results[1][0])
+    assert np.array_equal(results[0][1], results[1][1])
+    assert np.array_equal(results[0][2], results[1][2])
+    with pytest.raises(MlpError):
+        device.load_kernel(image, "noSuchEntryPoint")
+    with pytest.raises(MlpError):
+        device.load_kernel(b"not a device module", "learnGradient")
 
 
 def test_argument_errors(device):

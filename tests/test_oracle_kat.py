@@ -218,3 +218,54 @@ def test_example_half_arithmetic_rounds_every_operation():
     for k in range(4):
         total = h(total + h(d[k] * d[k]))
     assert np.float32(total) == loss[:1].view(np.float32)[0]
+
+
+def test_example_cpu_entry_point_flavours_agree():
+    """The example kernels behind the CPU compute calling convention (docs/cpu-target.md:363-424): the
+    group-range function, the per-group function and the per-thread function, driven in ascending
+    order, leave the same bytes as the plain sequential loop."""
+    rng = np.random.default_rng(11)
+    count = 300   # two groups of 256, the second ragged
+    init = np.zeros(384, dtype=np.uint16)
+    init[:192] = rng.uniform(-1, 1, 192).astype(np.float16).view(np.uint16)
+    inputs = rng.uniform(0, 1, 2 * count).astype(np.float32)
+    offs = [(0, 128), (192, 320)]
+
+    def run(mode):
+        host = init.copy()
+        base = host.ctypes.data
+        net = np.array([[base + w, base + 384 + w, base + b, base + 384 + b] for w, b in offs], dtype=np.uint64)
+        st = np.zeros(192, dtype=C.EXAMPLE_ADAM_STATE_DTYPE)
+        loss = np.zeros(2, dtype=np.uint32)
+        lp = oracle.EntryParams(net.ctypes.data, loss.ctypes.data, inputs.ctypes.data, count)
+        ap = oracle.EntryParams(st.ctypes.data, base, base + 384, 192)
+        for _ in range(2):
+            if mode == "plain":
+                oracle.example_learn_gradient(net, loss, inputs, count)
+                oracle.example_adjust_parameters(st, host[:192], host[192:], 192)
+            elif mode == "range":
+                oracle.cpu_entry_range("learnGradient", lp, 0, 2)
+                oracle.cpu_entry_range("adjustParameters", ap, 0, 1)
+            elif mode == "split":
+                oracle.cpu_entry_range("learnGradient", lp, 0, 1)
+                oracle.cpu_entry_range("learnGradient", lp, 1, 2)
+                oracle.cpu_entry_range("adjustParameters", ap, 0, 1)
+            elif mode == "group":
+                for g in range(2):
+                    oracle.cpu_entry_group("learnGradient", lp, g)
+                oracle.cpu_entry_group("adjustParameters", ap, 0)
+            else:
+                for g in range(2):
+                    for t in range(256):
+                        oracle.cpu_entry_thread("learnGradient", lp, g, t)
+                for t in range(256):
+                    oracle.cpu_entry_thread("adjustParameters", ap, 0, t)
+        return host.copy(), st.copy(), loss.copy()
+
+    ref = run("plain")
+    assert ref[2][0] != 0 and np.any(ref[0][:192] != init[:192])
+    for mode in ("range", "split", "group", "thread"):
+        got = run(mode)
+        assert np.array_equal(got[0], ref[0]), mode
+        assert got[1].tobytes() == ref[1].tobytes(), mode
+        assert np.array_equal(got[2], ref[2]), mode
