@@ -111,6 +111,29 @@ int32_t mlp_buffer_clear(MlpDevice* device, MlpBuffer* buffer, size_t offset, si
 int32_t mlp_buffer_read(MlpDevice* device, const MlpBuffer* buffer, size_t offset, size_t size, void* dst);
 int32_t mlp_buffer_write(MlpDevice* device, MlpBuffer* buffer, size_t offset, size_t size, const void* src);
 
+/* ---- gradient exchange between GPUs ------------------------------------------------------- */
+
+/* The reference example runs on one device; a data-parallel run of the same step (one process per
+ * GPU, each taking a contiguous block of every batch) needs exactly one exchange: the sum of the flat
+ * fp32 gradient segment after learnGradient, before every rank runs the same adjustParameters
+ * (examples/mlp-training/mlp-training.cpp:176-212 is the loop this slots into, between the two
+ * dispatches).  These calls bind NCCL (resolved at run time; MLP_E_NOT_AVAILABLE without it). */
+#define MLP_COMM_ID_BYTES 128
+typedef struct MlpComm MlpComm;
+/* Rank 0 creates the id and hands its bytes to the other ranks by any channel of the host's. */
+int32_t mlp_comm_unique_id(void* id_out, size_t id_bytes);
+/* Collective over the nranks processes; device is the rank's own GPU. */
+int32_t mlp_comm_init(MlpDevice* device, int32_t nranks, int32_t rank, const void* id, size_t id_bytes,
+                      MlpComm** out_comm);
+int32_t mlp_comm_destroy(MlpComm* comm);
+/* Add the ranks' terms in ascending rank order on every rank (all-gather plus a local ordered sum)
+ * instead of an all-reduce: the same bits whatever algorithm the collective library picks. */
+#define MLP_COMM_RANK_ORDERED_SUM 1u
+/* In place, stream ordered on the device's stream: gradients (count floats) become the sum over the
+ * ranks; loss_words (0 to skip) is two floats that combine as (max, sum). */
+int32_t mlp_allreduce_grads(MlpDevice* device, MlpComm* comm, uint64_t gradients, size_t count, uint64_t loss_words,
+                            uint32_t flags);
+
 /* ---- kernels ------------------------------------------------------------------------------ */
 
 /* loadComputeProgram / findEntryPointByName (mlp-training.cpp:291-312): the literal example's entry
@@ -122,7 +145,8 @@ int32_t mlp_kernel_get(MlpDevice* device, const char* entry_point, MlpKernel** o
  * or a module built by nvcc from the CUDA source the reference compiler emits for kernels.slang.
  * mlp_dispatch on such a kernel passes the argument bytes unchanged as the kernel's packed parameter
  * buffer and launches block (256,1,1), grid (gx,gy,gz), as tools/gfx/cuda/cuda-command-queue.cpp:122-147
- * does.  mlp_kernel_implementation reports "module". */
+ * does; trailing struct padding beyond the entry point's last parameter is dropped (the pitfall
+ * tests/cuda/cuda-kernel-param-layout.slang:1-8 describes).  mlp_kernel_implementation reports "module". */
 int32_t mlp_kernel_load(MlpDevice* device, const void* image, size_t image_size, const char* entry_point,
                         MlpKernel** out_kernel);
 /* The same entry points specialised for a problem description, the way the reference specialises

@@ -135,6 +135,37 @@ def groups_for(count):
     return (count + 255) // 256
 
 
+COMM_ID_BYTES = 128
+COMM_RANK_ORDERED_SUM = 1
+
+
+def comm_unique_id():
+    """128 bytes that rank 0 creates and hands to the other ranks (file, socket, store ...)."""
+    buf = ctypes.create_string_buffer(COMM_ID_BYTES)
+    check(load().mlp_comm_unique_id(buf, COMM_ID_BYTES))
+    return buf.raw
+
+
+class Comm:
+    """The gradient exchange of a data-parallel run, one object per rank (mlp_comm_*)."""
+
+    def __init__(self, device, nranks, rank, unique_id):
+        assert len(unique_id) == COMM_ID_BYTES
+        h = ctypes.c_void_p()
+        check(load().mlp_comm_init(device.handle, nranks, rank, unique_id, COMM_ID_BYTES, ctypes.byref(h)))
+        self.device, self.handle, self.nranks, self.rank = device, h, nranks, rank
+
+    def allreduce_grads(self, trainer, with_loss=True, rank_ordered=False):
+        check(load().mlp_allreduce_grads(self.device.handle, self.handle, trainer.grads.address, trainer.total,
+                                         trainer.loss.address if with_loss else 0,
+                                         COMM_RANK_ORDERED_SUM if rank_ordered else 0))
+
+    def destroy(self):
+        if self.handle:
+            load().mlp_comm_destroy(self.handle)
+            self.handle = None
+
+
 class Trainer:
     """The example's host program for an arbitrary MlpConfig.
 

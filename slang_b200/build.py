@@ -33,6 +33,7 @@ UNITS = [
     ("tc_kernels.cu", []),
     ("tc_forward.cu", []),
     ("tc_train_narrow.cu", []),
+    ("comm.cu", []),
 ]
 
 
@@ -74,7 +75,7 @@ def build(force=False, verbose=False):
             print(" ".join(cmd), flush=True)
         subprocess.check_call(cmd)
     if rebuilt or not os.path.exists(OUT):
-        cmd = [nvcc] + ARCH + ["-shared", "-cudart", "static", "-o", OUT] + objs
+        cmd = [nvcc] + ARCH + ["-shared", "-cudart", "static", "-o", OUT] + objs + ["-ldl"]
         if verbose:
             print(" ".join(cmd), flush=True)
         subprocess.check_call(cmd)

@@ -9,6 +9,7 @@
 #include <cstring>
 #include <string>
 
+#include "abi_internal.h"
 #include "launchers.h"
 #include "mlp_common.cuh"
 
@@ -46,6 +47,7 @@ struct DriverApi {
     CUresult (*launchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream,
                              void**, void**) = nullptr;
     CUresult (*getErrorString)(CUresult, const char**) = nullptr;
+    CUresult (*funcGetParamInfo)(CUfunction, size_t, size_t*, size_t*) = nullptr;  // optional
     bool ok = false;
 };
 
@@ -60,6 +62,7 @@ const DriverApi& driver_api()
         a.ok = get("cuModuleLoadData", (void**)&a.moduleLoadData) && get("cuModuleUnload", (void**)&a.moduleUnload) &&
                get("cuModuleGetFunction", (void**)&a.moduleGetFunction) && get("cuLaunchKernel", (void**)&a.launchKernel) &&
                get("cuGetErrorString", (void**)&a.getErrorString);
+        if (!get("cuFuncGetParamInfo", (void**)&a.funcGetParamInfo)) a.funcGetParamInfo = nullptr;
         return a;
     }();
     return api;
@@ -95,16 +98,6 @@ namespace mlpb200 {
 void set_last_error(const char* text) { g_last_error = text ? text : ""; }
 }  // namespace mlpb200
 
-struct MlpDevice {
-    int ordinal = 0;
-    cudaStream_t stream = nullptr;
-    bool owns_stream = false;
-    uint64_t launches = 0;
-    float* seq_scratch = nullptr;  // per-sample vectors of the sequential-sum mode
-    size_t seq_scratch_floats = 0;
-    TcWorkspace* tc = nullptr;
-};
-
 struct MlpBuffer {
     int ordinal = 0;
     void* ptr = nullptr;
@@ -119,6 +112,7 @@ struct MlpKernel {
     int ordinal = 0;
     CUmodule module = nullptr;     // Entry::Module only
     CUfunction function = nullptr;
+    size_t param_bytes = 0;        // end of the last launch parameter; 0 = unknown
 };
 
 extern "C" {
@@ -324,6 +318,11 @@ int32_t mlp_kernel_load(MlpDevice* d, const void* image, size_t image_size, cons
     k->ordinal = d->ordinal;
     k->module = mod;
     k->function = fn;
+    if (api.funcGetParamInfo) {
+        size_t off = 0, sz = 0;
+        for (size_t i = 0; i < 4096 && api.funcGetParamInfo(fn, i, &off, &sz) == CUDA_SUCCESS; ++i)
+            k->param_bytes = off + sz > k->param_bytes ? off + sz : k->param_bytes;
+    }
     *out_kernel = k;
     return MLP_OK;
 }
@@ -348,7 +347,16 @@ int32_t mlp_dispatch(MlpDevice* d, MlpKernel* k, const void* args, size_t args_s
         if (k->ordinal != d->ordinal) return fail(MLP_E_INVALID_ARG, "the kernel was loaded on device %d, not %d", k->ordinal, d->ordinal);
         if (gx == 0 || gy == 0 || gz == 0) return MLP_OK;
         CUDA_TRY(cudaSetDevice(d->ordinal));
+        // A host struct ends with padding up to its alignment (28 bytes of fields become 32); the launch
+        // wants exactly the bytes up to the end of the last parameter (tests/cuda/cuda-kernel-param-layout.slang:1-8).
         size_t size = args_size;
+        if (k->param_bytes) {
+            if (args_size < k->param_bytes)
+                return fail(MLP_E_INVALID_ARG, "the entry point takes %zu parameter bytes, got %zu", k->param_bytes, args_size);
+            if (args_size - k->param_bytes >= 16)
+                return fail(MLP_E_INVALID_ARG, "the entry point takes %zu parameter bytes, got %zu", k->param_bytes, args_size);
+            size = k->param_bytes;
+        }
         void* extra[] = {CU_LAUNCH_PARAM_BUFFER_POINTER, const_cast<void*>(args), CU_LAUNCH_PARAM_BUFFER_SIZE, &size, CU_LAUNCH_PARAM_END};
         CUresult r = driver_api().launchKernel(k->function, gx, gy, gz, 256, 1, 1, 0, (CUstream)d->stream, nullptr, extra);
         if (r != CUDA_SUCCESS) return fail(MLP_E_CUDA, "cuLaunchKernel failed: %s", cu_error(r));

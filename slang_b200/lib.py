@@ -20,6 +20,7 @@ EXPORTS = [
     "mlp_dispatch", "mlp_device_launch_count", "mlp_param_layout", "mlp_last_error_string",
     "mlp_learn_gradient_ordered_noalloc",
     "mlp_layout_sizes", "mlp_layout_to_optimal", "mlp_layout_to_portable",
+    "mlp_comm_unique_id", "mlp_comm_init", "mlp_comm_destroy", "mlp_allreduce_grads",
 ]
 
 # Stand-alone device module with the literal example entry points (built next to the library).
@@ -56,6 +57,10 @@ def load():
     L.mlp_buffer_read.argtypes = [vp, vp, sz, sz, vp]
     L.mlp_buffer_write.argtypes = [vp, vp, sz, sz, vp]
     L.mlp_kernel_get.argtypes = [vp, ctypes.c_char_p, pp]
+    L.mlp_comm_unique_id.argtypes = [vp, sz]
+    L.mlp_comm_init.argtypes = [vp, i32, i32, vp, sz, pp]
+    L.mlp_comm_destroy.argtypes = [vp]
+    L.mlp_allreduce_grads.argtypes = [vp, vp, u64, sz, u64, u32]
     L.mlp_kernel_load.argtypes = [vp, ctypes.c_char_p, sz, ctypes.c_char_p, pp]
     L.mlp_kernel_get_for_config.argtypes = [vp, ctypes.POINTER(MlpConfig), ctypes.c_char_p, pp]
     L.mlp_kernel_destroy.argtypes = [vp]
