@@ -111,6 +111,34 @@ int32_t mlp_buffer_clear(MlpDevice* device, MlpBuffer* buffer, size_t offset, si
 int32_t mlp_buffer_read(MlpDevice* device, const MlpBuffer* buffer, size_t offset, size_t size, void* dst);
 int32_t mlp_buffer_write(MlpDevice* device, MlpBuffer* buffer, size_t offset, size_t size, const void* src);
 
+/* ---- cooperative-vector matrices ------------------------------------------------------------ */
+
+/* Layouts, numbered like CoopVecMatrixLayout (source/slang/hlsl.meta.slang:32547-32553).  The two optimal
+ * layouts are one documented format here: rows and columns zero-padded to multiples of 16, 16x16 tiles in
+ * row-major tile order, row-major inside a tile. */
+enum MlpMatrixLayout {
+    MLP_MATRIX_ROW_MAJOR = 0,
+    MLP_MATRIX_COLUMN_MAJOR = 1,
+    MLP_MATRIX_INFERENCING_OPTIMAL = 2,
+    MLP_MATRIX_TRAINING_OPTIMAL = 3,
+};
+/* rhi::CooperativeVectorMatrixDesc (mlp-training-coopvec.cpp:205-225); component_type is an MlpDType;
+ * offset is relative to the buffer address given to mlp_matrix_convert; row_col_stride in bytes, 0 = packed. */
+typedef struct MlpMatrixDesc {
+    uint32_t rows, cols;
+    int32_t component_type, layout;
+    uint64_t size, offset, row_col_stride;
+} MlpMatrixDesc;
+/* getCooperativeVectorMatrixSize(rows, cols, type, layout, stride, &size) (mlp-training-coopvec.cpp:305-311).
+ * Needs no device. */
+int32_t mlp_matrix_size(uint32_t rows, uint32_t cols, int32_t component_type, int32_t layout, uint64_t row_col_stride,
+                        uint64_t* out_size);
+/* encoder->convertCooperativeVectorMatrix(dstBuffer, dstDescs, srcBuffer, srcDescs, n)
+ * (mlp-training-coopvec.cpp:226-235): layout and component-type conversion, stream ordered.  Ranges must
+ * not overlap. */
+int32_t mlp_matrix_convert(MlpDevice* device, uint64_t dst_address, const MlpMatrixDesc* dst_descs, uint64_t src_address,
+                           const MlpMatrixDesc* src_descs, uint32_t count);
+
 /* ---- gradient exchange between GPUs ------------------------------------------------------- */
 
 /* The reference example runs on one device; a data-parallel run of the same step (one process per
@@ -137,7 +165,9 @@ int32_t mlp_allreduce_grads(MlpDevice* device, MlpComm* comm, uint64_t gradients
 /* ---- kernels ------------------------------------------------------------------------------ */
 
 /* loadComputeProgram / findEntryPointByName (mlp-training.cpp:291-312): the literal example's entry
- * points "learnGradient" and "adjustParameters" (examples/mlp-training/kernels.slang:8-41). */
+ * points "learnGradient" and "adjustParameters" (examples/mlp-training/kernels.slang:8-41), and
+ * "learnGradient_coopvec", the learnGradient of examples/mlp-training-coopvec/kernels.slang:7-27 (its
+ * adjustParameters is the same kernel). */
 int32_t mlp_kernel_get(MlpDevice* device, const char* entry_point, MlpKernel** out_kernel);
 /* createShaderProgram / createComputePipeline for precompiled device code (mlp-training.cpp:341-377;
  * the CUDA backend loads the module it gets with cuModuleLoadData and looks the entry point up by

@@ -57,3 +57,38 @@ def reference_test_values(n):
     """makePortableValue of the reference's unit test (:149-153)."""
     idx = np.arange(n)
     return (((idx * 37 + 19) % 257) - 128).astype(np.float32) * 0.125
+
+
+# ---- cooperative-vector matrix layouts ------------------------------------------------------------
+ROW_MAJOR, COLUMN_MAJOR, INFERENCING_OPTIMAL, TRAINING_OPTIMAL = 0, 1, 2, 3
+
+
+def matrix_size(rows, cols, elem_size, layout, stride=0):
+    """Bytes a rows x cols matrix takes: packed or strided row-/column-major; the optimal layouts pad both
+    extents to multiples of 16 (16x16 tiles)."""
+    if layout == ROW_MAJOR:
+        return (rows - 1) * stride + cols * elem_size if stride else rows * cols * elem_size
+    if layout == COLUMN_MAJOR:
+        return (cols - 1) * stride + rows * elem_size if stride else rows * cols * elem_size
+    return -(-rows // 16) * 16 * (-(-cols // 16) * 16) * elem_size
+
+
+def matrix_to_bytes(m, np_dtype, layout, stride=0, fill=0):
+    """The bytes of matrix m (2-D float array) in the given layout and element type; bytes that the layout
+    does not define (stride gaps) hold `fill`."""
+    import numpy as np
+    rows, cols = m.shape
+    es = np.dtype(np_dtype).itemsize
+    out = np.full(matrix_size(rows, cols, es, layout, stride), fill, dtype=np.uint8)
+    vals = m.astype(np_dtype)
+    if layout in (ROW_MAJOR, COLUMN_MAJOR):
+        v = vals if layout == ROW_MAJOR else vals.T
+        st = stride if stride else v.shape[1] * es
+        for r in range(v.shape[0]):
+            out[r * st: r * st + v.shape[1] * es] = np.ascontiguousarray(v[r]).view(np.uint8)
+        return out
+    pr, pc = -(-rows // 16) * 16, -(-cols // 16) * 16
+    padded = np.zeros((pr, pc), dtype=np_dtype)
+    padded[:rows, :cols] = vals
+    tiles = padded.reshape(pr // 16, 16, pc // 16, 16).transpose(0, 2, 1, 3)   # [tile row][tile col][r][c]
+    return np.ascontiguousarray(tiles).view(np.uint8).reshape(-1).copy()

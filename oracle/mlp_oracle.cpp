@@ -538,6 +538,52 @@ static void ex_layer_bwd(const MlpLayerPointers& lp, const hf* x, hf* g /*[Out],
     }
 }
 
+// The cooperative-vector flavour of the example (examples/mlp-training-coopvec/fflayer.slang:16-66):
+// matrix-vector sums start from zero and the bias is added afterwards (source/slang/hlsl.meta.slang:
+// 32858-32912 and the bias loop after it); activation max(o, o * 0.001h).
+template <int In, int Out>
+static void cv_layer_sums(const MlpLayerPointers& lp, const hf* x, hf* o)
+{
+    for (int i = 0; i < Out; ++i) {
+        hf r = (hf)0.0f;
+        for (int j = 0; j < In; ++j) r += ld_h(lp.weights, i * In + j) * x[j];
+        o[i] = r + ld_h(lp.biases, i);
+    }
+}
+
+template <int N>
+static void cv_activation(const hf* o, hf* y)
+{
+    for (int i = 0; i < N; ++i) {
+        const hf scaled = o[i] * (hf)0.001f;
+        y[i] = o[i] > scaled ? o[i] : (o[i] < scaled ? scaled : o[i]);
+    }
+}
+
+// Reverse pass of one layer: max's derivative gives the whole gradient to the larger argument and half
+// to each at a tie (source/slang/diff.meta.slang:2268-2273); the second argument is o * 0.001h.  The
+// weight gradient goes to a 16x16 tile (the training-optimal layout of this library for matrices up to
+// 16x16: element (i, j) at i * 16 + j) by plain load-add-store (hlsl.meta.slang:33261-33315), the bias
+// gradient to its row-major slot (hlsl.meta.slang:33344-33351), dx = W^T g from zero.
+template <int In, int Out>
+static void cv_layer_bwd(const MlpLayerPointers& lp, const hf* x, const hf* o, hf* g, hf* dx)
+{
+    for (int i = 0; i < Out; ++i) {
+        const hf scaled = o[i] * (hf)0.001f;
+        if (o[i] > scaled) { /* first argument takes it all */ }
+        else if (o[i] < scaled) g[i] = g[i] * (hf)0.001f;
+        else { const hf h = (hf)0.5f * g[i]; g[i] = h + h * (hf)0.001f; }
+    }
+    for (int i = 0; i < Out; ++i)
+        for (int j = 0; j < In; ++j) add_h(lp.weightsGrad, i * 16 + j, g[i] * x[j]);
+    for (int i = 0; i < Out; ++i) add_h(lp.biasesGrad, i, g[i]);
+    for (int i = 0; i < In; ++i) {
+        hf r = (hf)0.0f;
+        for (int j = 0; j < Out; ++j) r += ld_h(lp.weights, j * In + i) * g[j];
+        dx[i] = r;
+    }
+}
+
 static void ex_groundtruth(hf x, hf y, hf* gt)
 {
     gt[0] = (x + y) / ((hf)1.0f + y * y);
@@ -577,6 +623,33 @@ int mlp_oracle_example_learn_gradient(const MlpLayerPointers* network, uint32_t*
                                       uint32_t count)
 {
     for (uint32_t tid = 0; tid < count; ++tid) ex_learn_thread(tid, network, loss_word, inputs, count);
+    return 0;
+}
+
+// learnGradient of the cooperative-vector example (examples/mlp-training-coopvec/kernels.slang:7-27).
+int mlp_oracle_example_coopvec_learn_gradient(const MlpLayerPointers* network, uint32_t* loss_word, const float* inputs,
+                                              uint32_t count)
+{
+    for (uint32_t tid = 0; tid < count; ++tid) {
+        hf x = (hf)inputs[2 * tid], y = (hf)inputs[2 * tid + 1];
+        hf enc[4] = {x, y, x * x, y * y};
+        hf o1[16], h1[16], o2[4], out[4], gt[4], diff[4];
+        cv_layer_sums<4, 16>(network[0], enc, o1);
+        cv_activation<16>(o1, h1);
+        cv_layer_sums<16, 4>(network[1], h1, o2);
+        cv_activation<4>(o2, out);
+        ex_groundtruth(x, y, gt);
+        for (int k = 0; k < 4; ++k) diff[k] = out[k] - gt[k];
+        hf g2[4];
+        for (int k = 0; k < 4; ++k) g2[k] = diff[k] * (hf)1.0f + diff[k] * (hf)1.0f;
+        hf g1[16], dead[4];
+        cv_layer_bwd<16, 4>(network[1], h1, o2, g2, g1);
+        cv_layer_bwd<4, 16>(network[0], enc, o1, g1, dead);
+        hf l = (hf)0.0f;
+        for (int k = 0; k < 4; ++k) l += diff[k] * diff[k];
+        uint32_t bits = f2u((float)l);
+        if (bits > *loss_word) *loss_word = bits;
+    }
     return 0;
 }
 

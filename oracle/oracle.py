@@ -132,3 +132,9 @@ def cpu_entry_group(name, params, group):
 def cpu_entry_thread(name, params, group, thread):
     v = ComputeThreadVaryingInput(_Uint3(group, 0, 0), _Uint3(thread, 0, 0))
     getattr(lib(), name + "_Thread")(ctypes.byref(v), ctypes.byref(params), None)
+
+
+def example_coopvec_learn_gradient(network_ptrs, loss_word, inputs, count):
+    """The cooperative-vector example's learnGradient; weightsGrad points at 16x16 training-optimal tiles."""
+    rc = lib().mlp_oracle_example_coopvec_learn_gradient(_p(network_ptrs), _p(loss_word), _p(inputs), ctypes.c_uint32(count))
+    assert rc == 0

@@ -111,6 +111,14 @@ class Device:
             check(load().mlp_kernel_get_for_config(self.handle, ctypes.byref(cfg), entry_point.encode(), ctypes.byref(h)))
         return Kernel(self, h)
 
+    def matrix_convert(self, dst_address, dst_descs, src_address, src_descs):
+        """convertCooperativeVectorMatrix: lists of MatrixDesc of equal length."""
+        n = len(dst_descs)
+        assert n == len(src_descs)
+        d = (MatrixDesc * n)(*dst_descs)
+        s_ = (MatrixDesc * n)(*src_descs)
+        check(load().mlp_matrix_convert(self.handle, dst_address, d, src_address, s_, n))
+
     def load_kernel(self, image, entry_point):
         """A kernel from a caller-supplied device module (cubin or PTX bytes); dispatch passes the argument
         bytes as the packed parameter buffer, block (256,1,1)."""
@@ -133,6 +141,22 @@ class Device:
 
 def groups_for(count):
     return (count + 255) // 256
+
+
+MATRIX_ROW_MAJOR, MATRIX_COLUMN_MAJOR, MATRIX_INFERENCING_OPTIMAL, MATRIX_TRAINING_OPTIMAL = 0, 1, 2, 3
+
+
+class MatrixDesc(ctypes.Structure):
+    """MlpMatrixDesc: one matrix inside a buffer (component_type is an MlpDType)."""
+    _fields_ = [("rows", ctypes.c_uint32), ("cols", ctypes.c_uint32), ("component_type", ctypes.c_int32),
+                ("layout", ctypes.c_int32), ("size", ctypes.c_uint64), ("offset", ctypes.c_uint64),
+                ("row_col_stride", ctypes.c_uint64)]
+
+
+def matrix_size(rows, cols, component_type, layout, stride=0):
+    out = ctypes.c_uint64()
+    check(load().mlp_matrix_size(rows, cols, component_type, layout, stride, ctypes.byref(out)))
+    return int(out.value)
 
 
 COMM_ID_BYTES = 128

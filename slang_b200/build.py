@@ -34,6 +34,7 @@ UNITS = [
     ("tc_forward.cu", []),
     ("tc_train_narrow.cu", []),
     ("comm.cu", []),
+    ("matrix_convert.cu", []),
 ]
 
 

@@ -36,7 +36,7 @@ int32_t fail(int32_t code, const char* fmt, ...)
         if (e_ != cudaSuccess) return fail(MLP_E_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e_)); \
     } while (0)
 
-enum class Entry { ExampleLearn, ExampleAdjust, Learn, LearnSimt, Adjust, Forward, ForwardSimt, Module };
+enum class Entry { ExampleLearn, ExampleLearnCoopVec, ExampleAdjust, Learn, LearnSimt, Adjust, Forward, ForwardSimt, Module };
 
 // Driver entry points for caller-supplied device modules, resolved through the runtime so that the
 // library carries no link-time dependency on the driver library.
@@ -261,6 +261,7 @@ int32_t mlp_kernel_get(MlpDevice* d, const char* entry_point, MlpKernel** out_ke
     std::memset(&k->cfg, 0, sizeof k->cfg);
     k->impl = "simt";
     if (!std::strcmp(entry_point, "learnGradient")) k->entry = Entry::ExampleLearn;
+    else if (!std::strcmp(entry_point, "learnGradient_coopvec")) k->entry = Entry::ExampleLearnCoopVec;
     else if (!std::strcmp(entry_point, "adjustParameters")) k->entry = Entry::ExampleAdjust;
     else { delete k; return fail(MLP_E_NOT_AVAILABLE, "no entry point named '%s'", entry_point); }
     *out_kernel = k;
@@ -369,13 +370,16 @@ int32_t mlp_dispatch(MlpDevice* d, MlpKernel* k, const void* args, size_t args_s
     std::string err;
     cudaError_t e = cudaSuccess;
     switch (k->entry) {
+    case Entry::ExampleLearnCoopVec:
     case Entry::ExampleLearn: {
         // The struct is 28 bytes of fields; hosts pass 28 or the padded 32 (tests/cuda/cuda-kernel-param-layout.slang).
         if (args_size != 28 && args_size != sizeof(MlpLearnGradParams)) return fail(MLP_E_INVALID_ARG, "learnGradient expects 28 or 32 argument bytes, got %zu", args_size);
         MlpLearnGradParams a; std::memset(&a, 0, sizeof a); std::memcpy(&a, args, 28);
         if ((uint64_t)gx * 256 < a.count) return fail(MLP_E_INVALID_ARG, "grid of %u groups does not cover %u samples", gx, a.count);
         if (a.count == 0 || gx == 0) return MLP_OK;
-        e = launch_example_learn_gradient(d->stream, a, gx); launches = 1;
+        e = k->entry == Entry::ExampleLearn ? launch_example_learn_gradient(d->stream, a, gx)
+                                            : launch_example_learn_gradient_coopvec(d->stream, a, gx);
+        launches = 1;
         break;
     }
     case Entry::ExampleAdjust: {
@@ -434,6 +438,33 @@ int32_t mlp_dispatch(MlpDevice* d, MlpKernel* k, const void* args, size_t args_s
     d->launches += (uint64_t)launches;
     if (e != cudaSuccess) {
         if (!err.empty()) return fail(e == cudaErrorInvalidValue ? MLP_E_NOT_AVAILABLE : MLP_E_CUDA, "%s", err.c_str());
+        return fail(MLP_E_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
+    }
+    return MLP_OK;
+}
+
+int32_t mlp_matrix_size(uint32_t rows, uint32_t cols, int32_t component_type, int32_t layout, uint64_t row_col_stride,
+                        uint64_t* out_size)
+{
+    if (!out_size) return fail(MLP_E_INVALID_ARG, "null argument");
+    std::string err;
+    size_t sz = 0;
+    if (!matrix_size(rows, cols, component_type, layout, (size_t)row_col_stride, &sz, &err)) return fail(MLP_E_INVALID_ARG, "%s", err.c_str());
+    *out_size = sz;
+    return MLP_OK;
+}
+
+int32_t mlp_matrix_convert(MlpDevice* d, uint64_t dst_address, const MlpMatrixDesc* dst_descs, uint64_t src_address,
+                           const MlpMatrixDesc* src_descs, uint32_t count)
+{
+    if (!d || !dst_address || !src_address || (count && (!dst_descs || !src_descs))) return fail(MLP_E_INVALID_ARG, "null argument");
+    CUDA_TRY(cudaSetDevice(d->ordinal));
+    std::string err;
+    int launches = 0;
+    cudaError_t e = launch_matrix_convert(d->stream, dst_address, dst_descs, src_address, src_descs, count, &launches, &err);
+    d->launches += (uint64_t)launches;
+    if (e != cudaSuccess) {
+        if (!err.empty()) return fail(MLP_E_INVALID_ARG, "%s", err.c_str());
         return fail(MLP_E_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
     }
     return MLP_OK;

@@ -154,6 +154,134 @@ learnGradient(const MlpLayerPointers* __restrict__ network, uint32_t* lossBuffer
     if ((threadIdx.x & 31) == 0 && first + (int)(threadIdx.x) < (int)count) atomicMax(lossBuffer, __float_as_uint(m));
 }
 
+// ------------------------------------------------------------------------------------------------
+// The cooperative-vector flavour of the same example (examples/mlp-training-coopvec/{kernels,network,
+// fflayer}.slang).  Differences from the software flavour above: a layer's sums start from zero and
+// the bias is added last (the matrix-vector fallback, source/slang/hlsl.meta.slang:32858-32912 and the
+// bias loop that follows it); the activation is max(o, o * 0.001h) and its derivative comes from the
+// derivative of max (1 above, 0.001 below, the mean of both at a tie, source/slang/diff.meta.slang:
+// 2268-2273), applied to the pre-activation sums; the weight gradient is accumulated into a matrix in
+// the training-optimal layout (here: 16x16 tiles, tile-major, row-major inside a tile, zero padded;
+// both of the example's matrices fit one tile, element (i, j) at i * 16 + j), which the host converts
+// to row-major afterwards (mlp-training-coopvec.cpp:201-236); the bias gradient goes straight to the
+// row-major gradient segment (coopVecReduceSumAccumulate, hlsl.meta.slang:33344-33351).
+// ------------------------------------------------------------------------------------------------
+template <int In, int Out>
+__device__ void cv_layer_sums(const MlpLayerPointers& lp, const __half* x, __half* o)
+{
+    const __half* W = (const __half*)lp.weights;
+    const __half* B = (const __half*)lp.biases;
+    for (int i = 0; i < Out; ++i) {
+        __half r = __float2half_rn(0.0f);
+        for (int j = 0; j < In; ++j) r = hadd_(r, hmul_(W[i * In + j], x[j]));
+        o[i] = hadd_(r, B[i]);
+    }
+}
+
+template <int N>
+__device__ void cv_activation(const __half* o, __half* y)
+{
+    const __half slope = __float2half_rn(0.001f);
+    for (int i = 0; i < N; ++i) {
+        const __half scaled = hmul_(o[i], slope);
+        y[i] = __half2float(o[i]) > __half2float(scaled) ? o[i] : (__half2float(o[i]) < __half2float(scaled) ? scaled : o[i]);
+    }
+}
+
+// g <- gradient with respect to the pre-activation sums o; dx = W^T g with sums starting from zero.
+template <int In, int Out>
+__device__ void cv_layer_bwd(const MlpLayerPointers& lp, const __half* o, __half* g, __half* dx)
+{
+    const __half slope = __float2half_rn(0.001f), half_ = __float2half_rn(0.5f);
+    for (int i = 0; i < Out; ++i) {
+        const float a = __half2float(o[i]), b = __half2float(hmul_(o[i], slope));
+        if (a > b) { /* whole gradient to the first argument */ }
+        else if (a < b) g[i] = hmul_(g[i], slope);
+        else { const __half h = hmul_(half_, g[i]); g[i] = hadd_(h, hmul_(h, slope)); }
+    }
+    const __half* W = (const __half*)lp.weights;
+    for (int i = 0; i < In; ++i) {
+        __half r = __float2half_rn(0.0f);
+        for (int j = 0; j < Out; ++j) r = hadd_(r, hmul_(W[j * In + i], g[j]));
+        dx[i] = r;
+    }
+}
+
+// Like ex_accumulate, with the weight gradient in the one-tile training-optimal layout.
+template <int In, int Out>
+__device__ void cv_accumulate(const MlpLayerPointers& lp, const __half* sg, const __half* sx, int n_valid, int gstride,
+                              int xstride)
+{
+    __half* dW = (__half*)lp.weightsGrad;
+    __half* dB = (__half*)lp.biasesGrad;
+    const bool single = gridDim.x == 1;
+    for (int p = threadIdx.x; p < In * Out + Out; p += blockDim.x) {
+        const bool is_w = p < In * Out;
+        const int i = is_w ? p / In : p - In * Out, j = is_w ? p % In : 0;
+        __half* dst = is_w ? dW + i * 16 + j : dB + i;
+        __half acc = single ? *dst : __float2half_rn(0.0f);
+        bool first = !single;
+        for (int s = 0; s < n_valid; ++s) {
+            const __half term = is_w ? hmul_(sg[s * gstride + i], sx[s * xstride + j]) : sg[s * gstride + i];
+            acc = first ? term : hadd_(acc, term);
+            first = false;
+        }
+        if (single) *dst = acc;
+        else if (n_valid > 0) atomic_add_half(dst, acc);
+    }
+}
+
+extern "C" __global__ void __launch_bounds__(256)
+learnGradient_coopvec(const MlpLayerPointers* __restrict__ network, uint32_t* lossBuffer,
+                      const float2* __restrict__ inputs, uint32_t count)
+{
+    __shared__ __half s_enc[256 * 4];
+    __shared__ __half s_h1[256 * 16];
+    __shared__ __half s_g2[256 * 4];
+    __shared__ __half s_g1[256 * 16];
+
+    const uint32_t tid = blockIdx.x * blockDim.x + threadIdx.x;
+    const bool valid = tid < count;
+    const MlpLayerPointers L1 = network[0], L2 = network[1];
+    float this_loss = 0.0f;
+    if (valid) {
+        const float2 in = inputs[tid];
+        const __half x = __float2half_rn(in.x), y = __float2half_rn(in.y);
+        __half enc[4] = {x, y, hmul_(x, x), hmul_(y, y)};
+        __half o1[16], h1[16], o2[4], out[4], g2[4], g1[16], dead[4];
+        cv_layer_sums<4, 16>(L1, enc, o1);
+        cv_activation<16>(o1, h1);
+        cv_layer_sums<16, 4>(L2, h1, o2);
+        cv_activation<4>(o2, out);
+        const __half one = __float2half_rn(1.0f), half_ = __float2half_rn(0.5f);
+        __half gt[4];
+        gt[0] = hdiv_(hadd_(x, y), hadd_(one, hmul_(y, y)));
+        gt[1] = hadd_(hmul_(__float2half_rn(2.0f), x), y);
+        gt[2] = hadd_(hmul_(hmul_(half_, x), x), hmul_(__float2half_rn(1.2f), y));
+        gt[3] = hadd_(x, hmul_(hmul_(half_, y), y));
+        __half l = __float2half_rn(0.0f);
+        for (int k = 0; k < 4; ++k) {
+            const __half d = hsub_(out[k], gt[k]);
+            g2[k] = hadd_(hmul_(d, one), hmul_(d, one));
+            l = hadd_(l, hmul_(d, d));
+        }
+        this_loss = __half2float(l);
+        cv_layer_bwd<16, 4>(L2, o2, g2, g1);
+        cv_layer_bwd<4, 16>(L1, o1, g1, dead);
+        for (int k = 0; k < 4; ++k) { s_enc[threadIdx.x * 4 + k] = enc[k]; s_g2[threadIdx.x * 4 + k] = g2[k]; }
+        for (int k = 0; k < 16; ++k) { s_h1[threadIdx.x * 16 + k] = h1[k]; s_g1[threadIdx.x * 16 + k] = g1[k]; }
+    }
+    __syncthreads();
+    const int first = blockIdx.x * blockDim.x;
+    const int n_valid = count > (uint32_t)first ? min((int)blockDim.x, (int)(count - first)) : 0;
+    cv_accumulate<16, 4>(L2, s_g2, s_h1, n_valid, 4, 16);
+    cv_accumulate<4, 16>(L1, s_g1, s_enc, n_valid, 16, 4);
+
+    float m = this_loss;
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((threadIdx.x & 31) == 0 && first + (int)(threadIdx.x) < (int)count) atomicMax(lossBuffer, __float_as_uint(m));
+}
+
 extern "C" __global__ void __launch_bounds__(256)
 adjustParameters(MlpExampleAdamState* states, __half* params, __half* gradients, uint32_t count)
 {

@@ -11,6 +11,7 @@ namespace mlpb200 {
 
 // One-thread-per-sample kernels (simt_kernels.cu).
 cudaError_t launch_example_learn_gradient(cudaStream_t st, const MlpLearnGradParams& a, uint32_t grid);
+cudaError_t launch_example_learn_gradient_coopvec(cudaStream_t st, const MlpLearnGradParams& a, uint32_t grid);
 cudaError_t launch_example_adjust_parameters(cudaStream_t st, const MlpAdjustParamsParams& a, uint32_t grid);
 cudaError_t launch_forward_simt(cudaStream_t st, const MlpConfig& c, const MlpForwardParams& a, int* launches,
                                 std::string* err);
@@ -23,6 +24,12 @@ cudaError_t launch_adjust_parameters(cudaStream_t st, const MlpConfig& c, const 
 bool layout_sizes(const MlpNetworkShape& n, long long* logical, long long* physical, std::string* err);
 cudaError_t launch_layout_convert(cudaStream_t st, const MlpNetworkShape& n, bool to_optimal, const void* src, void* dst,
                                   int* launches, std::string* err);
+
+// Matrix layout conversion of the cooperative-vector host calls (matrix_convert.cu).
+bool matrix_size(uint32_t rows, uint32_t cols, int32_t component_type, int32_t layout, size_t stride, size_t* size,
+                 std::string* err);
+cudaError_t launch_matrix_convert(cudaStream_t st, uint64_t dst_base, const MlpMatrixDesc* dst, uint64_t src_base,
+                                  const MlpMatrixDesc* src, uint32_t n, int* launches, std::string* err);
 
 // Tensor-core kernels (tc_kernels.cu).  tc_supported() says whether the shape is one they are built for.
 bool tc_forward_supported(const MlpConfig& c);

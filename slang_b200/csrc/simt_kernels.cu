@@ -269,6 +269,13 @@ cudaError_t launch_example_learn_gradient(cudaStream_t st, const MlpLearnGradPar
     return cudaGetLastError();
 }
 
+cudaError_t launch_example_learn_gradient_coopvec(cudaStream_t st, const MlpLearnGradParams& a, uint32_t grid)
+{
+    learnGradient_coopvec<<<grid, 256, 0, st>>>((const MlpLayerPointers*)a.networkBuffer, (uint32_t*)a.lossBuffer,
+                                                (const float2*)a.inputs, a.count);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_example_adjust_parameters(cudaStream_t st, const MlpAdjustParamsParams& a, uint32_t grid)
 {
     adjustParameters<<<grid, 256, 0, st>>>((MlpExampleAdamState*)a.adamStates, (__half*)a.params, (__half*)a.gradients,

@@ -20,6 +20,7 @@ EXPORTS = [
     "mlp_dispatch", "mlp_device_launch_count", "mlp_param_layout", "mlp_last_error_string",
     "mlp_learn_gradient_ordered_noalloc",
     "mlp_layout_sizes", "mlp_layout_to_optimal", "mlp_layout_to_portable",
+    "mlp_matrix_size", "mlp_matrix_convert",
     "mlp_comm_unique_id", "mlp_comm_init", "mlp_comm_destroy", "mlp_allreduce_grads",
 ]
 
@@ -57,6 +58,8 @@ def load():
     L.mlp_buffer_read.argtypes = [vp, vp, sz, sz, vp]
     L.mlp_buffer_write.argtypes = [vp, vp, sz, sz, vp]
     L.mlp_kernel_get.argtypes = [vp, ctypes.c_char_p, pp]
+    L.mlp_matrix_size.argtypes = [u32, u32, i32, i32, u64, ctypes.POINTER(u64)]
+    L.mlp_matrix_convert.argtypes = [vp, u64, vp, u64, vp, u32]
     L.mlp_comm_unique_id.argtypes = [vp, sz]
     L.mlp_comm_init.argtypes = [vp, i32, i32, vp, sz, pp]
     L.mlp_comm_destroy.argtypes = [vp]
