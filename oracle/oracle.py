@@ -15,8 +15,8 @@ _LIB = None
 
 def build(force=False):
     so = os.path.join(_HERE, "libmlp_oracle.so")
-    src = os.path.join(_HERE, "mlp_oracle.cpp")
-    if force or not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(src):
+    srcs = [os.path.join(_HERE, f) for f in ("mlp_oracle.cpp", "permuto_oracle.cpp")]
+    if force or not os.path.exists(so) or os.path.getmtime(so) < max(os.path.getmtime(f) for f in srcs):
         subprocess.check_call(["make", "-C", _HERE, "-s", "-B" if force else "-s"])
     return so
 

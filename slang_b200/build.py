@@ -35,6 +35,7 @@ UNITS = [
     ("tc_train_narrow.cu", []),
     ("comm.cu", []),
     ("matrix_convert.cu", []),
+    ("permuto.cu", ["-fmad=false"]),
 ]
 
 

@@ -21,6 +21,7 @@ EXPORTS = [
     "mlp_learn_gradient_ordered_noalloc",
     "mlp_layout_sizes", "mlp_layout_to_optimal", "mlp_layout_to_portable",
     "mlp_matrix_size", "mlp_matrix_convert",
+    "mlp_permuto_prepare", "mlp_grid_hash", "mlp_permuto_encode", "mlp_permuto_backward",
     "mlp_comm_unique_id", "mlp_comm_init", "mlp_comm_destroy", "mlp_allreduce_grads",
 ]
 
@@ -58,6 +59,12 @@ def load():
     L.mlp_buffer_read.argtypes = [vp, vp, sz, sz, vp]
     L.mlp_buffer_write.argtypes = [vp, vp, sz, sz, vp]
     L.mlp_kernel_get.argtypes = [vp, ctypes.c_char_p, pp]
+    f32 = ctypes.c_float
+    L.mlp_permuto_prepare.argtypes = [i32, i32, i32, i32, f32, f32, f32, u32, i32, vp]
+    L.mlp_grid_hash.argtypes = [i32, i32, vp]
+    L.mlp_grid_hash.restype = u32
+    L.mlp_permuto_encode.argtypes = [vp, vp, u64, u64, u64, u32]
+    L.mlp_permuto_backward.argtypes = [vp, vp, u64, u64, u64, u64, u64, u32]
     L.mlp_matrix_size.argtypes = [u32, u32, i32, i32, u64, ctypes.POINTER(u64)]
     L.mlp_matrix_convert.argtypes = [vp, u64, vp, u64, vp, u32]
     L.mlp_comm_unique_id.argtypes = [vp, sz]

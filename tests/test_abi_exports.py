@@ -14,7 +14,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def test_header_symbols_are_exported():
-    text = open(os.path.join(ROOT, "include", "slang_b200_mlp.h")).read()
+    inc = os.path.join(ROOT, "include")
+    text = "".join(open(os.path.join(inc, f)).read() for f in sorted(os.listdir(inc)) if f.endswith(".h"))
     declared = set(re.findall(r"\b(mlp_[a-z_]+)\s*\(", text))
     assert declared, "no declarations found"
     L = lib.load()
