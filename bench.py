@@ -302,6 +302,88 @@ def bench_narrow(args):
     device.destroy()
 
 
+def bench_permuto(args):
+    """Permutohedral encoder: 3-D positions, 16 levels of 2^19 entries, 2 features per entry (fp32 or fp16
+    tables).  Reports encode and reverse-pass rates; the roofline is HBM against the bytes that must cross
+    it when the table stays in L2 (positions in, feature rows out / upstream rows in)."""
+    import ctypes
+    import torch
+    from oracle import permuto as OP
+    from slang_b200 import config as C
+    from slang_b200 import permuto as P
+    from slang_b200.api import Device
+    torch.cuda.set_device(0)
+    dev_t = torch.device("cuda", 0)
+    stream = torch.cuda.Stream(device=dev_t)
+    torch.cuda.set_stream(stream)
+    device = Device(0, stream.cuda_stream)
+    half = args.config.endswith("f16")
+    dims, feats, log2, levels = 3, 2, 19, 16
+    cfg = P.prepare(dims, feats, log2, levels, 16.0, 0.5, 1.1, 1337, C.F16 if half else C.F32)
+    tdt = torch.float16 if half else torch.float32
+    es = 2 if half else 4
+    count = args.batch if args.batch != (1 << 26) else 1 << 22
+    gen = torch.Generator(device=dev_t); gen.manual_seed(5)
+    pos = torch.rand((count, dims), device=dev_t, generator=gen)
+    table = (torch.rand(cfg.table_values, device=dev_t, generator=gen) * 2e-4 - 1e-4).to(tdt)
+    out = torch.empty((count, cfg.n_features), dtype=tdt, device=dev_t)
+    g = torch.full((count, cfg.n_features), 1.0 / 64, dtype=tdt, device=dev_t)
+    dtable = torch.zeros(cfg.table_values, dtype=tdt, device=dev_t)
+    dpos = torch.empty((count, dims), device=dev_t)
+    enc = P.PermutoEncoder(device, cfg)
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev_t)
+
+    def fwd():
+        enc.encode(pos.data_ptr(), table.data_ptr(), out.data_ptr(), count)
+
+    def bwd():
+        enc.backward(pos.data_ptr(), table.data_ptr(), g.data_ptr(), dtable.data_ptr(), dpos.data_ptr(), count)
+
+    for _ in range(args.warmup):
+        fwd(); bwd()
+    torch.cuda.synchronize()
+    # parity spot check against the oracle on the first 4096 positions (checker only, outside the timing)
+    want = OP.encode(cfg, pos[:4096].cpu().numpy(), table.cpu().numpy())
+    assert np.array_equal(out[:4096].cpu().numpy(), want), "encode differs from the oracle"
+    tf, tb = [], []
+    launches0 = device.launch_count
+    for _ in range(args.steps):
+        flush.zero_()
+        e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        e0.record(); fwd(); e1.record(); bwd(); e2.record()
+        torch.cuda.synchronize()
+        tf.append(e0.elapsed_time(e1)); tb.append(e1.elapsed_time(e2))
+    launches = device.launch_count - launches0
+    mf, mb = float(np.mean(tf)), float(np.mean(tb))
+    peaks = measured_peaks()
+    bytes_f = count * (dims * 4 + cfg.n_features * es)
+    bytes_b = count * (dims * 4 + cfg.n_features * es + dims * 4)
+    gathered = count * levels * (dims + 1) * feats * es
+    line = {"metric": "permuto encoder positions/sec (encode + reverse)", "value": count / ((mf + mb) * 1e-3), "unit": "positions/s",
+            "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": mf + mb, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f16" if half else "f32", "data": "synthetic",
+            "config": {"workload": "permutohedral encoder, 3-D, 16 levels x 2^19 entries x 2 features, %s tables" % ("fp16" if half else "fp32"),
+                       "positions": count, "l2": "512 MB written between timed steps"},
+            "gpu_launches": launches,
+            "encode": {"ms": mf, "positions_per_s": count / (mf * 1e-3), "gathered_gbs": gathered / (mf * 1e-3) / 1e9},
+            "reverse": {"ms": mb, "positions_per_s": count / (mb * 1e-3), "scattered_gbs": gathered / (mb * 1e-3) / 1e9},
+            "roofline": {"bound": "hbm", "achieved": bytes_f / (mf * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": bytes_f / (mf * 1e-3) / 1e9 / peaks["hbm_gbs"], "traffic": None, "kernel": "permuto_encode_kernel",
+                         "reverse_achieved": bytes_b / (mb * 1e-3) / 1e9, "reverse_frac": bytes_b / (mb * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                         "peak_source": peaks["source"]}}
+    n_cpu = 1 << 16
+    p_h, t_h = pos[:n_cpu].cpu().numpy(), table.cpu().numpy()
+    g_h = g[:n_cpu].cpu().numpy()
+    t0 = time.perf_counter()
+    OP.encode(cfg, p_h, t_h)
+    OP.backward(cfg, p_h, t_h, g_h, np.zeros_like(t_h))
+    dt = time.perf_counter() - t0
+    line["cpu_baseline"] = {"value": n_cpu / dt, "unit": "positions/s", "cores": 1, "kind": "port",
+                            "sample": "%d positions, encode + reverse once, %.2f s" % (n_cpu, dt)}
+    print(json.dumps(line), flush=True)
+    device.destroy()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -327,6 +409,10 @@ def main():
     if args.config in ("c2", "c3"):
         if rank == 0:
             bench_narrow(args)
+        return
+    if args.config.startswith("permuto"):
+        if rank == 0:
+            bench_permuto(args)
         return
     if args.config == "c5_sweep" or args.config.startswith("c5_w"):
         if rank == 0:

@@ -209,7 +209,21 @@ __device__ inline uint32_t vertex_index(const Simplex<D>& s, int k, const MlpPer
         key[dim] = uint32_t(s.rem0[dim] + k);
         if (s.rank[dim] > D - k) key[dim] -= uint32_t(D + 1);
     }
-    return li.table_offset * uint32_t(F) + (base_convert_hash<D>(key) % li.table_size) * uint32_t(F);
+    const uint32_t h = base_convert_hash<D>(key);
+    // x % 2^k == x & (2^k - 1); the general remainder only for tables that are not a power of two
+    const uint32_t slot = (li.table_size & (li.table_size - 1)) == 0 ? (h & (li.table_size - 1)) : (h % li.table_size);
+    return (li.table_offset + slot) * uint32_t(F);
+}
+
+// The threads of a warp work on different levels, so the level constants are read from shared memory
+// (a kernel parameter indexed per lane would be fetched once per distinct level).
+__device__ inline void stage_levels(const MlpPermutoConfig& c, MlpPermutoLevelInfo* s_levels)
+{
+    constexpr int kWords = sizeof(MlpPermutoLevelInfo) / 4;
+    const uint32_t* src = reinterpret_cast<const uint32_t*>(c.levels);
+    uint32_t* dst = reinterpret_cast<uint32_t*>(s_levels);
+    for (int i = threadIdx.x; i < c.n_levels * kWords; i += blockDim.x) dst[i] = src[i];
+    __syncthreads();
 }
 
 __device__ inline bool level_live(const MlpPermutoConfig& c, const MlpPermutoLevelInfo& li)
@@ -217,17 +231,21 @@ __device__ inline bool level_live(const MlpPermutoConfig& c, const MlpPermutoLev
     return !(float(li.level_index) >= c.max_level + 1e-3f);
 }
 
+// Block of 256 threads = floor(256 / L) positions x L levels, levels fastest: the level threads of a
+// position write one contiguous output row.
 template <int D, int F, typename T>
 __global__ void __launch_bounds__(256)
 permuto_encode_kernel(const __grid_constant__ MlpPermutoConfig c, const float* __restrict__ positions,
                       const T* __restrict__ table, T* __restrict__ out, uint32_t count)
 {
+    __shared__ MlpPermutoLevelInfo s_levels[MLP_PERMUTO_MAX_LEVELS];
+    stage_levels(c, s_levels);
     const uint32_t L = uint32_t(c.n_levels);
-    const uint64_t gid = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
-    const uint64_t n = gid / L;
-    const uint32_t l = uint32_t(gid % L);
-    if (n >= count) return;
-    const MlpPermutoLevelInfo& li = c.levels[l];
+    const uint32_t per_block = 256u / L;
+    const uint32_t local = threadIdx.x / L, l = threadIdx.x - local * L;
+    const uint64_t n = uint64_t(blockIdx.x) * per_block + local;
+    if (local >= per_block || n >= count) return;
+    const MlpPermutoLevelInfo& li = s_levels[l];
     T acc[F];
 #pragma unroll
     for (int f = 0; f < F; ++f) acc[f] = Elem<T>::from(0.0f);
@@ -262,16 +280,18 @@ permuto_backward_kernel(const __grid_constant__ MlpPermutoConfig c, const float*
                         float* __restrict__ d_positions, uint32_t count)
 {
     __shared__ float s_dpos[256 * D];
+    __shared__ MlpPermutoLevelInfo s_levels[MLP_PERMUTO_MAX_LEVELS];
+    stage_levels(c, s_levels);
     const uint32_t L = uint32_t(c.n_levels);
     const uint32_t per_block = 256u / L;
-    const uint32_t local = threadIdx.x / L, l = threadIdx.x % L;
+    const uint32_t local = threadIdx.x / L, l = threadIdx.x - local * L;
     const uint64_t n = uint64_t(blockIdx.x) * per_block + local;
     const bool active = local < per_block && n < count;
     float dpos[D];
 #pragma unroll
     for (int d = 0; d < D; ++d) dpos[d] = 0.0f;
     if (active) {
-        const MlpPermutoLevelInfo& li = c.levels[l];
+        const MlpPermutoLevelInfo& li = s_levels[l];
         if (level_live(c, li)) {
             float pos[D];
 #pragma unroll
@@ -357,12 +377,11 @@ cudaError_t run(bool backward, cudaStream_t st, const MlpPermutoConfig& c, uint6
                 uint64_t d_table, uint64_t d_positions, uint32_t count)
 {
     const uint32_t L = uint32_t(c.n_levels);
+    const uint32_t per_block = 256u / L;
     if (!backward) {
-        const uint64_t threads = uint64_t(count) * L;
-        permuto_encode_kernel<D, F, T><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(
+        permuto_encode_kernel<D, F, T><<<(unsigned)((count + per_block - 1) / per_block), 256, 0, st>>>(
             c, (const float*)positions, (const T*)table, (T*)out, count);
     } else {
-        const uint32_t per_block = 256u / L;
         permuto_backward_kernel<D, F, T><<<(unsigned)((count + per_block - 1) / per_block), 256, 0, st>>>(
             c, (const float*)positions, (const T*)table, (const T*)out, (T*)d_table, (float*)d_positions, count);
     }
