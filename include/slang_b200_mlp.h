@@ -68,6 +68,16 @@ typedef struct MlpLearnGradParamsEx {
     uint32_t flags; /* MLP_FLAG_* */
 } MlpLearnGradParamsEx;
 
+/* MlpLearnGradParamsEx plus a destination for the gradient with respect to the inputs (fp32
+ * [count][dims[0]], values rounded to the network's storage type), written when flags has
+ * MLP_FLAG_INPUT_GRADIENT.  The example marks its inputs no_diff (examples/mlp-training/network.slang:36-43),
+ * so this has no counterpart there; the neural module's layers do return it (FFLayer's reverse pass,
+ * source/standard-modules/neural/layers.slang:34-110) and a trainable input encoder needs it. */
+typedef struct MlpLearnGradParamsEx2 {
+    MlpLearnGradParamsEx base;
+    uint64_t inputGradients;
+} MlpLearnGradParamsEx2;
+
 /* forward only: outputs are fp32 [count][dims[n_layers]], or the network's storage type with
  * MLP_FLAG_OUTPUT_STORAGE_TYPE (for feeding another network's targets). */
 typedef struct MlpForwardParams {
@@ -83,6 +93,9 @@ typedef struct MlpForwardParams {
 #define MLP_FLAG_SEQUENTIAL_SUM 1u
 /* forward: write the outputs rounded to the network's storage type (tensor-core path only). */
 #define MLP_FLAG_OUTPUT_STORAGE_TYPE 2u
+/* learnGradient with MlpLearnGradParamsEx2: also write the input gradients (one thread per sample path;
+ * networks without an input encoding). */
+#define MLP_FLAG_INPUT_GRADIENT 4u
 
 /* ---- device ------------------------------------------------------------------------------- */
 

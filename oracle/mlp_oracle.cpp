@@ -300,7 +300,7 @@ void forward_sample(const MlpConfig& c, const Layout& L, const float* params, co
 
 template <typename Acc>
 float learn_sample(const MlpConfig& c, const Layout& L, const float* params, float* grads, const void* inputs,
-                   const void* targets, int64_t s, Scratch& sc, int acc_mode)
+                   const void* targets, int64_t s, Scratch& sc, int acc_mode, float* input_grads = nullptr)
 {
     forward_sample<Acc>(c, L, params, inputs, s, sc, acc_mode);
     const int nl = c.n_layers;
@@ -325,7 +325,20 @@ float learn_sample(const MlpConfig& c, const Layout& L, const float* params, flo
             for (int i = 0; i < in; ++i) gw[i] = std::fmaf(g, sc.a[l][i], gw[i]);
             grads[L.b[l] + j] += g;
         }
-        if (l == 0) break;  // inputs are no_diff: the first layer's input gradient is dead
+        if (l == 0) {
+            // The example's inputs are no_diff, so this gradient is dead there; an encoder in front of the
+            // network needs it: dx = W_0^T dz_0 (same accumulation as the hidden layers), rounded to the
+            // storage type, one row of dims[0] floats per sample.
+            if (input_grads) {
+                for (int i = 0; i < in; ++i) {
+                    Acc r = Acc(0);
+                    const float* wcol = params + L.w[0] + i;
+                    for (int j = 0; j < out; ++j) r = AccOps<Acc>::mac(r, wcol[int64_t(j) * in], sc.dz[j]);
+                    input_grads[s * in + i] = round_to(c.dtype, float(r));
+                }
+            }
+            break;
+        }
         // da = W^T dz, then through the previous activation.
         for (int i = 0; i < in; ++i) {
             float v;
@@ -352,13 +365,14 @@ float learn_sample(const MlpConfig& c, const Layout& L, const float* params, flo
 
 template <typename Acc>
 void learn_range(const MlpConfig& c, const Layout& L, const float* params, float* grads, const void* inputs,
-                 const void* targets, int64_t s0, int64_t s1, int acc_mode, float* max_loss, double* sum_loss)
+                 const void* targets, int64_t s0, int64_t s1, int acc_mode, float* max_loss, double* sum_loss,
+                 float* input_grads = nullptr)
 {
     Scratch sc(c);
     float mx = 0.0f;
     double sum = 0.0;
     for (int64_t s = s0; s < s1; ++s) {
-        float l = learn_sample<Acc>(c, L, params, grads, inputs, targets, s, sc, acc_mode);
+        float l = learn_sample<Acc>(c, L, params, grads, inputs, targets, s, sc, acc_mode, input_grads);
         if (l > mx) mx = l;
         sum += double(l);
     }
@@ -449,6 +463,25 @@ int mlp_oracle_learn_gradient(const MlpConfig* c, const void* params, float* gra
             sum += sums[t];
         }
     }
+    if (loss_words) {
+        uint32_t bits = f2u(mx);
+        if (bits > loss_words[0]) loss_words[0] = bits;
+        loss_words[1] = f2u(u2f(loss_words[1]) + float(sum));
+    }
+    return 0;
+}
+
+// learnGradient that also returns the gradient with respect to the (unencoded) inputs: input_grads is
+// [count][dims[0]] fp32.  One thread, fp32 fused multiply-add accumulation.
+int mlp_oracle_learn_gradient_inputs(const MlpConfig* c, const void* params, float* grads, const void* inputs,
+                                     const void* targets, int64_t count, uint32_t* loss_words, float* input_grads)
+{
+    if (!config_ok(c) || c->encoding != MLP_ENC_NONE) return -1;
+    Layout L = make_layout(*c);
+    FloatParams fpar(*c, L, params);
+    float mx = 0.0f;
+    double sum = 0.0;
+    learn_range<float>(*c, L, fpar.v.data(), grads, inputs, targets, 0, count, 0, &mx, &sum, input_grads);
     if (loss_words) {
         uint32_t bits = f2u(mx);
         if (bits > loss_words[0]) loss_words[0] = bits;

@@ -87,6 +87,16 @@ def example_float_to_half(v):
     return int(lib().mlp_oracle_example_float_to_half(v))
 
 
+def learn_gradient_inputs(cfg, params, grads, inputs, targets, count, loss_words=None):
+    """learn_gradient that also returns d loss / d inputs, [count][dims[0]] fp32."""
+    assert grads.dtype == np.float32
+    ig = np.zeros((count, cfg.dims[0]), dtype=np.float32)
+    rc = lib().mlp_oracle_learn_gradient_inputs(ctypes.byref(cfg), _p(params), _p(grads), _p(inputs), _p(targets),
+                                                ctypes.c_int64(count), _p(loss_words), _p(ig))
+    assert rc == 0
+    return ig
+
+
 def example_learn_gradient(network_ptrs, loss_word, inputs, count):
     """network_ptrs: uint64 array [2][4] of host addresses (weights, weightsGrad, biases, biasesGrad)."""
     rc = lib().mlp_oracle_example_learn_gradient(_p(network_ptrs), _p(loss_word), _p(inputs), ctypes.c_uint32(count))

@@ -30,6 +30,10 @@ class LearnGradParamsEx(ctypes.Structure):
                 ("count", ctypes.c_uint32), ("flags", ctypes.c_uint32)]
 
 
+class LearnGradParamsEx2(ctypes.Structure):
+    _fields_ = [("base", LearnGradParamsEx), ("inputGradients", ctypes.c_uint64)]
+
+
 class ForwardParams(ctypes.Structure):
     _fields_ = [("networkBuffer", ctypes.c_uint64), ("inputs", ctypes.c_uint64),
                 ("outputs", ctypes.c_uint64), ("count", ctypes.c_uint32), ("flags", ctypes.c_uint32)]
@@ -37,6 +41,7 @@ class ForwardParams(ctypes.Structure):
 
 FLAG_SEQUENTIAL_SUM = 1
 FLAG_OUTPUT_STORAGE_TYPE = 2
+FLAG_INPUT_GRADIENT = 4
 
 
 class Buffer:
@@ -231,12 +236,16 @@ class Trainer:
         self.k_adjust = device.kernel("adjustParameters", cfg)
         self.k_forward = device.kernel(forward_entry, cfg)
 
-    def learn_gradient(self, inputs_address, targets_address, count, flags=0, clear_loss=True):
+    def learn_gradient(self, inputs_address, targets_address, count, flags=0, clear_loss=True, input_grads_address=0):
         """One learnGradient dispatch.  Gradients and the loss words accumulate across dispatches, so a
-        batch may be fed in several pieces with clear_loss=False after the first."""
+        batch may be fed in several pieces with clear_loss=False after the first.  With
+        input_grads_address the gradient with respect to the inputs ([count][dims[0]] fp32) is written too."""
         if clear_loss:
             self.loss.clear()
         args = LearnGradParamsEx(self.network.address, self.loss.address, inputs_address, targets_address, count, flags)
+        if input_grads_address:
+            args.flags |= FLAG_INPUT_GRADIENT
+            args = LearnGradParamsEx2(args, input_grads_address)
         self.k_learn.dispatch(args, groups_for(count))
 
     def adjust_parameters(self):

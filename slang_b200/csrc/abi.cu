@@ -399,12 +399,22 @@ int32_t mlp_dispatch(MlpDevice* d, MlpKernel* k, const void* args, size_t args_s
     }
     case Entry::Learn:
     case Entry::LearnSimt: {
-        if (args_size != sizeof(MlpLearnGradParamsEx)) return fail(MLP_E_INVALID_ARG, "learnGradient expects %zu argument bytes, got %zu", sizeof(MlpLearnGradParamsEx), args_size);
+        if (args_size != sizeof(MlpLearnGradParamsEx) && args_size != sizeof(MlpLearnGradParamsEx2))
+            return fail(MLP_E_INVALID_ARG, "learnGradient expects %zu or %zu argument bytes, got %zu", sizeof(MlpLearnGradParamsEx),
+                        sizeof(MlpLearnGradParamsEx2), args_size);
         MlpLearnGradParamsEx a; std::memcpy(&a, args, sizeof a);
+        float* input_grads = nullptr;
+        if (a.flags & MLP_FLAG_INPUT_GRADIENT) {
+            if (args_size != sizeof(MlpLearnGradParamsEx2)) return fail(MLP_E_INVALID_ARG, "MLP_FLAG_INPUT_GRADIENT needs MlpLearnGradParamsEx2");
+            MlpLearnGradParamsEx2 a2; std::memcpy(&a2, args, sizeof a2);
+            if (!a2.inputGradients) return fail(MLP_E_INVALID_ARG, "null input-gradient address");
+            if (k->cfg.encoding != MLP_ENC_NONE) return fail(MLP_E_NOT_AVAILABLE, "input gradients are not defined through the frequency encoding");
+            input_grads = (float*)a2.inputGradients;
+        }
         if ((uint64_t)gx * 256 < a.count) return fail(MLP_E_INVALID_ARG, "grid of %u groups does not cover %u samples", gx, a.count);
         if (!a.networkBuffer || !a.lossBuffer || (a.count && (!a.inputs || !a.targets))) return fail(MLP_E_INVALID_ARG, "null device address in the argument struct");
         const bool seq = (a.flags & MLP_FLAG_SEQUENTIAL_SUM) != 0;
-        if (k->entry == Entry::Learn && !seq) {
+        if (k->entry == Entry::Learn && !seq && !input_grads) {
             e = launch_learn_gradient_tc(d->stream, d->tc, k->cfg, a, &launches, &err);
         } else {
             if (seq) {
@@ -417,7 +427,7 @@ int32_t mlp_dispatch(MlpDevice* d, MlpKernel* k, const void* args, size_t args_s
                     d->seq_scratch_floats = need;
                 }
             }
-            e = launch_learn_gradient_simt(d->stream, k->cfg, a, d->seq_scratch, &launches, &err);
+            e = launch_learn_gradient_simt(d->stream, k->cfg, a, d->seq_scratch, &launches, &err, input_grads);
         }
         break;
     }

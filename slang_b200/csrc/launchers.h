@@ -16,7 +16,8 @@ cudaError_t launch_example_adjust_parameters(cudaStream_t st, const MlpAdjustPar
 cudaError_t launch_forward_simt(cudaStream_t st, const MlpConfig& c, const MlpForwardParams& a, int* launches,
                                 std::string* err);
 cudaError_t launch_learn_gradient_simt(cudaStream_t st, const MlpConfig& c, const MlpLearnGradParamsEx& a,
-                                       float* seq_scratch, int* launches, std::string* err);
+                                       float* seq_scratch, int* launches, std::string* err,
+                                       float* input_grads = nullptr);
 size_t sequential_scratch_floats_per_sample(const MlpConfig& c);
 cudaError_t launch_adjust_parameters(cudaStream_t st, const MlpConfig& c, const MlpAdjustParamsParams& a, int* launches);
 

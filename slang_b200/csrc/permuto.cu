@@ -12,6 +12,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cmath>
 #include <cstring>
 #include <string>
@@ -215,64 +216,56 @@ __device__ inline uint32_t vertex_index(const Simplex<D>& s, int k, const MlpPer
     return (li.table_offset + slot) * uint32_t(F);
 }
 
-// The threads of a warp work on different levels, so the level constants are read from shared memory
-// (a kernel parameter indexed per lane would be fetched once per distinct level).
-__device__ inline void stage_levels(const MlpPermutoConfig& c, MlpPermutoLevelInfo* s_levels)
-{
-    constexpr int kWords = sizeof(MlpPermutoLevelInfo) / 4;
-    const uint32_t* src = reinterpret_cast<const uint32_t*>(c.levels);
-    uint32_t* dst = reinterpret_cast<uint32_t*>(s_levels);
-    for (int i = threadIdx.x; i < c.n_levels * kWords; i += blockDim.x) dst[i] = src[i];
-    __syncthreads();
-}
-
 __device__ inline bool level_live(const MlpPermutoConfig& c, const MlpPermutoLevelInfo& li)
 {
     return !(float(li.level_index) >= c.max_level + 1e-3f);
 }
 
-// Block of 256 threads = floor(256 / L) positions x L levels, levels fastest: the level threads of a
-// position write one contiguous output row.
+// Thread mapping of both kernels: a block of 256 threads is floor(256 / L) positions x L levels, levels
+// fastest, so the level threads of a position write one contiguous output row.  The grid is sized to the
+// machine and every block walks over position groups with a grid stride; a thread keeps its level for its
+// whole life, so it reads its level's constants from the kernel parameters once.
 template <int D, int F, typename T>
 __global__ void __launch_bounds__(256)
 permuto_encode_kernel(const __grid_constant__ MlpPermutoConfig c, const float* __restrict__ positions,
                       const T* __restrict__ table, T* __restrict__ out, uint32_t count)
 {
-    __shared__ MlpPermutoLevelInfo s_levels[MLP_PERMUTO_MAX_LEVELS];
-    stage_levels(c, s_levels);
     const uint32_t L = uint32_t(c.n_levels);
     const uint32_t per_block = 256u / L;
     const uint32_t local = threadIdx.x / L, l = threadIdx.x - local * L;
-    const uint64_t n = uint64_t(blockIdx.x) * per_block + local;
-    if (local >= per_block || n >= count) return;
-    const MlpPermutoLevelInfo& li = s_levels[l];
-    T acc[F];
+    if (local >= per_block) return;
+    const MlpPermutoLevelInfo li = c.levels[l];
+    const bool live = level_live(c, li);
+    const uint64_t row = uint64_t(L) * F;
+    for (uint64_t n = uint64_t(blockIdx.x) * per_block + local; n < count; n += uint64_t(gridDim.x) * per_block) {
+        T acc[F];
 #pragma unroll
-    for (int f = 0; f < F; ++f) acc[f] = Elem<T>::from(0.0f);
-    if (level_live(c, li)) {
-        float pos[D];
+        for (int f = 0; f < F; ++f) acc[f] = Elem<T>::from(0.0f);
+        if (live) {
+            float pos[D];
 #pragma unroll
-        for (int d = 0; d < D; ++d) pos[d] = positions[n * D + d];
-        Simplex<D> s;
-        locate<D>(pos, li, s);
-        Vec<F, T> feat[D + 1];
+            for (int d = 0; d < D; ++d) pos[d] = positions[n * D + d];
+            Simplex<D> s;
+            locate<D>(pos, li, s);
+            Vec<F, T> feat[D + 1];
 #pragma unroll
-        for (int k = 0; k <= D; ++k) feat[k] = load_vec<F, T>(table + vertex_index<D, F>(s, k, li));
+            for (int k = 0; k <= D; ++k) feat[k] = load_vec<F, T>(table + vertex_index<D, F>(s, k, li));
 #pragma unroll
-        for (int k = 0; k <= D; ++k) {
-            const T w = Elem<T>::from(s.bary[k]);
+            for (int k = 0; k <= D; ++k) {
+                const T w = Elem<T>::from(s.bary[k]);
 #pragma unroll
-            for (int f = 0; f < F; ++f) acc[f] = Elem<T>::add(acc[f], Elem<T>::mul(w, feat[k].v[f]));
+                for (int f = 0; f < F; ++f) acc[f] = Elem<T>::add(acc[f], Elem<T>::mul(w, feat[k].v[f]));
+            }
         }
-    }
-    Vec<F, T> o;
+        Vec<F, T> o;
 #pragma unroll
-    for (int f = 0; f < F; ++f) o.v[f] = acc[f];
-    *reinterpret_cast<Vec<F, T>*>(out + n * (uint64_t(L) * F) + uint64_t(li.level_index) * F) = o;
+        for (int f = 0; f < F; ++f) o.v[f] = acc[f];
+        *reinterpret_cast<Vec<F, T>*>(out + n * row + uint64_t(li.level_index) * F) = o;
+    }
 }
 
-// Block of 256 threads = floor(256 / L) positions x L levels; the level threads of a position leave their
-// position-gradient terms in shared memory and the level-0 thread adds them in ascending level order.
+// The level-0 thread of a position adds the level threads' position-gradient terms in ascending level
+// order: by warp shuffles when a warp holds whole positions (L divides 32), through shared memory otherwise.
 template <int D, int F, typename T>
 __global__ void __launch_bounds__(256)
 permuto_backward_kernel(const __grid_constant__ MlpPermutoConfig c, const float* __restrict__ positions,
@@ -281,24 +274,35 @@ permuto_backward_kernel(const __grid_constant__ MlpPermutoConfig c, const float*
 {
     __shared__ float s_dpos[256 * D];
     __shared__ MlpPermutoLevelInfo s_levels[MLP_PERMUTO_MAX_LEVELS];
-    stage_levels(c, s_levels);
     const uint32_t L = uint32_t(c.n_levels);
     const uint32_t per_block = 256u / L;
     const uint32_t local = threadIdx.x / L, l = threadIdx.x - local * L;
-    const uint64_t n = uint64_t(blockIdx.x) * per_block + local;
-    const bool active = local < per_block && n < count;
-    float dpos[D];
+    // This kernel runs as many short-lived blocks (the reductions retire faster that way), so the level
+    // constants go through shared memory: a kernel parameter indexed per lane is fetched once per
+    // distinct level of the warp.
+    {
+        constexpr int kWords = sizeof(MlpPermutoLevelInfo) / 4;
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(c.levels);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(s_levels);
+        for (uint32_t i = threadIdx.x; i < L * kWords; i += blockDim.x) dst[i] = src[i];
+        __syncthreads();
+    }
+    const MlpPermutoLevelInfo li = s_levels[l];
+    const bool live = level_live(c, li);
+    const uint64_t row = uint64_t(L) * F;
+    for (uint64_t base = uint64_t(blockIdx.x) * per_block; base < count; base += uint64_t(gridDim.x) * per_block) {
+        const uint64_t n = base + local;
+        const bool active = local < per_block && n < count;
+        float dpos[D];
 #pragma unroll
-    for (int d = 0; d < D; ++d) dpos[d] = 0.0f;
-    if (active) {
-        const MlpPermutoLevelInfo& li = s_levels[l];
-        if (level_live(c, li)) {
+        for (int d = 0; d < D; ++d) dpos[d] = 0.0f;
+        if (active && live) {
             float pos[D];
 #pragma unroll
             for (int d = 0; d < D; ++d) pos[d] = positions[n * D + d];
             Simplex<D> s;
             locate<D>(pos, li, s);
-            const Vec<F, T> dy = load_vec<F, T>(d_out + n * (uint64_t(L) * F) + uint64_t(li.level_index) * F);
+            const Vec<F, T> dy = load_vec<F, T>(d_out + n * row + uint64_t(li.level_index) * F);
             float dbary[D + 2];
 #pragma unroll
             for (int k = 0; k <= D; ++k) {
@@ -336,17 +340,30 @@ permuto_backward_kernel(const __grid_constant__ MlpPermutoConfig c, const float*
                 }
             }
         }
-    }
-    if (!d_positions) return;
+        if (d_positions) {   // uniform over the block
+            if ((32u % L) == 0) {
+                // the level threads of a position sit in one warp: the level-0 lane pulls the others' terms
+                // in ascending level order (every lane runs the shuffles; lanes past the batch carry zeros)
 #pragma unroll
-    for (int d = 0; d < D; ++d) s_dpos[threadIdx.x * D + d] = dpos[d];
-    __syncthreads();
-    if (active && l == 0) {
+                for (int d = 0; d < D; ++d) {
+                    float acc = 0.0f + dpos[d];
+                    for (uint32_t j = 1; j < L; ++j) acc += __shfl_down_sync(0xffffffffu, dpos[d], j);
+                    if (active && l == 0) d_positions[n * D + d] = acc;
+                }
+            } else {
 #pragma unroll
-        for (int d = 0; d < D; ++d) {
-            float acc = 0.0f;
-            for (uint32_t j = 0; j < L; ++j) acc += s_dpos[(threadIdx.x + j) * D + d];
-            d_positions[n * D + d] = acc;
+                for (int d = 0; d < D; ++d) s_dpos[threadIdx.x * D + d] = dpos[d];
+                __syncthreads();
+                if (active && l == 0) {
+#pragma unroll
+                    for (int d = 0; d < D; ++d) {
+                        float acc = 0.0f;
+                        for (uint32_t j = 0; j < L; ++j) acc += s_dpos[(threadIdx.x + j) * D + d];
+                        d_positions[n * D + d] = acc;
+                    }
+                }
+                __syncthreads();
+            }
         }
     }
 }
@@ -378,11 +395,21 @@ cudaError_t run(bool backward, cudaStream_t st, const MlpPermutoConfig& c, uint6
 {
     const uint32_t L = uint32_t(c.n_levels);
     const uint32_t per_block = 256u / L;
+    const uint64_t groups = (uint64_t(count) + per_block - 1) / per_block;
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int resident = 0;   // blocks of this kernel that fit an SM at once
+    if (!backward) cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, permuto_encode_kernel<D, F, T>, 256, 0);
+    else cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, permuto_backward_kernel<D, F, T>, 256, 0);
+    if (resident < 1) resident = 1;
+    // encode: one wave of blocks that walk the positions; reverse: up to 64 waves of short blocks
+    const unsigned grid = (unsigned)std::min<uint64_t>(groups, uint64_t(sms) * resident * (backward ? 64 : 1));
     if (!backward) {
-        permuto_encode_kernel<D, F, T><<<(unsigned)((count + per_block - 1) / per_block), 256, 0, st>>>(
+        permuto_encode_kernel<D, F, T><<<grid, 256, 0, st>>>(
             c, (const float*)positions, (const T*)table, (T*)out, count);
     } else {
-        permuto_backward_kernel<D, F, T><<<(unsigned)((count + per_block - 1) / per_block), 256, 0, st>>>(
+        permuto_backward_kernel<D, F, T><<<grid, 256, 0, st>>>(
             c, (const float*)positions, (const T*)table, (const T*)out, (T*)d_table, (float*)d_positions, count);
     }
     return cudaGetLastError();

@@ -94,7 +94,7 @@ forward_simt_kernel(SimtNet net, const MlpLayerPointers* __restrict__ lp, const 
 __global__ void __launch_bounds__(256)
 learn_gradient_simt_kernel(SimtNet net, const MlpLayerPointers* __restrict__ lp, uint32_t* lossBuffer,
                            const void* __restrict__ inputs, const void* __restrict__ targets, uint32_t count,
-                           int group, float* __restrict__ seq_scratch)
+                           int group, float* __restrict__ seq_scratch, float* __restrict__ input_grads)
 {
     extern __shared__ float smem[];
     const MlpConfig& c = net.cfg;
@@ -128,6 +128,17 @@ learn_gradient_simt_kernel(SimtNet net, const MlpLayerPointers* __restrict__ lp,
                 for (int j = 0; j < out; ++j) r = fmaf(load_as_f32(c.dtype, W, int64_t(j) * in + i), dz[j], r);
                 const float d = round_to(c.dtype, act_deriv(c.hidden_act, c.act_alpha, zprev[i]));
                 zprev[i] = round_to(c.dtype, r * d);
+            }
+        }
+        if (input_grads) {
+            // dx = W_0^T dz_0: dead in the example (its inputs are no_diff), wanted by an encoder in front
+            const int in = c.dims[0], out = c.dims[1];
+            const float* dz = zd;
+            const void* W = (const void*)lp[0].weights;
+            for (int i = 0; i < in; ++i) {
+                float r = 0.0f;
+                for (int j = 0; j < out; ++j) r = fmaf(load_as_f32(c.dtype, W, int64_t(j) * in + i), dz[j], r);
+                input_grads[int64_t(tid) * in + i] = round_to(c.dtype, r);
             }
         }
     }
@@ -297,7 +308,7 @@ cudaError_t launch_forward_simt(cudaStream_t st, const MlpConfig& c, const MlpFo
 }
 
 cudaError_t launch_learn_gradient_simt(cudaStream_t st, const MlpConfig& c, const MlpLearnGradParamsEx& a,
-                                       float* seq_scratch, int* launches, std::string* err)
+                                       float* seq_scratch, int* launches, std::string* err, float* input_grads)
 {
     SimtNet net;
     if (!make_simt_net(c, &net, err)) return cudaErrorInvalidValue;
@@ -321,7 +332,7 @@ cudaError_t launch_learn_gradient_simt(cudaStream_t st, const MlpConfig& c, cons
     learn_gradient_simt_kernel<<<grid, 256, smem, st>>>(net, (const MlpLayerPointers*)a.networkBuffer,
                                                         (uint32_t*)a.lossBuffer, (const void*)a.inputs,
                                                         (const void*)a.targets, a.count, group,
-                                                        seq ? seq_scratch : nullptr);
+                                                        seq ? seq_scratch : nullptr, input_grads);
     *launches += 1;
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess || !seq) return e;

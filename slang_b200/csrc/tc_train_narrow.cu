@@ -41,7 +41,9 @@ using namespace layout;
 
 constexpr int H = 64;         // padded width of every layer
 constexpr int TS = 128;       // samples per tile
-constexpr int kThreads = 64 + 128;
+// Threads: warp 0 issues the products, warp 1 owns the tensor-memory allocation, then CS groups of four
+// epilogue warps; group g handles columns [g * 64 / CS, (g + 1) * 64 / CS) of every row.
+constexpr int threads_for(int cs) { return 64 + 128 * cs; }
 constexpr uint32_t kMat = 64 * 64 * 2;     // one padded weight matrix: 64 rows of 128 bytes
 constexpr uint32_t kTile = 128 * 64 * 2;   // one [128][64] operand tile: 128 rows of 128 bytes
 
@@ -105,9 +107,13 @@ struct Map {
 
 // HACT / OACT: the hidden and output activation as compile-time constants, or -1 to read them from
 // the configuration at run time (slower: every element goes through a switch).
-template <int NL, int FMT, int HACT, int OACT>
-__global__ void __launch_bounds__(kThreads, 1) learn_gradient_narrow_kernel(const Params p)
+// CS: column split of the epilogue (1, 2 or 4 groups of four warps).  The loss of a sample is summed by
+// the group that holds the output columns, so CS > 1 needs the output width to fit one group (64 / CS).
+template <int NL, int FMT, int HACT, int OACT, int CS>
+__global__ void __launch_bounds__(threads_for(CS), 1) learn_gradient_narrow_kernel(const Params p)
 {
+    constexpr int kThreads = threads_for(CS);
+    constexpr int GW = H / CS;   // columns per epilogue group
     using M = Map<NL>;
     using C = Cvt<FMT>;
     extern __shared__ uint8_t smem_raw[];
@@ -126,7 +132,7 @@ __global__ void __launch_bounds__(kThreads, 1) learn_gradient_narrow_kernel(cons
 
     if (threadIdx.x == 0) {
         mbar_init(acc_full, 1);
-        mbar_init(acc_free, 4);
+        mbar_init(acc_free, 4 * CS);
         mbar_init(tile_done, 1);
         *abort_flag = 0u;
         fence_mbar_init();
@@ -242,8 +248,10 @@ __global__ void __launch_bounds__(kThreads, 1) learn_gradient_narrow_kernel(cons
         }
     } else if (warp >= 2) {
         // =================================== epilogue warps ========================================
-        const int q = warp & 3;
-        const int r = q * 32 + lane;  // the sample row (TMEM lane) this thread owns
+        const int q = warp & 3;       // a warp reaches the 32 tensor-memory lanes of its index modulo four
+        const int r = q * 32 + lane;  // the sample row (TMEM lane) this thread works on
+        const int g = (warp - 2) >> 2;
+        const int cbeg = g * GW, cend = cbeg + GW;   // this thread's columns of the row
         const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16) + M::kColAcc;
         const int od = c.dims[NL];
         const int hact = HACT >= 0 ? HACT : c.hidden_act;
@@ -272,30 +280,31 @@ __global__ void __launch_bounds__(kThreads, 1) learn_gradient_narrow_kernel(cons
             if (it > 0) ok = ok && mbar_wait(tile_done, (it - 1) & 1u, abort_flag, p.status, kStatusEpi);
             if (!ok) break;
             {
-                float x[H];
 #pragma unroll
-                for (int i = 0; i < H; ++i) x[i] = 0.0f;
-                if (valid) {
-                    if (c.encoding == MLP_ENC_FREQ2D) {
+                for (int c0 = cbeg; c0 < cend; c0 += 16) {
+                    float x[16];
 #pragma unroll
-                        for (int u = 0; u < 2; ++u) {
-                            const float v = load_as_f32(c.input_dtype, p.inputs, sample * 2 + u);
+                    for (int i = 0; i < 16; ++i) x[i] = 0.0f;
+                    if (valid) {
+                        if (c.encoding == MLP_ENC_FREQ2D) {
+                            // features [16u, 16u + 16) are sin/cos of 2^k pi times coordinate u, k = 0..7
+                            if (c0 < 32) {
+                                const float v = load_as_f32(c.input_dtype, p.inputs, sample * 2 + (c0 >> 4));
 #pragma unroll
-                            for (int k = 0; k < 8; ++k) {
-                                const float arg = ldexpf(3.14159265358979323846f, k) * v;
-                                sincosf(arg, &x[u * 16 + k * 2 + 0], &x[u * 16 + k * 2 + 1]);
+                                for (int k = 0; k < 8; ++k) {
+                                    const float arg = ldexpf(3.14159265358979323846f, k) * v;
+                                    sincosf(arg, &x[k * 2 + 0], &x[k * 2 + 1]);
+                                }
                             }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i)
+                                if (c0 + i < c.dims[0]) x[i] = load_as_f32(c.input_dtype, p.inputs, sample * c.dims[0] + c0 + i);
                         }
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < H; ++i)
-                            if (i < c.dims[0]) x[i] = load_as_f32(c.input_dtype, p.inputs, sample * c.dims[0] + i);
                     }
+                    *row_chunk(M::kA, c0 / 8) = make_uint4(C::pack2(x[0], x[1]), C::pack2(x[2], x[3]), C::pack2(x[4], x[5]), C::pack2(x[6], x[7]));
+                    *row_chunk(M::kA, c0 / 8 + 1) = make_uint4(C::pack2(x[8], x[9]), C::pack2(x[10], x[11]), C::pack2(x[12], x[13]), C::pack2(x[14], x[15]));
                 }
-#pragma unroll
-                for (int j = 0; j < H / 8; ++j)
-                    *row_chunk(M::kA, j) = make_uint4(C::pack2(x[8 * j], x[8 * j + 1]), C::pack2(x[8 * j + 2], x[8 * j + 3]),
-                                                      C::pack2(x[8 * j + 4], x[8 * j + 5]), C::pack2(x[8 * j + 6], x[8 * j + 7]));
                 release();
             }
             // ---- forward ----
@@ -307,7 +316,7 @@ __global__ void __launch_bounds__(kThreads, 1) learn_gradient_narrow_kernel(cons
                     float loss = 0.0f;
                     const int width = c.dims[l + 1];  // real features of this layer; the padding beyond stays zero
 #pragma unroll
-                    for (int c0 = 0; c0 < H; c0 += 16) {
+                    for (int c0 = cbeg; c0 < cend; c0 += 16) {
                         const uint32_t abuf = last ? M::kDZ : M::kA + (uint32_t)(l + 1) * kTile;
                         if (c0 >= width) {
                             *row_chunk(abuf, c0 / 8) = make_uint4(0u, 0u, 0u, 0u);
@@ -369,7 +378,7 @@ __global__ void __launch_bounds__(kThreads, 1) learn_gradient_narrow_kernel(cons
                 if (ok) {
                     const int width = c.dims[l];  // real features of dZ_{l-1}
 #pragma unroll
-                    for (int c0 = 0; c0 < H; c0 += 16) {
+                    for (int c0 = cbeg; c0 < cend; c0 += 16) {
                         if (c0 >= width) {
                             *row_chunk(M::kA + (uint32_t)l * kTile, c0 / 8) = make_uint4(0u, 0u, 0u, 0u);
                             *row_chunk(M::kA + (uint32_t)l * kTile, c0 / 8 + 1) = make_uint4(0u, 0u, 0u, 0u);
@@ -402,7 +411,7 @@ __global__ void __launch_bounds__(kThreads, 1) learn_gradient_narrow_kernel(cons
                 const int in = c.dims[l], out = c.dims[l + 1];
                 float* dW = (float*)p.net[l].weightsGrad;
                 float* dB = (float*)p.net[l].biasesGrad;
-                for (int c0 = 0; c0 < H; c0 += 16) {
+                for (int c0 = cbeg; c0 < cend; c0 += 16) {
                     uint32_t v[16];
                     tmem_ld_32x16(lane_base + M::kColDW + (uint32_t)l * 64u + (uint32_t)c0, v);
                     tmem_ld_wait();
@@ -412,10 +421,12 @@ __global__ void __launch_bounds__(kThreads, 1) learn_gradient_narrow_kernel(cons
                             if (c0 + i < in) atomicAdd(dW + (size_t)r * in + c0 + i, __uint_as_float(v[i]));
                     }
                 }
-                uint32_t b[16];
-                tmem_ld_32x16(lane_base + M::kColDB + (uint32_t)l * 16u, b);
-                tmem_ld_wait();
-                if (r < out) atomicAdd(dB + r, __uint_as_float(b[0]));
+                if (g == 0) {
+                    uint32_t b[16];
+                    tmem_ld_32x16(lane_base + M::kColDB + (uint32_t)l * 16u, b);
+                    tmem_ld_wait();
+                    if (r < out) atomicAdd(dB + r, __uint_as_float(b[0]));
+                }
             }
             float mx = run_max, sm = run_sum;
 #pragma unroll
@@ -423,7 +434,7 @@ __global__ void __launch_bounds__(kThreads, 1) learn_gradient_narrow_kernel(cons
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
                 sm += __shfl_xor_sync(0xffffffffu, sm, o);
             }
-            if (lane == 0) {
+            if (lane == 0 && g == 0) {   // the output columns, and with them the loss, live in group 0
                 atomicMax(p.loss_words, __float_as_uint(mx));
                 atomicAdd((float*)(p.loss_words + 1), sm);
             }
@@ -450,15 +461,25 @@ bool tc_train_narrow_supported(const MlpConfig& c)
     return true;
 }
 
-template <int NL, int FMT, int HACT, int OACT>
-static cudaError_t launch_narrow(cudaStream_t st, TcWorkspace* ws, const narrow::Params& p)
+template <int NL, int FMT, int HACT, int OACT, int CS>
+static cudaError_t launch_narrow_cs(cudaStream_t st, TcWorkspace* ws, const narrow::Params& p)
 {
-    auto kern = narrow::learn_gradient_narrow_kernel<NL, FMT, HACT, OACT>;
+    auto kern = narrow::learn_gradient_narrow_kernel<NL, FMT, HACT, OACT, CS>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)narrow::Map<NL>::kSmemBytes);
     if (e != cudaSuccess) return e;
     const uint32_t grid = p.n_tiles < (uint32_t)ws->sm_count ? p.n_tiles : (uint32_t)ws->sm_count;
-    kern<<<grid, narrow::kThreads, narrow::Map<NL>::kSmemBytes, st>>>(p);
+    kern<<<grid, narrow::threads_for(CS), narrow::Map<NL>::kSmemBytes, st>>>(p);
     return cudaGetLastError();
+}
+
+// The widest column split whose group still holds every output column.
+template <int NL, int FMT, int HACT, int OACT>
+static cudaError_t launch_narrow(cudaStream_t st, TcWorkspace* ws, const narrow::Params& p)
+{
+    const int od = p.cfg.dims[NL];
+    if (od <= narrow::H / 4) return launch_narrow_cs<NL, FMT, HACT, OACT, 4>(st, ws, p);
+    if (od <= narrow::H / 2) return launch_narrow_cs<NL, FMT, HACT, OACT, 2>(st, ws, p);
+    return launch_narrow_cs<NL, FMT, HACT, OACT, 1>(st, ws, p);
 }
 
 cudaError_t launch_learn_gradient_narrow(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const MlpLearnGradParamsEx& a,

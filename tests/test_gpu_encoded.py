@@ -1,0 +1,93 @@
+"""Input gradients of learnGradient and the encoder-in-front composition (positions -> permutohedral
+features -> MLP), against the oracle doing the same three stages on the CPU."""
+import numpy as np
+import pytest
+
+from oracle import oracle
+from oracle import permuto as OP
+from slang_b200 import config as C
+from slang_b200 import permuto as P
+from mlp_testlib import make_problem, rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def device():
+    from slang_b200.api import Device
+    d = Device(0)
+    yield d
+    d.destroy()
+
+
+@pytest.mark.parametrize("name,count", [("c1", 1000), ("c2", 777), ("c4", 300)])
+def test_input_gradients_match_oracle(device, name, count):
+    from slang_b200.api import Trainer
+    cfg, p0, batches = make_problem(name, count, seed=9, steps=1)
+    x, t = batches[0]
+    _, _, total = C.param_layout(cfg)
+    g_ref = np.zeros(total, dtype=np.float32)
+    words = np.zeros(2, dtype=np.uint32)
+    ig_ref = oracle.learn_gradient_inputs(cfg, p0, g_ref, x, t, count, words)
+    tr = Trainer(device, cfg, p0)
+    xb, tb = device.create_buffer(x.nbytes, x), device.create_buffer(t.nbytes, t)
+    igb = device.create_buffer(count * cfg.dims[0] * 4)
+    tr.learn_gradient(xb.address, tb.address, count, input_grads_address=igb.address)
+    device.wait()
+    ig = igb.read(np.float32).reshape(count, cfg.dims[0])
+    if cfg.dtype == C.F32:
+        assert np.array_equal(ig.view(np.uint32), ig_ref.view(np.uint32))     # per-sample work is bit-exact
+    else:
+        assert rel_err(ig, ig_ref) <= 1e-2
+    assert rel_err(tr.read_grads(), g_ref) <= (1e-5 if cfg.dtype == C.F32 else 1e-2)
+    # the flag needs the longer argument struct and a destination
+    from slang_b200.api import FLAG_INPUT_GRADIENT
+    from slang_b200.lib import MlpError
+    with pytest.raises(MlpError):
+        tr.learn_gradient(xb.address, tb.address, count, flags=FLAG_INPUT_GRADIENT)
+
+
+def test_encoder_in_front_of_the_network_trains_like_the_oracle(device):
+    from slang_b200.encoded import EncodedTrainer
+    rng = np.random.default_rng(12)
+    pcfg = P.prepare(2, 2, 10, 4, 2.0, 1.0, 1.1, 1337, C.F32)
+    cfg = C.make_config([8, 16, 16, 3], dtype=C.F32, hidden_act=C.ACT_RELU, lr=1e-2)
+    p0 = C.init_params(cfg, seed=2, scheme="kaiming")
+    table0 = rng.uniform(-1e-1, 1e-1, pcfg.table_values).astype(np.float32)
+    count, steps = 2000, 5
+    tcfg = C.make_config([1, 1], dtype=C.F32, lr=1e-2)
+    # oracle
+    params, table = p0.copy(), table0.copy()
+    _, _, total = C.param_layout(cfg)
+    st = np.zeros(total, dtype=C.ADAM_STATE_DTYPE); st["master"] = p0
+    tst = np.zeros(table.size, dtype=C.ADAM_STATE_DTYPE); tst["master"] = table0
+    batches, ref_losses = [], []
+    for k in range(steps):
+        pos = rng.uniform(0, 1, (count, 2)).astype(np.float32)
+        tgt = np.stack([np.sin(6 * pos[:, 0]), np.cos(5 * pos[:, 1]), pos[:, 0] * pos[:, 1]], axis=1).astype(np.float32)
+        batches.append((pos, tgt))
+        feats = OP.encode(pcfg, pos, table)
+        grads = np.zeros(total, dtype=np.float32)
+        words = np.zeros(2, dtype=np.uint32)
+        ig = oracle.learn_gradient_inputs(cfg, params, grads, feats, tgt, count, words)
+        dtable = np.zeros_like(table)
+        OP.backward(pcfg, pos, table, ig, dtable)
+        oracle.adjust_parameters(cfg, st, params, grads)
+        oracle.adjust_parameters(tcfg, tst, table, dtable)
+        ref_losses.append(float(words[1:].view(np.float32)[0]) / count)
+    # library
+    et = EncodedTrainer(device, pcfg, cfg, table0, p0, max_count=count)
+    gpu_losses = []
+    for pos, tgt in batches:
+        pb, tb = device.create_buffer(pos.nbytes, pos), device.create_buffer(tgt.nbytes, tgt)
+        et.learn_gradient(pb.address, tb.address, count)
+        gpu_losses.append(et.trainer.read_loss()[1] / count)
+        et.adjust_parameters()
+    device.wait()
+    print("losses gpu", gpu_losses, "ref", ref_losses)
+    assert ref_losses[-1] < ref_losses[0]
+    for a, b in zip(gpu_losses, ref_losses):
+        assert abs(a - b) <= 1e-4 * abs(b)
+    assert rel_err(et.trainer.read_params(), params) <= 1e-3
+    assert rel_err(et.read_table(), table) <= 1e-3
+    assert not et.read_table_grads().any()     # Adam cleared the table gradient

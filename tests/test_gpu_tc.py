@@ -119,6 +119,27 @@ def test_narrow_networks_on_tensor_cores(device, name, count):
     assert abs(l_gpu[0][0] - l_ref[0][0]) <= 1e-2 * abs(l_ref[0][0])
 
 
+@pytest.mark.parametrize("dims", [[8, 48, 24], [20, 64, 33, 40], [64, 64, 64, 64, 64, 64], [3, 16, 7]])
+def test_narrow_kernel_other_shapes(device, dims):
+    """Shapes that exercise each column split of the padded kernel's epilogue (output width <= 16, <= 32,
+    larger), odd widths, bf16, tanh hidden units."""
+    from oracle import oracle
+    rng = np.random.default_rng(sum(dims))
+    cfg = C.make_config(dims, dtype=C.BF16, hidden_act=C.ACT_TANH, output_act=C.ACT_IDENTITY, adam_master=1)
+    p0 = C.init_params(cfg, seed=5, scheme="xavier")
+    count = 128 * 3 + 17
+    x = rng.uniform(-1, 1, (count, dims[0])).astype(np.float32)
+    t = rng.uniform(-1, 1, (count, dims[-1])).astype(np.float32)
+    _, l_ref, g_ref, _ = oracle_trajectory(cfg, p0, [(x, t)])
+    _, l_gpu, g_gpu, _, tr = gpu_trajectory(device, cfg, p0, [(x, t)])
+    assert tr.k_learn.implementation == "tcgen05"
+    err = _grad_layer_errs(cfg, g_gpu, g_ref)
+    print(dims, "worst per-tensor gradient rel err %.3g" % err)
+    assert err < 1e-2
+    assert abs(l_gpu[0][1] - l_ref[0][1]) <= 1e-2 * abs(l_ref[0][1])
+    assert abs(l_gpu[0][0] - l_ref[0][0]) <= 1e-2 * abs(l_ref[0][0])
+
+
 @pytest.mark.parametrize("name,count,steps", [("c2", 2048, 10), ("c3", 1024, 10)])
 def test_narrow_network_trajectories(device, name, count, steps):
     cfg, p0, batches = make_problem(name, count, seed=3, steps=steps)
