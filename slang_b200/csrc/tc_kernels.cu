@@ -8,11 +8,15 @@
 // the end.  Activations never leave the SM.
 //
 // Orientation: features run along the 128 TMEM lanes (the MMA's M), samples along the columns (N = 64):
-//   forward   Z_l^T [out x 64]  = W_l [out x in]   . A_l^T          A: W_l, K-major      B: A_l,  K-major
-//   input     dA_l^T [in x 64]  = W_l^T [in x out] . dZ_l^T         A: W_l, MN-major     B: dZ_l, K-major
-//   weights   dW_l [out x in]  += dZ_l^T [out x 64] . A_l [64 x in]  A: dZ_l, MN-major    B: A_l,  MN-major
-// so a single copy of W_l (row-major rows of 128 bytes, 128-byte swizzle) serves both directions and
-// each activation / gradient tile [64 samples][features] serves as a K-major and an MN-major operand.
+//   forward   Z_l^T [out x 64]  = W_l [out x in]   . A_l^T          A: W_l, K-major      B: A_l,  MN-major
+//   input     dA_l^T [in x 64]  = W_l^T [in x out] . dZ_l^T         A: W_l, MN-major     B: dZ_l, MN-major
+//   weights   dW_l [out x in]  += dZ_l^T [out x 64] . A_l [64 x in]  A: dZ_l, K-major     B: A_l,  K-major
+// so a single copy of W_l (row-major rows of 128 bytes, 128-byte swizzle) serves both directions.  The
+// hidden activations and their gradients are stored feature-major, [128 features][64 samples] with the
+// samples of a feature contiguous (one 128-byte swizzled row per feature): the epilogue thread that owns
+// a feature writes its 16 samples as two 16-byte stores, the row is a K-major operand of the weight-
+// gradient products (K = samples) and an MN-major operand of the layer products (N = samples).  The input
+// tile and the target / dZ_4 tile keep the layout they arrive in, [64 samples][64 features].
 // An epilogue thread owns one feature (one TMEM lane) and 32 of the 64 sample columns: the bias is a
 // per-thread constant and the bias gradient a per-thread sum.
 //
@@ -70,7 +74,7 @@ constexpr uint32_t kW2 = kW1 + 32768;
 constexpr uint32_t kW3 = kW2 + 32768;
 constexpr uint32_t kW4 = kW3 + 32768;        // 64 rows x 2 panels (panel stride 8192)
 constexpr uint32_t kX = kW4 + 16384;         // 2 buffers x [64 rows x 1 panel]
-constexpr uint32_t kA1 = kX + 2 * 8192;      // A_1..A_4: [64 rows x 2 panels] each (panel stride 8192)
+constexpr uint32_t kA1 = kX + 2 * 8192;      // A_1..A_4: [128 feature rows][64 samples] each, 128-byte rows
 constexpr uint32_t kDZ4 = kA1 + 4 * 16384;   // [64 rows x 1 panel]: targets land here, dZ_4 replaces them
 constexpr uint32_t kBias = kDZ4 + 8192;      // fp32 [5][128]
 constexpr uint32_t kLossPart = kBias + 5 * 128 * 4;  // fp32 [2][64]
@@ -255,10 +259,12 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
         if (n_my_tiles > 0) {
             const bool leader = elect_one();
             constexpr uint32_t F = E::kUmmaFmt;
-            constexpr uint32_t kIdescFwd = umma_idesc(F, 0, 0, 128, CH);    // W (K) x act (K)
-            constexpr uint32_t kIdescDx = umma_idesc(F, 1, 0, 128, CH);     // W^T (MN) x dZ (K)
-            constexpr uint32_t kIdescDw = umma_idesc(F, 1, 1, 128, 128);    // dZ^T (MN) x act (MN)
-            constexpr uint32_t kIdescDw64 = umma_idesc(F, 1, 1, 128, 64);   // N = 64 variants (dW_4^T, dW_0)
+            constexpr uint32_t kIdescFwd0 = umma_idesc(F, 0, 0, 128, CH);   // W_0 (K) x input tile (K)
+            constexpr uint32_t kIdescFwd = umma_idesc(F, 0, 1, 128, CH);    // W (K) x act (MN: samples contiguous)
+            constexpr uint32_t kIdescDx4 = umma_idesc(F, 1, 0, 128, CH);    // W_4^T (MN) x dZ_4 (K: features contiguous)
+            constexpr uint32_t kIdescDx = umma_idesc(F, 1, 1, 128, CH);     // W^T (MN) x dZ (MN)
+            constexpr uint32_t kIdescDw = umma_idesc(F, 0, 0, 128, 128);    // dZ (K = samples) x act (K = samples)
+            constexpr uint32_t kIdescDw64 = umma_idesc(F, 0, 1, 128, 64);   // act or dZ_0 (K) x dZ_4 or input tile (MN)
             uint32_t step = 0;   // both chains are at the same step whenever this warp looks
             bool ok = true;
             long long t_wait = 0;
@@ -309,7 +315,7 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                         const uint32_t acc = tmem_base + kColAcc + (uint32_t)(h * CH);
 #pragma unroll
                         for (int k = 0; k < D0 / 16; ++k)
-                            umma_f16_warp(acc, desc_k(kW0, 16384u, k), desc_k(xbuf + (uint32_t)h * (uint32_t)(CH * 128), 8192u, k), kIdescFwd, k > 0);
+                            umma_f16_warp(acc, desc_k(kW0, 16384u, k), desc_k(xbuf + (uint32_t)h * (uint32_t)(CH * 128), 8192u, k), kIdescFwd0, k > 0);
                         umma_commit_warp(&acc_full[h]);
                     }
                 }
@@ -324,9 +330,10 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                         chain_wait(h);
                         if (ok) {
                             const uint32_t acc = tmem_base + kColAcc + (uint32_t)(h * CH);
+                            const uint32_t half = (uint32_t)h * (uint32_t)(CH * 2);  // the chain's samples inside a feature row
 #pragma unroll
                             for (int k = 0; k < H / 16; ++k)
-                                umma_f16_warp(acc, desc_k(w_off(l), wpanel, k), desc_k(abuf + (uint32_t)h * (uint32_t)(CH * 128), 8192u, k), kIdescFwd, k > 0);
+                                umma_f16_warp(acc, desc_k(w_off(l), wpanel, k), desc_mn(abuf + half, 8192u, k), kIdescFwd, k > 0);
                             umma_commit_warp(&acc_full[h]);
                         }
                     }
@@ -343,22 +350,26 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                         chain_wait(h);
                         if (ok) {
                             const uint32_t acc = tmem_base + kColAcc + (uint32_t)(h * CH);
-                            const uint32_t row = (uint32_t)h * (uint32_t)(CH * 128);  // 32 rows of 128 bytes
+                            const uint32_t row = (uint32_t)h * (uint32_t)(CH * 128);  // sample-major tiles: 32 rows of 128 bytes
+                            const uint32_t half = (uint32_t)h * (uint32_t)(CH * 2);   // feature-major tiles: 64 bytes inside a row
                             const uint32_t prior = (it > 0 || h > 0) ? 1u : 0u;  // the launch's first product overwrites
                             {
-#pragma unroll
-                                for (int k = 0; k < out_dim(l) / 16; ++k)
-                                    umma_f16_warp(acc, desc_mn(w_off(l), wpanel, k), desc_k(dzbuf + row, 8192u, k), kIdescDx, k > 0);
                                 if (l == NL - 1) {
 #pragma unroll
+                                    for (int k = 0; k < out_dim(l) / 16; ++k)
+                                        umma_f16_warp(acc, desc_mn(w_off(l), wpanel, k), desc_k(dzbuf + row, 8192u, k), kIdescDx4, k > 0);
+#pragma unroll
                                     for (int k = 0; k < CH / 16; ++k)
-                                        umma_f16_warp(tmem_base + kColDW4T, desc_mn(abuf + row, 8192u, k), desc_mn(dzbuf + row, 8192u, k),
+                                        umma_f16_warp(tmem_base + kColDW4T, desc_k(abuf + half, 0u, k), desc_mn(dzbuf + row, 8192u, k),
                                                  kIdescDw64, prior | (uint32_t)(k > 0));
                                 } else {
 #pragma unroll
+                                    for (int k = 0; k < out_dim(l) / 16; ++k)
+                                        umma_f16_warp(acc, desc_mn(w_off(l), wpanel, k), desc_mn(dzbuf + half, 8192u, k), kIdescDx, k > 0);
+#pragma unroll
                                     for (int k = 0; k < CH / 16; ++k)
-                                        umma_f16_warp(tmem_base + kColDW1 + (uint32_t)(l - 1) * 128u, desc_mn(dzbuf + row, 8192u, k),
-                                                 desc_mn(abuf + row, 8192u, k), kIdescDw, prior | (uint32_t)(k > 0));
+                                        umma_f16_warp(tmem_base + kColDW1 + (uint32_t)(l - 1) * 128u, desc_k(dzbuf + half, 0u, k),
+                                                 desc_k(abuf + half, 0u, k), kIdescDw, prior | (uint32_t)(k > 0));
                                 }
                                 umma_commit_warp(&acc_full[h]);
                             }
@@ -373,7 +384,7 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                 if (ok) {
 #pragma unroll
                     for (int k = 0; k < NS / 16; ++k)
-                        umma_f16_warp(tmem_base + kColAcc, desc_mn(kA1, 8192u, k), desc_mn(xbuf, 8192u, k), kIdescDw64, k > 0);
+                        umma_f16_warp(tmem_base + kColAcc, desc_k(kA1, 0u, k), desc_mn(xbuf, 8192u, k), kIdescDw64, k > 0);
 #pragma unroll
                     for (int h = 0; h < NCH; ++h) umma_commit_warp(&acc_full[h]);
                     if (leader) {
@@ -409,11 +420,23 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
         const int col0 = e * CPT;
         const int h = col0 / CH;               // the chain those columns belong to
         const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16) + kColAcc + (uint32_t)col0;
-        // Byte offset of (row col0, feature f) inside a [64 x W] operand buffer, minus the swizzled chunk.
+        // Sample-major tiles ([64 samples][64 features], the target / dZ_4 buffer): byte offset of
+        // (row col0, feature f) minus the swizzled chunk.  Row s of this thread's column group puts feature
+        // f in 16-byte chunk ((f & 63) >> 3) ^ (s & 7); bits 4..6 of the base are that chunk for row 0, so
+        // the other rows' chunks are an XOR away.
         const uint32_t pbase = (uint32_t)(f >> 6) * 8192u + (uint32_t)col0 * 128u + (uint32_t)(f & 7) * 2u;
-        // Row s of this thread's column group puts feature f in 16-byte chunk ((f & 63) >> 3) ^ (s & 7);
-        // bit 4..6 of the base are that chunk for row 0, so the other rows' chunks are an XOR away.
         const uint32_t xo0 = pbase + (uint32_t)(((f & 63) >> 3) << 4);
+        // Feature-major tiles ([128 features][64 samples]): this thread's CPT samples are CPT / 8
+        // consecutive 16-byte chunks of row f, chunk c stored at c ^ (f & 7).
+        static_assert(CPT % 8 == 0, "a thread's samples fill whole 16-byte chunks");
+        const uint32_t frow = (uint32_t)f * 128u;
+        const uint32_t fchunk0 = (uint32_t)(col0 >> 3);
+        auto store_row = [&](uint8_t* buf, const uint32_t* w) {
+#pragma unroll
+            for (int c = 0; c < CPT / 8; ++c)
+                *(uint4*)(buf + frow + (((fchunk0 + (uint32_t)c) ^ (uint32_t)(f & 7)) << 4)) =
+                    make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
+        };
 
         uint32_t dreg[NL - 1][CPT / 2];  // activation derivatives of the four hidden layers, two per register
         float dw0[CPT];                  // this thread's slice of dW_0 (row f, columns col0..), summed over tiles
@@ -454,6 +477,7 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                     uint8_t* dst = smem + kA1 + (uint32_t)l * 16384u;
                     const float bl = s_bias[l * 128 + f];
                     const float2 bias2 = make_float2(bl, bl);
+                    uint32_t aw[CPT / 2];
 #pragma unroll
                     for (int s = 0; s < CPT; s += 2) {
                         // bias, storage rounding of the pre-activation (one paired conversion), activation
@@ -461,11 +485,10 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                         const uint32_t zr = E::pack2(zf.x, zf.y);
                         float2 a, d;
                         act_pair2<ACT>(make_float2(E::unpack_lo(zr), E::unpack_hi(zr)), p.act_alpha, a, d);
-                        const uint32_t ap = E::pack2(a.x, a.y);
-                        *(uint16_t*)(dst + (xo0 ^ (uint32_t)((s & 7) << 4)) + s * 128) = (uint16_t)(ap & 0xffffu);
-                        *(uint16_t*)(dst + (xo0 ^ (uint32_t)(((s + 1) & 7) << 4)) + (s + 1) * 128) = (uint16_t)(ap >> 16);
+                        aw[s >> 1] = E::pack2(a.x, a.y);
                         dreg[l][s >> 1] = E::pack2(d.x, d.y);
                     }
+                    store_row(dst, aw);
                     release_acc();
                 }
             }
@@ -547,16 +570,17 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                     tmem_ld_wait();
                     uint8_t* dst = smem + kA1 + (uint32_t)(l - 1) * 16384u;
                     float2 dbp = make_float2(0.0f, 0.0f);
+                    uint32_t zw[CPT / 2];
 #pragma unroll
                     for (int s = 0; s < CPT; s += 2) {
                         const uint32_t dd = dreg[l - 1][s >> 1];
                         const float2 g = __fmul2_rn(make_float2(__uint_as_float(v[s]), __uint_as_float(v[s + 1])),
                                                     make_float2(E::unpack_lo(dd), E::unpack_hi(dd)));
                         const uint32_t zp = E::pack2(g.x, g.y);
-                        *(uint16_t*)(dst + (xo0 ^ (uint32_t)((s & 7) << 4)) + s * 128) = (uint16_t)(zp & 0xffffu);
-                        *(uint16_t*)(dst + (xo0 ^ (uint32_t)(((s + 1) & 7) << 4)) + (s + 1) * 128) = (uint16_t)(zp >> 16);
+                        zw[s >> 1] = zp;
                         dbp = __fadd2_rn(dbp, make_float2(E::unpack_lo(zp), E::unpack_hi(zp)));
                     }
+                    store_row(dst, zw);
                     db[l - 1] += dbp.x + dbp.y;
                     release_acc();
                 }
