@@ -43,8 +43,10 @@ cudaError_t launch_forward_tc(cudaStream_t st, TcWorkspace* ws, const MlpConfig&
                               int* launches, std::string* err);
 cudaError_t launch_learn_gradient_tc(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c,
                                      const MlpLearnGradParamsEx& a, int* launches, std::string* err);
+// input_grads (optional): [count][dims[0]] fp32 gradient with respect to the inputs (no input encoding).
 cudaError_t launch_learn_gradient_narrow(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c,
-                                         const MlpLearnGradParamsEx& a, int* launches, std::string* err);
+                                         const MlpLearnGradParamsEx& a, int* launches, std::string* err,
+                                         float* input_grads = nullptr);
 // Cycle counts CTA 0 of the last tensor-core learnGradient recorded (diagnostics).
 cudaError_t tc_read_timing(cudaStream_t st, TcWorkspace* ws, unsigned long long* out8);
 // Reads and clears the device status word (0 = no kernel gave up on a bounded wait).

@@ -56,6 +56,7 @@ struct Params {
     uint32_t* status;
     const void* inputs;
     const void* targets;
+    float* input_grads;   // optional: [count][dims[0]] gradient with respect to the (unencoded) inputs
     uint32_t count;
     uint32_t n_tiles;
 };
@@ -238,11 +239,20 @@ __global__ void __launch_bounds__(threads_for(CS), 1) learn_gradient_narrow_kern
                 }
                 wait_free();  // dZ_0 is in shared memory (in A_1's buffer, or the last layer's own buffer)
                 if (ok) {
+                    const uint32_t dz0 = NL == 1 ? M::kDZ : M::kA + kTile;
                     if (leader) {
-                        grads(0, NL == 1 ? M::kDZ : M::kA + kTile, first);
+                        if (p.input_grads) {
+                            // the input gradient dA_0 = dZ_0 . W_0, wanted by an encoder in front of the network
+#pragma unroll
+                            for (int k = 0; k < H / 16; ++k)
+                                umma_f16(acc, desc_k(dz0, k), desc_mn(M::kW, k), kIdDx, k > 0);
+                        }
+                        grads(0, dz0, first);
+                        if (p.input_grads) umma_commit(acc_full);
                         umma_commit(tile_done);
                     }
                     __syncwarp();
+                    if (p.input_grads) wait_free();  // the epilogue has read dA_0 out of the accumulator
                 }
             }
         }
@@ -400,6 +410,27 @@ __global__ void __launch_bounds__(threads_for(CS), 1) learn_gradient_narrow_kern
                     release();
                 }
             }
+            // ---- optional: the input gradient rows, rounded to the storage type ----
+            if (p.input_grads) {
+                wait_full();
+                if (ok) {
+                    const int in0 = c.dims[0];
+#pragma unroll
+                    for (int c0 = cbeg; c0 < cend; c0 += 16) {
+                        if (c0 >= in0) continue;
+                        uint32_t v[16];
+                        tmem_ld_32x16(t_acc + (uint32_t)c0, v);
+                        tmem_ld_wait();
+                        if (valid) {
+                            float* dst = p.input_grads + sample * (uint64_t)in0 + c0;
+#pragma unroll
+                            for (int i = 0; i < 16; ++i)
+                                if (c0 + i < in0) dst[i] = C::round(__uint_as_float(v[i]));
+                        }
+                    }
+                    release();
+                }
+            }
         }
 
         // ---- one add per parameter per CTA: lane = output feature, column = input feature ----
@@ -483,7 +514,7 @@ static cudaError_t launch_narrow(cudaStream_t st, TcWorkspace* ws, const narrow:
 }
 
 cudaError_t launch_learn_gradient_narrow(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const MlpLearnGradParamsEx& a,
-                                         int* launches, std::string* err)
+                                         int* launches, std::string* err, float* input_grads)
 {
     if (!tc_train_narrow_supported(c)) { if (err) *err = "shape not built for the narrow tensor-core path"; return cudaErrorInvalidValue; }
     if (a.count == 0) return cudaSuccess;
@@ -494,6 +525,7 @@ cudaError_t launch_learn_gradient_narrow(cudaStream_t st, TcWorkspace* ws, const
     p.status = ws->status;
     p.inputs = (const void*)a.inputs;
     p.targets = (const void*)a.targets;
+    p.input_grads = input_grads;
     p.count = a.count;
     p.n_tiles = (a.count + narrow::TS - 1) / narrow::TS;
     cudaError_t e = cudaErrorInvalidValue;
