@@ -384,6 +384,62 @@ def bench_permuto(args):
     device.destroy()
 
 
+def bench_encoded(args):
+    """Trainable encoder in front of a small network: 3-D positions -> permutohedral features (16 levels x 2)
+    -> fp16 MLP 32-64-64-3 (ReLU, sigmoid output, L2).  One step = encode, learnGradient with input
+    gradients (tensor cores), the encoder's reverse pass, Adam over the network and over the table."""
+    import torch
+    from slang_b200 import config as C
+    from slang_b200 import permuto as P
+    from slang_b200.api import Device
+    from slang_b200.encoded import EncodedTrainer
+    torch.cuda.set_device(0)
+    dev_t = torch.device("cuda", 0)
+    stream = torch.cuda.Stream(device=dev_t)
+    torch.cuda.set_stream(stream)
+    device = Device(0, stream.cuda_stream)
+    count = args.batch if args.batch != (1 << 26) else 1 << 22
+    pcfg = P.prepare(3, 2, 19, 16, 16.0, 0.5, 1.1, 1337, C.F32)
+    cfg = C.make_config([32, 64, 64, 3], dtype=C.F16, hidden_act=C.ACT_RELU, output_act=C.ACT_SIGMOID, loss=C.LOSS_L2_SUM,
+                        target_dtype=C.F16, lr=1e-2, adam_master=1)
+    rng = np.random.default_rng(3)
+    table0 = rng.uniform(-1e-4, 1e-4, pcfg.table_values).astype(np.float32)
+    et = EncodedTrainer(device, pcfg, cfg, table0, C.init_params(cfg, seed=1, scheme="kaiming"), max_count=count)
+    gen = torch.Generator(device=dev_t); gen.manual_seed(9)
+    pos = torch.rand((count, 3), device=dev_t, generator=gen)
+    tgt = (0.5 + 0.5 * torch.sin(pos * torch.tensor([7.0, 11.0, 13.0], device=dev_t))).to(torch.float16).contiguous()
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev_t)
+
+    def step():
+        et.learn_gradient(pos.data_ptr(), tgt.data_ptr(), count)
+        et.adjust_parameters()
+
+    losses = []
+    for _ in range(args.warmup):
+        step()
+        losses.append(et.trainer.read_loss()[1] / count)
+    times = []
+    launches0 = device.launch_count
+    for _ in range(args.steps):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); step(); e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    launches = device.launch_count - launches0
+    losses.append(et.trainer.read_loss()[1] / count)
+    ms = float(np.mean(times))
+    line = {"metric": "encoder + MLP train positions/sec (encode, fwd+bwd with input gradients, encoder reverse, Adam x2)",
+            "value": count / (ms * 1e-3), "unit": "positions/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "permutohedral encoder (3-D, 16 x 2^19 x 2, fp32 table) + fp16 MLP 32-64-64-3", "positions": count,
+                       "l2": "512 MB written between timed steps"},
+            "gpu_launches": launches, "implementation": et.trainer.k_learn.implementation,
+            "loss": {"first_warmup_step": losses[0], "last_step": losses[-1]}}
+    print(json.dumps(line), flush=True)
+    device.destroy()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -409,6 +465,10 @@ def main():
     if args.config in ("c2", "c3"):
         if rank == 0:
             bench_narrow(args)
+        return
+    if args.config == "encoded":
+        if rank == 0:
+            bench_encoded(args)
         return
     if args.config.startswith("permuto"):
         if rank == 0:
