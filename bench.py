@@ -638,6 +638,22 @@ def main():
             r, n, dt = oracle_rate(cfg, args.config, threads, 12.0)
             line["cpu_baseline"] = {"value": r, "unit": UNIT, "cores": threads, "kind": "port",
                                     "sample": "%d samples, learnGradient + adjustParameters once, %.1f s" % (n, dt)}
+            # The structure of the reference's example kernels on the same GPU: one thread per sample,
+            # scalar fused multiply-adds, block-level sums and atomics (learnGradient_simt), on a bounded sample.
+            n_simt = min(count, 1 << 18)
+            tr_simt = Trainer(device, cfg, p0, learn_entry="learnGradient_simt")
+            for _ in range(2):
+                tr_simt.learn_gradient(xs[0].data_ptr(), ts[0].data_ptr(), n_simt)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            tr_simt.learn_gradient(xs[0].data_ptr(), ts[0].data_ptr(), n_simt)
+            tr_simt.adjust_parameters()
+            e1.record()
+            torch.cuda.synchronize()
+            line["gpu_baseline"] = {"value": n_simt / (e0.elapsed_time(e1) * 1e-3), "unit": UNIT,
+                                    "kind": "one thread per sample on the same GPU (the example kernels' structure, this library's learnGradient_simt)",
+                                    "sample": "%d samples, learnGradient + adjustParameters once" % n_simt}
         print(json.dumps(line), flush=True)
     device.destroy()
     if world > 1:
