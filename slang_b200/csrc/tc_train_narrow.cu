@@ -87,21 +87,24 @@ template <> struct Cvt<MLP_F16> {
     __device__ static __forceinline__ uint16_t one() { return 0x3C00; }
 };
 
-// Shared-memory map for NL layers (bytes from a 1024-aligned base).
-template <int NL>
+// Shared-memory map for NL layers and NCH tiles in flight (bytes from a 1024-aligned base).  DFA: the
+// activation derivative is read back from the stored activation instead of being kept in its own buffer.
+template <int NL, int NCH, bool DFA>
 struct Map {
     static constexpr uint32_t kW = 0;                          // NL padded weight matrices
-    static constexpr uint32_t kA = kW + NL * kMat;             // A_0 .. A_{NL-1}: layer inputs; dZ_{l-1} later replaces A_l
-    static constexpr uint32_t kD = kA + NL * kTile;            // activation derivatives of layers 0 .. NL-2
-    static constexpr uint32_t kDZ = kD + (NL - 1) * kTile;     // dZ of the last layer
-    static constexpr uint32_t kOnes = kDZ + kTile;             // [128 rows][16 elements]: first column one, rest zero
+    static constexpr uint32_t kChain = kW + NL * kMat;         // per tile in flight:
+    static constexpr uint32_t kA = 0;                          //   A_0 .. A_{NL-1}: layer inputs; dZ_{l-1} later replaces A_l
+    static constexpr uint32_t kD = kA + NL * kTile;            //   activation derivatives of layers 0 .. NL-2 (absent with DFA)
+    static constexpr uint32_t kDZ = kD + (DFA ? 0 : (NL - 1) * kTile);   //   dZ of the last layer
+    static constexpr uint32_t kChainBytes = kDZ + kTile;
+    static constexpr uint32_t kOnes = kChain + NCH * kChainBytes;  // [128 rows][16 elements]: first column one, rest zero
     static constexpr uint32_t kBias = kOnes + 128 * 32;        // fp32 [NL][64]
-    static constexpr uint32_t kBars = kBias + NL * 64 * 4;     // acc_full, acc_free, tile_done
-    static constexpr uint32_t kTmemPtr = kBars + 3 * 8;
+    static constexpr uint32_t kBars = kBias + NL * 64 * 4;     // per chain: acc_full, acc_free, tile_done
+    static constexpr uint32_t kTmemPtr = kBars + 3 * NCH * 8;
     static constexpr uint32_t kAbort = kTmemPtr + 4;
     static constexpr uint32_t kSmemBytes = kAbort + 4 + 1024;
-    // tensor-memory columns
-    static constexpr uint32_t kColAcc = 0, kColDW = 64, kColDB = 64 + 64 * NL, kTmemCols = 512;
+    // tensor-memory columns: one working accumulator per chain, then the gradients (shared by the chains)
+    static constexpr uint32_t kColAcc = 0, kColDW = 64 * NCH, kColDB = kColDW + 64 * NL, kTmemCols = 512;
     static_assert(kColDB + 16 * NL <= 512, "tensor memory budget");
     static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 };
@@ -110,19 +113,25 @@ struct Map {
 // the configuration at run time (slower: every element goes through a switch).
 // CS: column split of the epilogue (1, 2 or 4 groups of four warps).  The loss of a sample is summed by
 // the group that holds the output columns, so CS > 1 needs the output width to fit one group (64 / CS).
-template <int NL, int FMT, int HACT, int OACT, int CS>
-__global__ void __launch_bounds__(threads_for(CS), 1) learn_gradient_narrow_kernel(const Params p)
+// NCH: tiles in flight per CTA ("chains"): each has its own operand buffers, working accumulator,
+// barriers and epilogue warps, and both accumulate into the same gradient columns; while one chain's
+// epilogue runs, the tensor pipe works on the other chain's product.  NCH = 2 needs the derivative-
+// from-activation form (ReLU only): the forward epilogue stores max(z, 0) and marks z == 0 with a
+// negative zero, so the backward epilogue recovers the derivative 1 / one half / 0 exactly from the
+// stored value (a negative zero is a zero to every product that reads the buffer).
+template <int NL, int FMT, int HACT, int OACT, int CS, int NCH>
+__global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narrow_kernel(const Params p)
 {
-    constexpr int kThreads = threads_for(CS);
+    constexpr int kThreads = threads_for(CS * NCH);
     constexpr int GW = H / CS;   // columns per epilogue group
-    using M = Map<NL>;
+    constexpr bool DFA = NCH > 1;
+    static_assert(!DFA || HACT == MLP_ACT_RELU, "the derivative is recovered from the activation only for ReLU");
+    using M = Map<NL, NCH, DFA>;
     using C = Cvt<FMT>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const uint32_t sbase = smem_u32(smem);
-    uint64_t* acc_full = (uint64_t*)(smem + M::kBars);
-    uint64_t* acc_free = acc_full + 1;
-    uint64_t* tile_done = acc_full + 2;
+    uint64_t* bars = (uint64_t*)(smem + M::kBars);   // [chain][acc_full, acc_free, tile_done]
     uint32_t* tmem_ptr = (uint32_t*)(smem + M::kTmemPtr);
     volatile uint32_t* abort_flag = (volatile uint32_t*)(smem + M::kAbort);
     float* s_bias = (float*)(smem + M::kBias);
@@ -132,9 +141,11 @@ __global__ void __launch_bounds__(threads_for(CS), 1) learn_gradient_narrow_kern
     const uint32_t n_my_tiles = (p.n_tiles > blockIdx.x) ? (p.n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
 
     if (threadIdx.x == 0) {
-        mbar_init(acc_full, 1);
-        mbar_init(acc_free, 4 * CS);
-        mbar_init(tile_done, 1);
+        for (int h = 0; h < NCH; ++h) {
+            mbar_init(&bars[3 * h + 0], 1);
+            mbar_init(&bars[3 * h + 1], 4 * CS);
+            mbar_init(&bars[3 * h + 2], 1);
+        }
         *abort_flag = 0u;
         fence_mbar_init();
     }
@@ -166,6 +177,8 @@ __global__ void __launch_bounds__(threads_for(CS), 1) learn_gradient_narrow_kern
 
     if (warp == 0) {
         // =================================== control warp ==========================================
+        // Chain h works on this CTA's tiles h, h + NCH, h + 2 NCH, ...; the warp walks the layer schedule
+        // once per round and serves the chains in turn at every step.
         if (n_my_tiles > 0) {
             const bool leader = elect_one();
             constexpr uint32_t F = C::kUmmaFmt;
@@ -188,71 +201,89 @@ __global__ void __launch_bounds__(threads_for(CS), 1) learn_gradient_narrow_kern
             auto desc_ones = [&](int k) -> uint64_t {
                 return ((uint64_t)kHi32 << 32) | (lo_base + ((M::kOnes + (uint32_t)k * 512u) >> 4) + (1u << 16));
             };
-            const uint32_t acc = tmem_base + M::kColAcc;
-            uint32_t n_free = 0;  // acc_free phases observed
+            uint32_t n_free[NCH];  // acc_free phases observed, per chain
+#pragma unroll
+            for (int h = 0; h < NCH; ++h) n_free[h] = 0;
             bool ok = true;
-            auto wait_free = [&]() {
-                ok = ok && mbar_wait(acc_free, n_free & 1u, abort_flag, p.status, kStatusCtrl);
-                ++n_free;
+            auto wait_free = [&](int h) {
+                ok = ok && mbar_wait(&bars[3 * h + 1], n_free[h] & 1u, abort_flag, p.status, kStatusCtrl);
+                ++n_free[h];
                 tc_fence_after();
             };
-            // dW_l and db_l of the current tile; `first` is true only for the launch's first tile.
-            auto grads = [&](int l, uint32_t dzbuf, bool first) {
+            // dW_l and db_l of a tile; `first` is true only for the launch's first product into them.
+            auto grads = [&](int l, uint32_t dzbuf, uint32_t abuf, bool first) {
 #pragma unroll
                 for (int k = 0; k < TS / 16; ++k) {
-                    umma_f16(tmem_base + M::kColDW + (uint32_t)l * 64u, desc_mn(dzbuf, k), desc_mn(M::kA + (uint32_t)l * kTile, k), kIdDw,
+                    umma_f16(tmem_base + M::kColDW + (uint32_t)l * 64u, desc_mn(dzbuf, k), desc_mn(abuf, k), kIdDw,
                              (first && k == 0) ? 0u : 1u);
                     umma_f16(tmem_base + M::kColDB + (uint32_t)l * 16u, desc_mn(dzbuf, k), desc_ones(k), kIdDb, (first && k == 0) ? 0u : 1u);
                 }
             };
-            for (uint32_t it = 0; it < n_my_tiles && ok; ++it) {
-                const bool first = it == 0;
+            const uint32_t rounds = (n_my_tiles + NCH - 1) / NCH;
+            for (uint32_t rd = 0; rd < rounds && ok; ++rd) {
                 // ---- forward ----
 #pragma unroll
                 for (int l = 0; l < NL; ++l) {
-                    wait_free();  // A_l is in shared memory (l = 0: the input rows) and the accumulator is drained
-                    if (ok) {
-                        if (leader) {
 #pragma unroll
-                            for (int k = 0; k < H / 16; ++k)
-                                umma_f16(acc, desc_k(M::kA + (uint32_t)l * kTile, k), desc_k(M::kW + (uint32_t)l * kMat, k), kIdFwd, k > 0);
-                            umma_commit(acc_full);
+                    for (int h = 0; h < NCH; ++h) {
+                        if (rd * NCH + h >= n_my_tiles) continue;
+                        const uint32_t cb = M::kChain + (uint32_t)h * M::kChainBytes;
+                        wait_free(h);  // A_l is in shared memory (l = 0: the input rows) and the accumulator is drained
+                        if (ok) {
+                            if (leader) {
+#pragma unroll
+                                for (int k = 0; k < H / 16; ++k)
+                                    umma_f16(tmem_base + M::kColAcc + (uint32_t)h * 64u, desc_k(cb + M::kA + (uint32_t)l * kTile, k),
+                                             desc_k(M::kW + (uint32_t)l * kMat, k), kIdFwd, k > 0);
+                                umma_commit(&bars[3 * h + 0]);
+                            }
+                            __syncwarp();
                         }
-                        __syncwarp();
                     }
                 }
                 // ---- backward ----
 #pragma unroll
                 for (int l = NL - 1; l >= 1; --l) {
-                    wait_free();  // dZ_l is in shared memory
-                    if (ok) {
-                        const uint32_t dzbuf = (l == NL - 1) ? M::kDZ : M::kA + (uint32_t)(l + 1) * kTile;
-                        if (leader) {
 #pragma unroll
-                            for (int k = 0; k < H / 16; ++k)
-                                umma_f16(acc, desc_k(dzbuf, k), desc_mn(M::kW + (uint32_t)l * kMat, k), kIdDx, k > 0);
-                            grads(l, dzbuf, first);
-                            umma_commit(acc_full);
+                    for (int h = 0; h < NCH; ++h) {
+                        if (rd * NCH + h >= n_my_tiles) continue;
+                        const uint32_t cb = M::kChain + (uint32_t)h * M::kChainBytes;
+                        wait_free(h);  // dZ_l is in shared memory
+                        if (ok) {
+                            const uint32_t dzbuf = cb + ((l == NL - 1) ? M::kDZ : M::kA + (uint32_t)(l + 1) * kTile);
+                            if (leader) {
+#pragma unroll
+                                for (int k = 0; k < H / 16; ++k)
+                                    umma_f16(tmem_base + M::kColAcc + (uint32_t)h * 64u, desc_k(dzbuf, k), desc_mn(M::kW + (uint32_t)l * kMat, k),
+                                             kIdDx, k > 0);
+                                grads(l, dzbuf, cb + M::kA + (uint32_t)l * kTile, rd == 0 && h == 0);
+                                umma_commit(&bars[3 * h + 0]);
+                            }
+                            __syncwarp();
                         }
-                        __syncwarp();
                     }
                 }
-                wait_free();  // dZ_0 is in shared memory (in A_1's buffer, or the last layer's own buffer)
-                if (ok) {
-                    const uint32_t dz0 = NL == 1 ? M::kDZ : M::kA + kTile;
-                    if (leader) {
-                        if (p.input_grads) {
-                            // the input gradient dA_0 = dZ_0 . W_0, wanted by an encoder in front of the network
 #pragma unroll
-                            for (int k = 0; k < H / 16; ++k)
-                                umma_f16(acc, desc_k(dz0, k), desc_mn(M::kW, k), kIdDx, k > 0);
+                for (int h = 0; h < NCH; ++h) {
+                    if (rd * NCH + h >= n_my_tiles) continue;
+                    const uint32_t cb = M::kChain + (uint32_t)h * M::kChainBytes;
+                    wait_free(h);  // dZ_0 is in shared memory (in A_1's buffer, or the last layer's own buffer)
+                    if (ok) {
+                        const uint32_t dz0 = cb + (NL == 1 ? M::kDZ : M::kA + kTile);
+                        if (leader) {
+                            if (p.input_grads) {
+                                // the input gradient dA_0 = dZ_0 . W_0, wanted by an encoder in front of the network
+#pragma unroll
+                                for (int k = 0; k < H / 16; ++k)
+                                    umma_f16(tmem_base + M::kColAcc + (uint32_t)h * 64u, desc_k(dz0, k), desc_mn(M::kW, k), kIdDx, k > 0);
+                            }
+                            grads(0, dz0, cb + M::kA, rd == 0 && h == 0);
+                            if (p.input_grads) umma_commit(&bars[3 * h + 0]);
+                            umma_commit(&bars[3 * h + 2]);
                         }
-                        grads(0, dz0, first);
-                        if (p.input_grads) umma_commit(acc_full);
-                        umma_commit(tile_done);
+                        __syncwarp();
+                        if (p.input_grads) wait_free(h);  // the epilogue has read dA_0 out of the accumulator
                     }
-                    __syncwarp();
-                    if (p.input_grads) wait_free();  // the epilogue has read dA_0 out of the accumulator
                 }
             }
         }
@@ -260,9 +291,14 @@ __global__ void __launch_bounds__(threads_for(CS), 1) learn_gradient_narrow_kern
         // =================================== epilogue warps ========================================
         const int q = warp & 3;       // a warp reaches the 32 tensor-memory lanes of its index modulo four
         const int r = q * 32 + lane;  // the sample row (TMEM lane) this thread works on
-        const int g = (warp - 2) >> 2;
+        const int h = (warp - 2) / (4 * CS);          // the chain (tile in flight) this warp serves
+        const int g = ((warp - 2) >> 2) % CS;
         const int cbeg = g * GW, cend = cbeg + GW;   // this thread's columns of the row
-        const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16) + M::kColAcc;
+        uint64_t* acc_full = &bars[3 * h + 0];
+        uint64_t* acc_free = &bars[3 * h + 1];
+        uint64_t* tile_done = &bars[3 * h + 2];
+        const uint32_t cb = M::kChain + (uint32_t)h * M::kChainBytes;
+        const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16) + M::kColAcc + (uint32_t)h * 64u;
         const int od = c.dims[NL];
         const int hact = HACT >= 0 ? HACT : c.hidden_act;
         const int oact = OACT >= 0 ? OACT : c.output_act;
@@ -281,10 +317,12 @@ __global__ void __launch_bounds__(threads_for(CS), 1) learn_gradient_narrow_kern
             ++n_full;
             tc_fence_after();
         };
-        auto row_chunk = [&](uint32_t buf, int j) -> uint4* { return (uint4*)(smem + buf + chunk_offset<H>(128, r, j)); };
+        auto row_chunk = [&](uint32_t buf, int j) -> uint4* { return (uint4*)(smem + cb + buf + chunk_offset<H>(128, r, j)); };
+        const uint32_t n_chain_tiles = n_my_tiles > (uint32_t)h ? (n_my_tiles - (uint32_t)h + NCH - 1) / NCH : 0;
 
-        for (uint32_t it = 0; it < n_my_tiles && ok; ++it) {
-            const uint64_t sample = ((uint64_t)blockIdx.x + (uint64_t)it * gridDim.x) * TS + (uint64_t)r;
+        for (uint32_t it = 0; it < n_chain_tiles && ok; ++it) {
+            const uint64_t tile = (uint64_t)blockIdx.x + ((uint64_t)it * NCH + (uint64_t)h) * gridDim.x;
+            const uint64_t sample = tile * TS + (uint64_t)r;
             const bool valid = sample < p.count;
             // ---- the input row: conversion (and zero padding) or the frequency encoding ----
             if (it > 0) ok = ok && mbar_wait(tile_done, (it - 1) & 1u, abort_flag, p.status, kStatusEpi);
@@ -347,8 +385,15 @@ __global__ void __launch_bounds__(threads_for(CS), 1) learn_gradient_narrow_kern
                                 const int j = c0 + k + e;
                                 const float z = C::round(__uint_as_float(v[k + e]) + bb[e]);
                                 if (!last) {
-                                    a4[e] = act_value(hact, c.act_alpha, z);
-                                    d4[e] = act_deriv(hact, c.act_alpha, z);
+                                    if constexpr (DFA) {
+                                        // max(z, 0), with z == 0 stored as a negative zero: the backward epilogue
+                                        // tells "below zero", "zero" and "above zero" apart by the stored bits
+                                        a4[e] = z > 0.0f ? z : (z == 0.0f ? -0.0f : 0.0f);
+                                        d4[e] = 0.0f;
+                                    } else {
+                                        a4[e] = act_value(hact, c.act_alpha, z);
+                                        d4[e] = act_deriv(hact, c.act_alpha, z);
+                                    }
                                 } else {
                                     // loss and dZ of the last layer; padded outputs and rows past the batch give zero
                                     float dz = 0.0f;
@@ -369,9 +414,11 @@ __global__ void __launch_bounds__(threads_for(CS), 1) learn_gradient_narrow_kern
                         }
                         *row_chunk(abuf, c0 / 8) = make_uint4(pa[0], pa[1], pa[2], pa[3]);
                         *row_chunk(abuf, c0 / 8 + 1) = make_uint4(pa[4], pa[5], pa[6], pa[7]);
-                        if (!last) {
-                            *row_chunk(M::kD + (uint32_t)l * kTile, c0 / 8) = make_uint4(pd[0], pd[1], pd[2], pd[3]);
-                            *row_chunk(M::kD + (uint32_t)l * kTile, c0 / 8 + 1) = make_uint4(pd[4], pd[5], pd[6], pd[7]);
+                        if constexpr (!DFA) {
+                            if (!last) {
+                                *row_chunk(M::kD + (uint32_t)l * kTile, c0 / 8) = make_uint4(pd[0], pd[1], pd[2], pd[3]);
+                                *row_chunk(M::kD + (uint32_t)l * kTile, c0 / 8 + 1) = make_uint4(pd[4], pd[5], pd[6], pd[7]);
+                            }
                         }
                     }
                     if (last) {
@@ -381,7 +428,7 @@ __global__ void __launch_bounds__(threads_for(CS), 1) learn_gradient_narrow_kern
                     release();
                 }
             }
-            // ---- backward: dA_l in the accumulator times the stored derivative gives dZ_{l-1}, written over A_l ----
+            // ---- backward: dA_l in the accumulator times the derivative gives dZ_{l-1}, written over A_l ----
 #pragma unroll
             for (int l = NL - 1; l >= 1; --l) {
                 wait_full();
@@ -397,13 +444,25 @@ __global__ void __launch_bounds__(threads_for(CS), 1) learn_gradient_narrow_kern
                         uint32_t v[16];
                         tmem_ld_32x16(t_acc + (uint32_t)c0, v);
                         tmem_ld_wait();
-                        const uint4 d0 = *row_chunk(M::kD + (uint32_t)(l - 1) * kTile, c0 / 8);
-                        const uint4 d1 = *row_chunk(M::kD + (uint32_t)(l - 1) * kTile, c0 / 8 + 1);
+                        const uint32_t dbuf = DFA ? M::kA + (uint32_t)l * kTile : M::kD + (uint32_t)(l - 1) * kTile;
+                        const uint4 d0 = *row_chunk(dbuf, c0 / 8);
+                        const uint4 d1 = *row_chunk(dbuf, c0 / 8 + 1);
                         const uint32_t dd[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
                         uint32_t pz[8];
 #pragma unroll
-                        for (int k = 0; k < 8; ++k)
-                            pz[k] = C::pack2(__uint_as_float(v[2 * k]) * C::lo(dd[k]), __uint_as_float(v[2 * k + 1]) * C::hi(dd[k]));
+                        for (int k = 0; k < 8; ++k) {
+                            float dl, dh;
+                            if constexpr (DFA) {
+                                // stored activation: positive -> 1, negative zero -> one half (z was 0), zero -> 0
+                                const uint32_t lo16 = dd[k] & 0xffffu, hi16 = dd[k] >> 16;
+                                dl = (lo16 & 0x7fffu) ? 1.0f : (lo16 ? 0.5f : 0.0f);
+                                dh = (hi16 & 0x7fffu) ? 1.0f : (hi16 ? 0.5f : 0.0f);
+                            } else {
+                                dl = C::lo(dd[k]);
+                                dh = C::hi(dd[k]);
+                            }
+                            pz[k] = C::pack2(__uint_as_float(v[2 * k]) * dl, __uint_as_float(v[2 * k + 1]) * dh);
+                        }
                         *row_chunk(M::kA + (uint32_t)l * kTile, c0 / 8) = make_uint4(pz[0], pz[1], pz[2], pz[3]);
                         *row_chunk(M::kA + (uint32_t)l * kTile, c0 / 8 + 1) = make_uint4(pz[4], pz[5], pz[6], pz[7]);
                     }
@@ -434,15 +493,20 @@ __global__ void __launch_bounds__(threads_for(CS), 1) learn_gradient_narrow_kern
         }
 
         // ---- one add per parameter per CTA: lane = output feature, column = input feature ----
-        if (ok && n_my_tiles > 0) ok = mbar_wait(tile_done, (n_my_tiles - 1) & 1u, abort_flag, p.status, kStatusEpi);
+        if (ok && n_chain_tiles > 0) ok = mbar_wait(tile_done, (n_chain_tiles - 1) & 1u, abort_flag, p.status, kStatusEpi);
+        // Every epilogue warp arrives here, whatever happened before: after this barrier the last product
+        // of every chain has completed (or the CTA is aborting).
+        asm volatile("bar.sync 1, %0;" ::"n"(128 * CS * NCH) : "memory");
         if (ok && !*abort_flag && n_my_tiles > 0) {
             tc_fence_after();
             const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
+            constexpr int GWF = H / (CS * NCH);               // columns per warp group in this read-out
+            const int fbeg = (h * CS + g) * GWF, fend = fbeg + GWF;
             for (int l = 0; l < NL; ++l) {
                 const int in = c.dims[l], out = c.dims[l + 1];
                 float* dW = (float*)p.net[l].weightsGrad;
                 float* dB = (float*)p.net[l].biasesGrad;
-                for (int c0 = cbeg; c0 < cend; c0 += 16) {
+                for (int c0 = fbeg; c0 < fend; c0 += 16) {
                     uint32_t v[16];
                     tmem_ld_32x16(lane_base + M::kColDW + (uint32_t)l * 64u + (uint32_t)c0, v);
                     tmem_ld_wait();
@@ -452,7 +516,7 @@ __global__ void __launch_bounds__(threads_for(CS), 1) learn_gradient_narrow_kern
                             if (c0 + i < in) atomicAdd(dW + (size_t)r * in + c0 + i, __uint_as_float(v[i]));
                     }
                 }
-                if (g == 0) {
+                if (h == 0 && g == 0) {
                     uint32_t b[16];
                     tmem_ld_32x16(lane_base + M::kColDB + (uint32_t)l * 16u, b);
                     tmem_ld_wait();
@@ -465,7 +529,7 @@ __global__ void __launch_bounds__(threads_for(CS), 1) learn_gradient_narrow_kern
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
                 sm += __shfl_xor_sync(0xffffffffu, sm, o);
             }
-            if (lane == 0 && g == 0) {   // the output columns, and with them the loss, live in group 0
+            if (lane == 0 && g == 0) {   // the output columns, and with them the loss, live in group 0 of each chain
                 atomicMax(p.loss_words, __float_as_uint(mx));
                 atomicAdd((float*)(p.loss_words + 1), sm);
             }
@@ -476,7 +540,7 @@ __global__ void __launch_bounds__(threads_for(CS), 1) learn_gradient_narrow_kern
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, Map<NL>::kTmemCols);
+        tmem_dealloc(tmem_base, M::kTmemCols);
     }
 }
 
@@ -492,14 +556,15 @@ bool tc_train_narrow_supported(const MlpConfig& c)
     return true;
 }
 
-template <int NL, int FMT, int HACT, int OACT, int CS>
+template <int NL, int FMT, int HACT, int OACT, int CS, int NCH = 1>
 static cudaError_t launch_narrow_cs(cudaStream_t st, TcWorkspace* ws, const narrow::Params& p)
 {
-    auto kern = narrow::learn_gradient_narrow_kernel<NL, FMT, HACT, OACT, CS>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)narrow::Map<NL>::kSmemBytes);
+    using M = narrow::Map<NL, NCH, (NCH > 1)>;
+    auto kern = narrow::learn_gradient_narrow_kernel<NL, FMT, HACT, OACT, CS, NCH>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)M::kSmemBytes);
     if (e != cudaSuccess) return e;
     const uint32_t grid = p.n_tiles < (uint32_t)ws->sm_count ? p.n_tiles : (uint32_t)ws->sm_count;
-    kern<<<grid, narrow::threads_for(CS), narrow::Map<NL>::kSmemBytes, st>>>(p);
+    kern<<<grid, narrow::threads_for(CS * NCH), M::kSmemBytes, st>>>(p);
     return cudaGetLastError();
 }
 
@@ -532,9 +597,22 @@ cudaError_t launch_learn_gradient_narrow(cudaStream_t st, TcWorkspace* ws, const
     // the two benchmark shapes get their activations as compile-time constants
     if (c.n_layers == 5 && c.dtype == MLP_F16 && c.hidden_act == MLP_ACT_LEAKY_RELU && c.output_act == MLP_ACT_IDENTITY)
         e = launch_narrow<5, MLP_F16, MLP_ACT_LEAKY_RELU, MLP_ACT_IDENTITY>(st, ws, p);
-    else if (c.n_layers == 4 && c.dtype == MLP_F16 && c.hidden_act == MLP_ACT_RELU && c.output_act == MLP_ACT_SIGMOID)
-        e = launch_narrow<4, MLP_F16, MLP_ACT_RELU, MLP_ACT_SIGMOID>(st, ws, p);
-    else {
+    else if (c.n_layers == 4 && c.dtype == MLP_F16 && c.hidden_act == MLP_ACT_RELU && c.output_act == MLP_ACT_SIGMOID) {
+        // ReLU, four layers, few outputs: two tiles in flight per CTA (two column groups each)
+        if (c.dims[4] <= narrow::H / 2 && p.n_tiles > (uint32_t)ws->sm_count)
+            e = launch_narrow_cs<4, MLP_F16, MLP_ACT_RELU, MLP_ACT_SIGMOID, 2, 2>(st, ws, p);
+        else
+            e = launch_narrow<4, MLP_F16, MLP_ACT_RELU, MLP_ACT_SIGMOID>(st, ws, p);
+    }
+    else if (c.hidden_act == MLP_ACT_RELU && c.n_layers >= 2 && c.n_layers <= 4 && c.dims[c.n_layers] <= narrow::H / 2 &&
+             p.n_tiles > (uint32_t)ws->sm_count) {
+        // any ReLU network of up to four layers with few outputs: two tiles in flight per CTA
+#define MLPB200_NARROW2(NL_) \
+    if (c.n_layers == NL_) e = c.dtype == MLP_BF16 ? launch_narrow_cs<NL_, MLP_BF16, MLP_ACT_RELU, -1, 2, 2>(st, ws, p) \
+                                                   : launch_narrow_cs<NL_, MLP_F16, MLP_ACT_RELU, -1, 2, 2>(st, ws, p);
+        MLPB200_NARROW2(2) MLPB200_NARROW2(3) MLPB200_NARROW2(4)
+#undef MLPB200_NARROW2
+    } else {
 #define MLPB200_NARROW(NL_) \
     if (c.n_layers == NL_) e = c.dtype == MLP_BF16 ? launch_narrow<NL_, MLP_BF16, -1, -1>(st, ws, p) : launch_narrow<NL_, MLP_F16, -1, -1>(st, ws, p);
         MLPB200_NARROW(2) MLPB200_NARROW(3) MLPB200_NARROW(4) MLPB200_NARROW(5)

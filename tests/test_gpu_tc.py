@@ -140,6 +140,28 @@ def test_narrow_kernel_other_shapes(device, dims):
     assert abs(l_gpu[0][0] - l_ref[0][0]) <= 1e-2 * abs(l_ref[0][0])
 
 
+@pytest.mark.parametrize("dims,dtype", [([32, 64, 64, 3], C.F16), ([10, 40, 12], C.BF16), ([64, 64, 64, 64, 32], C.BF16)])
+def test_narrow_kernel_two_tiles_in_flight(device, dims, dtype):
+    """ReLU networks of up to four layers run two tiles per CTA once there are more tiles than SMs; the
+    derivative is recovered from the stored activation (negative zero marks a zero pre-activation).  Inputs
+    with many exact zeros exercise the tie: zero inputs and zero biases give zero pre-activations."""
+    rng = np.random.default_rng(len(dims) * 7 + dims[0])
+    cfg = C.make_config(dims, dtype=dtype, hidden_act=C.ACT_RELU, output_act=C.ACT_IDENTITY, adam_master=1)
+    p0 = C.init_params(cfg, seed=8, scheme="kaiming")   # biases start at zero
+    count = 128 * 148 * 2 + 77
+    x = rng.uniform(-1, 1, (count, dims[0])).astype(np.float32)
+    x[::5] = 0.0                                         # every fifth sample: all pre-activations of layer 0 are zero
+    t = rng.uniform(-1, 1, (count, dims[-1])).astype(np.float32)
+    _, l_ref, g_ref, _ = oracle_trajectory(cfg, p0, [(x, t)], n_threads=8)
+    _, l_gpu, g_gpu, _, tr = gpu_trajectory(device, cfg, p0, [(x, t)])
+    assert tr.k_learn.implementation == "tcgen05"
+    err = _grad_layer_errs(cfg, g_gpu, g_ref)
+    print(dims, "worst per-tensor gradient rel err %.3g" % err)
+    assert err < 1e-2
+    assert abs(l_gpu[0][1] - l_ref[0][1]) <= 1e-2 * abs(l_ref[0][1])
+    assert abs(l_gpu[0][0] - l_ref[0][0]) <= 1e-2 * abs(l_ref[0][0])
+
+
 @pytest.mark.parametrize("name,count,steps", [("c2", 2048, 10), ("c3", 1024, 10)])
 def test_narrow_network_trajectories(device, name, count, steps):
     cfg, p0, batches = make_problem(name, count, seed=3, steps=steps)
