@@ -39,13 +39,11 @@ namespace narrow {
 
 using namespace layout;
 
-constexpr int H = 64;         // padded width of every layer
+constexpr int HMAX = 64;      // widest padded layer; the kernel is built for padded widths H = 64 and H = 32
 constexpr int TS = 128;       // samples per tile
 // Threads: warp 0 issues the products, warp 1 owns the tensor-memory allocation, then CS groups of four
-// epilogue warps; group g handles columns [g * 64 / CS, (g + 1) * 64 / CS) of every row.
+// epilogue warps; group g handles columns [g * H / CS, (g + 1) * H / CS) of every row (H: the padded width).
 constexpr int threads_for(int cs) { return 64 + 128 * cs; }
-constexpr uint32_t kMat = 64 * 64 * 2;     // one padded weight matrix: 64 rows of 128 bytes
-constexpr uint32_t kTile = 128 * 64 * 2;   // one [128][64] operand tile: 128 rows of 128 bytes
 
 enum : uint32_t { kStatusCtrl = 0x1000u, kStatusEpi = 0x2000u };
 
@@ -89,8 +87,10 @@ template <> struct Cvt<MLP_F16> {
 
 // Shared-memory map for NL layers and NCH tiles in flight (bytes from a 1024-aligned base).  DFA: the
 // activation derivative is read back from the stored activation instead of being kept in its own buffer.
-template <int NL, int NCH, bool DFA>
+template <int NL, int NCH, bool DFA, int H>
 struct Map {
+    static constexpr uint32_t kMat = H * H * 2;                // one padded weight matrix: H rows of 2 H bytes
+    static constexpr uint32_t kTile = 128 * H * 2;             // one [128][H] operand tile
     static constexpr uint32_t kW = 0;                          // NL padded weight matrices
     static constexpr uint32_t kChain = kW + NL * kMat;         // per tile in flight:
     static constexpr uint32_t kA = 0;                          //   A_0 .. A_{NL-1}: layer inputs; dZ_{l-1} later replaces A_l
@@ -98,13 +98,13 @@ struct Map {
     static constexpr uint32_t kDZ = kD + (DFA ? 0 : (NL - 1) * kTile);   //   dZ of the last layer
     static constexpr uint32_t kChainBytes = kDZ + kTile;
     static constexpr uint32_t kOnes = kChain + NCH * kChainBytes;  // [128 rows][16 elements]: first column one, rest zero
-    static constexpr uint32_t kBias = kOnes + 128 * 32;        // fp32 [NL][64]
-    static constexpr uint32_t kBars = kBias + NL * 64 * 4;     // per chain: acc_full, acc_free, tile_done
+    static constexpr uint32_t kBias = kOnes + 128 * 32;        // fp32 [NL][H]
+    static constexpr uint32_t kBars = kBias + NL * H * 4;      // per chain: acc_full, acc_free, tile_done
     static constexpr uint32_t kTmemPtr = kBars + 3 * NCH * 8;
     static constexpr uint32_t kAbort = kTmemPtr + 4;
     static constexpr uint32_t kSmemBytes = kAbort + 4 + 1024;
     // tensor-memory columns: one working accumulator per chain, then the gradients (shared by the chains)
-    static constexpr uint32_t kColAcc = 0, kColDW = 64 * NCH, kColDB = kColDW + 64 * NL, kTmemCols = 512;
+    static constexpr uint32_t kColAcc = 0, kColDW = H * NCH, kColDB = kColDW + H * NL, kTmemCols = 512;
     static_assert(kColDB + 16 * NL <= 512, "tensor memory budget");
     static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 };
@@ -115,19 +115,24 @@ struct Map {
 // the group that holds the output columns, so CS > 1 needs the output width to fit one group (64 / CS).
 // NCH: tiles in flight per CTA ("chains"): each has its own operand buffers, working accumulator,
 // barriers and epilogue warps, and both accumulate into the same gradient columns; while one chain's
-// epilogue runs, the tensor pipe works on the other chain's product.  NCH = 2 needs the derivative-
-// from-activation form (ReLU only): the forward epilogue stores max(z, 0) and marks z == 0 with a
-// negative zero, so the backward epilogue recovers the derivative 1 / one half / 0 exactly from the
-// stored value (a negative zero is a zero to every product that reads the buffer).
-template <int NL, int FMT, int HACT, int OACT, int CS, int NCH>
+// epilogue runs, the tensor pipe works on the other chain's product.
+// DFA: derivative-from-activation form (ReLU only), which frees the derivative buffers: the forward
+// epilogue stores max(z, 0) and marks z == 0 with a negative zero, so the backward epilogue recovers
+// the derivative 1 / one half / 0 exactly from the stored value (a negative zero is a zero to every
+// product that reads the buffer).
+// H: the padded width of every layer, 64 (128-byte operand rows, 128-byte swizzle) or 32 (64-byte rows,
+// 64-byte swizzle; a quarter of the shared memory and half of the epilogue work per tile).
+template <int NL, int FMT, int HACT, int OACT, int CS, int NCH, bool DFA, int H>
 __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narrow_kernel(const Params p)
 {
     constexpr int kThreads = threads_for(CS * NCH);
     constexpr int GW = H / CS;   // columns per epilogue group
-    constexpr bool DFA = NCH > 1;
+    static_assert(H == 64 || H == 32, "padded width");
+    static_assert(GW % 16 == 0, "an epilogue group works on whole 16-column accumulator reads");
     static_assert(!DFA || HACT == MLP_ACT_RELU, "the derivative is recovered from the activation only for ReLU");
-    using M = Map<NL, NCH, DFA>;
+    using M = Map<NL, NCH, DFA, H>;
     using C = Cvt<FMT>;
+    constexpr uint32_t kMat = M::kMat, kTile = M::kTile;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const uint32_t sbase = smem_u32(smem);
@@ -187,16 +192,18 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
             constexpr uint32_t kIdDw = umma_idesc(F, 1, 1, 128, H);    // dZ^T (MN) x acts (MN)
             constexpr uint32_t kIdDb = umma_idesc(F, 1, 1, 128, 16);   // dZ^T (MN) x ones (MN)
             const uint32_t lo_base = (sbase & 0x3FFFFu) >> 4;
-            constexpr uint32_t kHi128 = (1024u >> 4) | (1u << 14) | (2u << 29);  // 128-byte rows and swizzle
+            // operand rows of 2 H bytes with the swizzle of that span; groups of eight rows are 16 H bytes apart
+            constexpr uint32_t kRow = (uint32_t)row_bytes(H);
+            constexpr uint32_t kHi128 = ((8u * kRow) >> 4) | (1u << 14) | (layout_type(H) << 29);
             constexpr uint32_t kHi32 = (256u >> 4) | (1u << 14) | (6u << 29);    // 32-byte rows and swizzle (ones column)
-            // K-major [rows][64]: a K step of 16 elements is 32 bytes inside the 128-byte row.
+            // K-major [rows][H]: a K step of 16 elements is 32 bytes inside the row.
             auto desc_k = [&](uint32_t buf, int k) -> uint64_t {
                 return ((uint64_t)kHi128 << 32) | (lo_base + ((buf + (uint32_t)k * 32u) >> 4) + (1u << 16));
             };
-            // MN-major [K rows][64]: a K step of 16 rows is 2048 bytes; a second 64-element block, where the
-            // instruction asks for 128, starts 16 bytes further (its results are never read).
+            // MN-major [K rows][H]: a K step is 16 rows; a further H-element block, where the instruction
+            // asks for 128 rows of output, starts 16 bytes further (its results are never read).
             auto desc_mn = [&](uint32_t buf, int k) -> uint64_t {
-                return ((uint64_t)kHi128 << 32) | (lo_base + ((buf + (uint32_t)k * 2048u) >> 4) + (1u << 16));
+                return ((uint64_t)kHi128 << 32) | (lo_base + ((buf + (uint32_t)k * 16u * kRow) >> 4) + (1u << 16));
             };
             auto desc_ones = [&](int k) -> uint64_t {
                 return ((uint64_t)kHi32 << 32) | (lo_base + ((M::kOnes + (uint32_t)k * 512u) >> 4) + (1u << 16));
@@ -214,7 +221,7 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
             auto grads = [&](int l, uint32_t dzbuf, uint32_t abuf, bool first) {
 #pragma unroll
                 for (int k = 0; k < TS / 16; ++k) {
-                    umma_f16(tmem_base + M::kColDW + (uint32_t)l * 64u, desc_mn(dzbuf, k), desc_mn(abuf, k), kIdDw,
+                    umma_f16(tmem_base + M::kColDW + (uint32_t)(l * H), desc_mn(dzbuf, k), desc_mn(abuf, k), kIdDw,
                              (first && k == 0) ? 0u : 1u);
                     umma_f16(tmem_base + M::kColDB + (uint32_t)l * 16u, desc_mn(dzbuf, k), desc_ones(k), kIdDb, (first && k == 0) ? 0u : 1u);
                 }
@@ -233,7 +240,7 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
                             if (leader) {
 #pragma unroll
                                 for (int k = 0; k < H / 16; ++k)
-                                    umma_f16(tmem_base + M::kColAcc + (uint32_t)h * 64u, desc_k(cb + M::kA + (uint32_t)l * kTile, k),
+                                    umma_f16(tmem_base + M::kColAcc + (uint32_t)(h * H), desc_k(cb + M::kA + (uint32_t)l * kTile, k),
                                              desc_k(M::kW + (uint32_t)l * kMat, k), kIdFwd, k > 0);
                                 umma_commit(&bars[3 * h + 0]);
                             }
@@ -254,7 +261,7 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
                             if (leader) {
 #pragma unroll
                                 for (int k = 0; k < H / 16; ++k)
-                                    umma_f16(tmem_base + M::kColAcc + (uint32_t)h * 64u, desc_k(dzbuf, k), desc_mn(M::kW + (uint32_t)l * kMat, k),
+                                    umma_f16(tmem_base + M::kColAcc + (uint32_t)(h * H), desc_k(dzbuf, k), desc_mn(M::kW + (uint32_t)l * kMat, k),
                                              kIdDx, k > 0);
                                 grads(l, dzbuf, cb + M::kA + (uint32_t)l * kTile, rd == 0 && h == 0);
                                 umma_commit(&bars[3 * h + 0]);
@@ -275,7 +282,7 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
                                 // the input gradient dA_0 = dZ_0 . W_0, wanted by an encoder in front of the network
 #pragma unroll
                                 for (int k = 0; k < H / 16; ++k)
-                                    umma_f16(tmem_base + M::kColAcc + (uint32_t)h * 64u, desc_k(dz0, k), desc_mn(M::kW, k), kIdDx, k > 0);
+                                    umma_f16(tmem_base + M::kColAcc + (uint32_t)(h * H), desc_k(dz0, k), desc_mn(M::kW, k), kIdDx, k > 0);
                             }
                             grads(0, dz0, cb + M::kA, rd == 0 && h == 0);
                             if (p.input_grads) umma_commit(&bars[3 * h + 0]);
@@ -298,7 +305,7 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
         uint64_t* acc_free = &bars[3 * h + 1];
         uint64_t* tile_done = &bars[3 * h + 2];
         const uint32_t cb = M::kChain + (uint32_t)h * M::kChainBytes;
-        const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16) + M::kColAcc + (uint32_t)h * 64u;
+        const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16) + M::kColAcc + (uint32_t)(h * H);
         const int od = c.dims[NL];
         const int hact = HACT >= 0 ? HACT : c.hidden_act;
         const int oact = OACT >= 0 ? OACT : c.output_act;
@@ -500,15 +507,15 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
         if (ok && !*abort_flag && n_my_tiles > 0) {
             tc_fence_after();
             const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
-            constexpr int GWF = H / (CS * NCH);               // columns per warp group in this read-out
-            const int fbeg = (h * CS + g) * GWF, fend = fbeg + GWF;
+            // the warp groups of all chains share the columns: group i takes the 16-column pieces i, i + G, ...
+            constexpr int G = CS * NCH;
             for (int l = 0; l < NL; ++l) {
                 const int in = c.dims[l], out = c.dims[l + 1];
                 float* dW = (float*)p.net[l].weightsGrad;
                 float* dB = (float*)p.net[l].biasesGrad;
-                for (int c0 = fbeg; c0 < fend; c0 += 16) {
+                for (int c0 = (h * CS + g) * 16; c0 < H; c0 += 16 * G) {
                     uint32_t v[16];
-                    tmem_ld_32x16(lane_base + M::kColDW + (uint32_t)l * 64u + (uint32_t)c0, v);
+                    tmem_ld_32x16(lane_base + M::kColDW + (uint32_t)(l * H) + (uint32_t)c0, v);
                     tmem_ld_wait();
                     if (r < out) {
 #pragma unroll
@@ -551,16 +558,16 @@ bool tc_train_narrow_supported(const MlpConfig& c)
     if (c.n_layers < 2 || c.n_layers > 5) return false;
     if (c.dtype != MLP_BF16 && c.dtype != MLP_F16) return false;
     for (int l = 0; l <= c.n_layers; ++l)
-        if (c.dims[l] > narrow::H) return false;
+        if (c.dims[l] > narrow::HMAX) return false;
     if (c.encoding == MLP_ENC_FREQ2D && c.dims[0] != 32) return false;
     return true;
 }
 
-template <int NL, int FMT, int HACT, int OACT, int CS, int NCH = 1>
+template <int NL, int FMT, int HACT, int OACT, int CS, int NCH = 1, bool DFA = false, int H = narrow::HMAX>
 static cudaError_t launch_narrow_cs(cudaStream_t st, TcWorkspace* ws, const narrow::Params& p)
 {
-    using M = narrow::Map<NL, NCH, (NCH > 1)>;
-    auto kern = narrow::learn_gradient_narrow_kernel<NL, FMT, HACT, OACT, CS, NCH>;
+    using M = narrow::Map<NL, NCH, DFA, H>;
+    auto kern = narrow::learn_gradient_narrow_kernel<NL, FMT, HACT, OACT, CS, NCH, DFA, H>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)M::kSmemBytes);
     if (e != cudaSuccess) return e;
     const uint32_t grid = p.n_tiles < (uint32_t)ws->sm_count ? p.n_tiles : (uint32_t)ws->sm_count;
@@ -573,8 +580,8 @@ template <int NL, int FMT, int HACT, int OACT>
 static cudaError_t launch_narrow(cudaStream_t st, TcWorkspace* ws, const narrow::Params& p)
 {
     const int od = p.cfg.dims[NL];
-    if (od <= narrow::H / 4) return launch_narrow_cs<NL, FMT, HACT, OACT, 4>(st, ws, p);
-    if (od <= narrow::H / 2) return launch_narrow_cs<NL, FMT, HACT, OACT, 2>(st, ws, p);
+    if (od <= narrow::HMAX / 4) return launch_narrow_cs<NL, FMT, HACT, OACT, 4>(st, ws, p);
+    if (od <= narrow::HMAX / 2) return launch_narrow_cs<NL, FMT, HACT, OACT, 2>(st, ws, p);
     return launch_narrow_cs<NL, FMT, HACT, OACT, 1>(st, ws, p);
 }
 
@@ -594,22 +601,35 @@ cudaError_t launch_learn_gradient_narrow(cudaStream_t st, TcWorkspace* ws, const
     p.count = a.count;
     p.n_tiles = (a.count + narrow::TS - 1) / narrow::TS;
     cudaError_t e = cudaErrorInvalidValue;
+    // Networks whose every width fits 32 (and whose outputs fit one 16-column epilogue group) run the
+    // 32-wide build: operand tiles a quarter of the size, so two tiles are in flight with every buffer kept.
+    bool fits32 = c.dims[c.n_layers] <= 16;
+    for (int l = 0; l <= c.n_layers; ++l) fits32 = fits32 && c.dims[l] <= 32;
     // the two benchmark shapes get their activations as compile-time constants
-    if (c.n_layers == 5 && c.dtype == MLP_F16 && c.hidden_act == MLP_ACT_LEAKY_RELU && c.output_act == MLP_ACT_IDENTITY)
+    if (fits32 && c.n_layers == 5 && c.dtype == MLP_F16 && c.hidden_act == MLP_ACT_LEAKY_RELU && c.output_act == MLP_ACT_IDENTITY)
+        e = launch_narrow_cs<5, MLP_F16, MLP_ACT_LEAKY_RELU, MLP_ACT_IDENTITY, 2, 2, false, 32>(st, ws, p);
+    else if (fits32) {
+#define MLPB200_NARROW32(NL_) \
+    if (c.n_layers == NL_) e = c.dtype == MLP_BF16 ? launch_narrow_cs<NL_, MLP_BF16, -1, -1, 2, 2, false, 32>(st, ws, p) \
+                                                   : launch_narrow_cs<NL_, MLP_F16, -1, -1, 2, 2, false, 32>(st, ws, p);
+        MLPB200_NARROW32(2) MLPB200_NARROW32(3) MLPB200_NARROW32(4) MLPB200_NARROW32(5)
+#undef MLPB200_NARROW32
+    }
+    else if (c.n_layers == 5 && c.dtype == MLP_F16 && c.hidden_act == MLP_ACT_LEAKY_RELU && c.output_act == MLP_ACT_IDENTITY)
         e = launch_narrow<5, MLP_F16, MLP_ACT_LEAKY_RELU, MLP_ACT_IDENTITY>(st, ws, p);
     else if (c.n_layers == 4 && c.dtype == MLP_F16 && c.hidden_act == MLP_ACT_RELU && c.output_act == MLP_ACT_SIGMOID) {
         // ReLU, four layers, few outputs: two tiles in flight per CTA (two column groups each)
-        if (c.dims[4] <= narrow::H / 2 && p.n_tiles > (uint32_t)ws->sm_count)
-            e = launch_narrow_cs<4, MLP_F16, MLP_ACT_RELU, MLP_ACT_SIGMOID, 2, 2>(st, ws, p);
+        if (c.dims[4] <= narrow::HMAX / 2 && p.n_tiles > (uint32_t)ws->sm_count)
+            e = launch_narrow_cs<4, MLP_F16, MLP_ACT_RELU, MLP_ACT_SIGMOID, 2, 2, true>(st, ws, p);
         else
             e = launch_narrow<4, MLP_F16, MLP_ACT_RELU, MLP_ACT_SIGMOID>(st, ws, p);
     }
-    else if (c.hidden_act == MLP_ACT_RELU && c.n_layers >= 2 && c.n_layers <= 4 && c.dims[c.n_layers] <= narrow::H / 2 &&
+    else if (c.hidden_act == MLP_ACT_RELU && c.n_layers >= 2 && c.n_layers <= 4 && c.dims[c.n_layers] <= narrow::HMAX / 2 &&
              p.n_tiles > (uint32_t)ws->sm_count) {
         // any ReLU network of up to four layers with few outputs: two tiles in flight per CTA
 #define MLPB200_NARROW2(NL_) \
-    if (c.n_layers == NL_) e = c.dtype == MLP_BF16 ? launch_narrow_cs<NL_, MLP_BF16, MLP_ACT_RELU, -1, 2, 2>(st, ws, p) \
-                                                   : launch_narrow_cs<NL_, MLP_F16, MLP_ACT_RELU, -1, 2, 2>(st, ws, p);
+    if (c.n_layers == NL_) e = c.dtype == MLP_BF16 ? launch_narrow_cs<NL_, MLP_BF16, MLP_ACT_RELU, -1, 2, 2, true>(st, ws, p) \
+                                                   : launch_narrow_cs<NL_, MLP_F16, MLP_ACT_RELU, -1, 2, 2, true>(st, ws, p);
         MLPB200_NARROW2(2) MLPB200_NARROW2(3) MLPB200_NARROW2(4)
 #undef MLPB200_NARROW2
     } else {
