@@ -1,10 +1,12 @@
 // learnGradient on the tensor cores for narrow networks: every layer width <= 64 (the fp16 CoopVec-style
 // network 4-32-32-32-32-4 and the neural-texture network enc(2->32)-64-64-64-3).
 //
-// Every layer is padded to 64 x 64 in shared memory (zero rows and columns), so one kernel shape
-// serves all such networks: padded features stay exactly zero through the forward and backward pass.
+// Every layer is padded to H x H in shared memory (zero rows and columns; H = 64, or 32 when every width
+// fits), so one kernel shape serves all such networks: padded features stay exactly zero through the
+// forward and backward pass.  Up to two tiles are in flight per CTA, each with its own operand buffers,
+// working accumulator and epilogue warps.  (The shapes below are written for H = 64.)
 // Orientation: the 128 samples of a tile run along the TMEM lanes (the MMA's M), features along the
-// columns; an epilogue thread owns one sample.
+// columns; an epilogue thread owns one sample row (or a column group of it).
 //   forward   Z_l [128 x 64]  = A_l [128 x 64] . W_l^T        A: A_l, K-major          B: W_l [out][in], K-major
 //   input     dA_l [128 x 64] = dZ_l [128 x 64] . W_l          A: dZ_l, K-major         B: W_l, MN-major
 //   weights   dW_l [64 x 64] += dZ_l^T . A_l                   A: dZ_l, MN-major        B: A_l, MN-major (K = 128 samples)
