@@ -36,7 +36,7 @@ int32_t fail(int32_t code, const char* fmt, ...)
         if (e_ != cudaSuccess) return fail(MLP_E_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e_)); \
     } while (0)
 
-enum class Entry { ExampleLearn, ExampleLearnCoopVec, ExampleAdjust, Learn, LearnSimt, Adjust, Forward, ForwardSimt, Module };
+enum class Entry { ExampleLearn, ExampleLearnCoopVec, ExampleAdjust, Learn, LearnSimt, Adjust, Forward, ForwardNarrow, ForwardSimt, Module };
 
 // Driver entry points for caller-supplied device modules, resolved through the runtime so that the
 // library carries no link-time dependency on the driver library.
@@ -284,6 +284,7 @@ int32_t mlp_kernel_get_for_config(MlpDevice* d, const MlpConfig* config, const c
     else if (!std::strcmp(entry_point, "adjustParameters")) k->entry = Entry::Adjust;
     else if (!std::strcmp(entry_point, "forward")) {
         if (tc_forward_supported(*config)) { k->entry = Entry::Forward; k->impl = "tcgen05"; }
+        else if (tc_train_narrow_supported(*config)) { k->entry = Entry::ForwardNarrow; k->impl = "tcgen05"; }
         else k->entry = Entry::ForwardSimt;
     } else if (!std::strcmp(entry_point, "forward_simt")) k->entry = Entry::ForwardSimt;
     else { delete k; return fail(MLP_E_NOT_AVAILABLE, "no entry point named '%s'", entry_point); }
@@ -435,14 +436,16 @@ int32_t mlp_dispatch(MlpDevice* d, MlpKernel* k, const void* args, size_t args_s
         break;
     }
     case Entry::Forward:
+    case Entry::ForwardNarrow:
     case Entry::ForwardSimt: {
         if (args_size != sizeof(MlpForwardParams)) return fail(MLP_E_INVALID_ARG, "forward expects %zu argument bytes, got %zu", sizeof(MlpForwardParams), args_size);
         MlpForwardParams a; std::memcpy(&a, args, sizeof a);
         if ((uint64_t)gx * 256 < a.count) return fail(MLP_E_INVALID_ARG, "grid of %u groups does not cover %u samples", gx, a.count);
         if (!a.networkBuffer || (a.count && (!a.inputs || !a.outputs))) return fail(MLP_E_INVALID_ARG, "null device address in the argument struct");
         if ((a.flags & MLP_FLAG_OUTPUT_STORAGE_TYPE) && k->entry != Entry::Forward)
-            return fail(MLP_E_NOT_AVAILABLE, "MLP_FLAG_OUTPUT_STORAGE_TYPE needs the tensor-core forward kernel");
+            return fail(MLP_E_NOT_AVAILABLE, "MLP_FLAG_OUTPUT_STORAGE_TYPE needs the constant-width tensor-core forward kernel");
         if (k->entry == Entry::Forward) e = launch_forward_tc(d->stream, d->tc, k->cfg, a, &launches, &err);
+        else if (k->entry == Entry::ForwardNarrow) e = launch_forward_narrow(d->stream, d->tc, k->cfg, a, &launches, &err);
         else e = launch_forward_simt(d->stream, k->cfg, a, &launches, &err);
         break;
     }

@@ -47,6 +47,10 @@ cudaError_t launch_learn_gradient_tc(cudaStream_t st, TcWorkspace* ws, const Mlp
 cudaError_t launch_learn_gradient_narrow(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c,
                                          const MlpLearnGradParamsEx& a, int* launches, std::string* err,
                                          float* input_grads = nullptr);
+// Forward pass of the same padded kernel (any widths up to 64, any activation, input conversion or the
+// frequency encoding); fp32 outputs.
+cudaError_t launch_forward_narrow(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const MlpForwardParams& a,
+                                  int* launches, std::string* err);
 // Cycle counts CTA 0 of the last tensor-core learnGradient recorded (diagnostics).
 cudaError_t tc_read_timing(cudaStream_t st, TcWorkspace* ws, unsigned long long* out8);
 // Reads and clears the device status word (0 = no kernel gave up on a bounded wait).

@@ -57,6 +57,7 @@ struct Params {
     const void* inputs;
     const void* targets;
     float* input_grads;   // optional: [count][dims[0]] gradient with respect to the (unencoded) inputs
+    float* outputs;       // optional: forward only; fp32 [count][dims[n_layers]] network outputs, nothing else is written
     uint32_t count;
     uint32_t n_tiles;
 };
@@ -250,6 +251,7 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
                         }
                     }
                 }
+                if (p.outputs) continue;   // forward only: the next round's layer 0 waits for the epilogue as usual
                 // ---- backward ----
 #pragma unroll
                 for (int l = NL - 1; l >= 1; --l) {
@@ -334,7 +336,9 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
             const uint64_t sample = tile * TS + (uint64_t)r;
             const bool valid = sample < p.count;
             // ---- the input row: conversion (and zero padding) or the frequency encoding ----
-            if (it > 0) ok = ok && mbar_wait(tile_done, (it - 1) & 1u, abort_flag, p.status, kStatusEpi);
+            // training: dW_0 of the chain's previous tile still reads A_0 until tile_done; forward only: the
+            // layer-0 product that read it has long completed (its accumulator was consumed)
+            if (it > 0 && !p.outputs) ok = ok && mbar_wait(tile_done, (it - 1) & 1u, abort_flag, p.status, kStatusEpi);
             if (!ok) break;
             {
 #pragma unroll
@@ -372,6 +376,27 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
                     const bool last = (l == NL - 1);
                     float loss = 0.0f;
                     const int width = c.dims[l + 1];  // real features of this layer; the padding beyond stays zero
+                    if (last && p.outputs) {
+                        // forward only: the output activation of the real columns goes to global memory.  No
+                        // separate release: the release after the next tile's input row (same warps, program
+                        // order) tells the control warp that this accumulator is drained.
+#pragma unroll
+                        for (int c0 = cbeg; c0 < cend; c0 += 16) {
+                            if (c0 >= width) continue;
+                            uint32_t v[16];
+                            tmem_ld_32x16(t_acc + (uint32_t)c0, v);
+                            tmem_ld_wait();
+                            if (valid) {
+                                float* dst = p.outputs + sample * (uint64_t)od + c0;
+#pragma unroll
+                                for (int i = 0; i < 16; ++i)
+                                    if (c0 + i < od)
+                                        dst[i] = act_value(oact, c.act_alpha, C::round(__uint_as_float(v[i]) + s_bias[l * H + c0 + i]));
+                            }
+                        }
+                        tc_fence_before();
+                        continue;
+                    }
 #pragma unroll
                     for (int c0 = cbeg; c0 < cend; c0 += 16) {
                         const uint32_t abuf = last ? M::kDZ : M::kA + (uint32_t)(l + 1) * kTile;
@@ -424,7 +449,7 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
                         *row_chunk(abuf, c0 / 8) = make_uint4(pa[0], pa[1], pa[2], pa[3]);
                         *row_chunk(abuf, c0 / 8 + 1) = make_uint4(pa[4], pa[5], pa[6], pa[7]);
                         if constexpr (!DFA) {
-                            if (!last) {
+                            if (!last && !p.outputs) {
                                 *row_chunk(M::kD + (uint32_t)l * kTile, c0 / 8) = make_uint4(pd[0], pd[1], pd[2], pd[3]);
                                 *row_chunk(M::kD + (uint32_t)l * kTile, c0 / 8 + 1) = make_uint4(pd[4], pd[5], pd[6], pd[7]);
                             }
@@ -437,6 +462,7 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
                     release();
                 }
             }
+            if (p.outputs) continue;   // forward only
             // ---- backward: dA_l in the accumulator times the derivative gives dZ_{l-1}, written over A_l ----
 #pragma unroll
             for (int l = NL - 1; l >= 1; --l) {
@@ -502,11 +528,11 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
         }
 
         // ---- one add per parameter per CTA: lane = output feature, column = input feature ----
-        if (ok && n_chain_tiles > 0) ok = mbar_wait(tile_done, (n_chain_tiles - 1) & 1u, abort_flag, p.status, kStatusEpi);
+        if (ok && n_chain_tiles > 0 && !p.outputs) ok = mbar_wait(tile_done, (n_chain_tiles - 1) & 1u, abort_flag, p.status, kStatusEpi);
         // Every epilogue warp arrives here, whatever happened before: after this barrier the last product
         // of every chain has completed (or the CTA is aborting).
         asm volatile("bar.sync 1, %0;" ::"n"(128 * CS * NCH) : "memory");
-        if (ok && !*abort_flag && n_my_tiles > 0) {
+        if (ok && !*abort_flag && n_my_tiles > 0 && !p.outputs) {
             tc_fence_after();
             const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
             // the warp groups of all chains share the columns: group i takes the 16-column pieces i, i + G, ...
@@ -587,6 +613,28 @@ static cudaError_t launch_narrow(cudaStream_t st, TcWorkspace* ws, const narrow:
     return launch_narrow_cs<NL, FMT, HACT, OACT, 1>(st, ws, p);
 }
 
+static cudaError_t launch_narrow_any(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const narrow::Params& p);
+
+cudaError_t launch_forward_narrow(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const MlpForwardParams& a,
+                                  int* launches, std::string* err)
+{
+    if (!tc_train_narrow_supported(c)) { if (err) *err = "shape not built for the narrow tensor-core path"; return cudaErrorInvalidValue; }
+    if (a.count == 0) return cudaSuccess;
+    narrow::Params p;
+    p.cfg = c;
+    p.net = (const MlpLayerPointers*)a.networkBuffer;
+    p.loss_words = nullptr;
+    p.status = ws->status;
+    p.inputs = (const void*)a.inputs;
+    p.targets = nullptr;
+    p.input_grads = nullptr;
+    p.outputs = (float*)a.outputs;
+    p.count = a.count;
+    p.n_tiles = (a.count + narrow::TS - 1) / narrow::TS;
+    *launches += 1;
+    return launch_narrow_any(st, ws, c, p);
+}
+
 cudaError_t launch_learn_gradient_narrow(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const MlpLearnGradParamsEx& a,
                                          int* launches, std::string* err, float* input_grads)
 {
@@ -600,8 +648,16 @@ cudaError_t launch_learn_gradient_narrow(cudaStream_t st, TcWorkspace* ws, const
     p.inputs = (const void*)a.inputs;
     p.targets = (const void*)a.targets;
     p.input_grads = input_grads;
+    p.outputs = nullptr;
     p.count = a.count;
     p.n_tiles = (a.count + narrow::TS - 1) / narrow::TS;
+    *launches += 1;
+    return launch_narrow_any(st, ws, c, p);
+}
+
+// Picks the build of the kernel for the shape: padded width, tiles in flight, column split, activations.
+static cudaError_t launch_narrow_any(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const narrow::Params& p)
+{
     cudaError_t e = cudaErrorInvalidValue;
     // Networks whose every width fits 32 (and whose outputs fit one 16-column epilogue group) run the
     // 32-wide build: operand tiles a quarter of the size, so two tiles are in flight with every buffer kept.
@@ -640,7 +696,6 @@ cudaError_t launch_learn_gradient_narrow(cudaStream_t st, TcWorkspace* ws, const
         MLPB200_NARROW(2) MLPB200_NARROW(3) MLPB200_NARROW(4) MLPB200_NARROW(5)
 #undef MLPB200_NARROW
     }
-    *launches += 1;
     return e;
 }
 

@@ -19,7 +19,10 @@ def device():
 def _forward(device, cfg, params, x, count, entry):
     from slang_b200.api import Trainer
     tr = Trainer(device, cfg, params, forward_entry=entry)
-    xb = device.create_buffer(max(x.nbytes, 16), x if x.nbytes else None)
+    xin = np.ascontiguousarray(x).view(np.uint8).reshape(-1)
+    if xin.size < 16:
+        xin = np.concatenate([xin, np.zeros(16 - xin.size, dtype=np.uint8)])
+    xb = device.create_buffer(xin.size, xin)
     ob = device.create_buffer(max(count * cfg.out_dim * 4, 16))
     tr.forward(xb.address, ob.address, count)
     device.wait()
@@ -92,3 +95,34 @@ def test_forward_output_in_storage_type(device):
     a = o32.read(np.float32)
     b = o16.read(np.uint16)
     assert np.array_equal(C.f32_to_bf16_bits(a), b)
+
+
+@pytest.mark.parametrize("case", ["c2", "c3", "tanh_bf16", "tiny", "relu3"])
+@pytest.mark.parametrize("count", [1, 130, 128 * 148 * 2 + 9])
+def test_narrow_network_forward_on_tensor_cores(device, case, count):
+    """Networks of any widths up to 64 (any activation, input conversion or the frequency encoding) run
+    their forward pass through the padded tensor-core kernel; outputs against the oracle."""
+    rng = np.random.default_rng(count % 97 + len(case))
+    if case in ("c2", "c3"):
+        cfg = C.named_config(case)
+        params = C.init_params(cfg, seed=3, scheme="xavier" if case == "c2" else "kaiming")
+        x, _ = C.synthetic_batch(case, cfg, count, seed=3)
+    else:
+        dims, dtype, act = {"tanh_bf16": ([20, 64, 33, 40], C.BF16, C.ACT_TANH), "tiny": ([3, 16, 7], C.F16, C.ACT_SILU),
+                            "relu3": ([32, 64, 64, 3], C.F16, C.ACT_RELU)}[case]
+        cfg = C.make_config(dims, dtype=dtype, hidden_act=act, output_act=C.ACT_SIGMOID if case == "relu3" else C.ACT_IDENTITY)
+        params = C.init_params(cfg, seed=3, scheme="xavier")
+        x = rng.uniform(-1, 1, (count, dims[0])).astype(np.float32)
+    # non-zero biases
+    w_off, b_off, total = C.param_layout(cfg)
+    pf = C.from_storage(params, cfg.dtype).copy()
+    for l in range(cfg.n_layers):
+        pf[b_off[l]:b_off[l] + cfg.dims[l + 1]] = rng.uniform(-0.2, 0.2, cfg.dims[l + 1])
+    params = C.to_storage(pf, cfg.dtype)
+    ref = oracle.forward(cfg, params, x, count)
+    out, impl = _forward(device, cfg, params, x, count, "forward")
+    assert impl == "tcgen05"
+    scale = max(float(np.max(np.abs(ref))), 1e-6)
+    err = float(np.max(np.abs(out - ref))) / scale
+    print("narrow forward %s count %d: max err / max|out| = %.3g" % (case, count, err))
+    assert err < (1e-2 if cfg.dtype == C.BF16 else 3e-3)
