@@ -287,6 +287,19 @@ def bench_narrow(args):
     device.wait()
     ms, kms = float(np.mean(times)), float(np.mean(ktimes))
     mx, sm = tr.read_loss()
+    # the forward entry point of the same network (outputs fp32), timed the same way
+    out = torch.empty((count, cfg.out_dim), dtype=torch.float32, device=dev_t)
+    ftimes = []
+    for i in range(args.warmup + args.steps):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        tr.forward(x.data_ptr(), out.data_ptr(), count)
+        e1.record()
+        torch.cuda.synchronize()
+        if i >= args.warmup:
+            ftimes.append(e0.elapsed_time(e1))
+    fms = float(np.mean(ftimes))
     peaks = measured_peaks()
     flops = C.flops_per_sample(cfg, training=True)
     achieved = flops * count / (kms * 1e-3) / 1e12
@@ -294,6 +307,7 @@ def bench_narrow(args):
             "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": workload, "global_batch": count, "l2": "512 MB written between timed steps"},
             "gpu_launches": launches, "implementation": impl,
+            "forward": {"ms": fms, "samples_per_s": count / (fms * 1e-3), "implementation": tr.k_forward.implementation},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_burst"], "unit": "TFLOP/s",
                          "frac": achieved / peaks["bf16_burst"], "traffic": None, "kernel": "learn_gradient_narrow_kernel",
                          "kernel_ms": kms, "flop_per_sample": flops, "peak_source": peaks["source"] + " (burst; kernel timed alone)"},
