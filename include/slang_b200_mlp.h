@@ -32,6 +32,7 @@ extern "C" {
 #define MLP_E_NOT_AVAILABLE (-3)  /* SLANG_E_NOT_AVAILABLE: no kernel of that name / unsupported shape */
 #define MLP_E_CUDA (-4)           /* a CUDA call failed; see mlp_last_error_string() */
 #define MLP_E_DEVICE_STATUS (-5)  /* a kernel gave up on a bounded wait and set its status word */
+#define MLP_E_COMM (-6)           /* a collective failed asynchronously or ran past its time limit; communicator aborted */
 
 typedef struct MlpDevice MlpDevice;
 typedef struct MlpBuffer MlpBuffer;
@@ -175,6 +176,16 @@ int32_t mlp_comm_destroy(MlpComm* comm);
 int32_t mlp_allreduce_grads(MlpDevice* device, MlpComm* comm, uint64_t gradients, size_t count, uint64_t loss_words,
                             uint32_t flags);
 
+/* Waits on the host, with a limit, for everything queued on the device's stream so far (the
+ * collectives of mlp_allreduce_grads included), asking the collective library for asynchronous errors
+ * while it waits.  MLP_OK: the stream drained.  MLP_E_COMM: the library reported an error (a peer
+ * process died, a link failed) or timeout_ms passed; the communicator has been aborted so that nothing
+ * stays queued behind a peer that will never arrive, and the handle is good for mlp_comm_destroy only.
+ * A data-parallel host calls this where it would otherwise synchronise (before reading the loss).
+ * The environment variable SLANG_B200_NCCL_LIBRARY names the collective library file to bind in place
+ * of the default search for libnccl.so.2. */
+int32_t mlp_comm_wait(MlpDevice* device, MlpComm* comm, uint32_t timeout_ms);
+
 /* ---- kernels ------------------------------------------------------------------------------ */
 
 /* loadComputeProgram / findEntryPointByName (mlp-training.cpp:291-312): the literal example's entry
@@ -248,14 +259,34 @@ int32_t mlp_layout_to_portable(MlpDevice* device, const MlpNetworkShape* shape, 
  *   - Limit: count * (sum over layers of in + out widths) floats must fit in 1 048 576 floats
  *     (e.g. 10 591 samples of the 2-16-16-16-1 network); larger batches get MLP_E_INVALID_ARG with
  *     the limit in the message.  Split them: gradients and loss words accumulate across calls.
- *   - The first call on each device resolves the area's device address (no allocation, but a CUDA
- *     runtime query): make that first call before any stream capture begins.
+ *   - The first call on each device resolves the area's device address.  That query allocates
+ *     nothing through the allocator API, but with lazy module loading it is the moment the driver
+ *     places this library's device image, the 4 MiB area included, on that GPU: make one call per
+ *     device (count 0 is enough) at start-up, before the memory budget is claimed and before any
+ *     stream capture begins.
+ *   - The call makes device_ordinal current while it works and puts the caller's current device
+ *     back before it returns.
+ *   - The config goes through the same validity check as every other entry point; flag bits other
+ *     than MLP_FLAG_SEQUENTIAL_SUM are refused (MLP_FLAG_INPUT_GRADIENT with MLP_E_NOT_AVAILABLE:
+ *     the argument struct has no place for the result), all before any CUDA call.
  *   - Every call on a device uses the same area and leaves its contents behind; each call
  *     overwrites all the slots it later reads, so nothing has to be cleared.  Two calls whose
  *     kernels overlap on the GPU (different streams, no ordering between them) race on the area.
  *   - The 4 MiB are resident on every GPU that loads the library until the process exits. */
 int32_t mlp_learn_gradient_ordered_noalloc(int32_t device_ordinal, void* cuda_stream, const MlpConfig* config,
                                            const MlpLearnGradParamsEx* args);
+
+/* ---- self-test of the failure-reporting path ------------------------------------------------- */
+
+/* No counterpart in the reference (its device code has no bounded waits; a hung kernel there ends in
+ * the driver's watchdog, examples/nv-aftermath-example being the post-mortem tool).  Every wait inside
+ * this library's tensor-core kernels gives up after a fixed number of polls, records a code in a device
+ * status word and lets the kernel exit; mlp_wait() then returns MLP_E_DEVICE_STATUS once.  This call
+ * launches a one-CTA kernel that makes such a wait run out on purpose (an mbarrier nobody arrives on,
+ * max_polls polls, 1..100000) so that an integrator can see the whole path work: the launch returns
+ * MLP_OK, the next mlp_wait() returns MLP_E_DEVICE_STATUS with status bit 0x40000000, the one after
+ * that MLP_OK.  Nothing faults or hangs; bit 0x20000000 would mean the path itself is defective. */
+int32_t mlp_selftest_bounded_wait(MlpDevice* device, uint32_t max_polls);
 
 /* ---- host-side layout helpers ------------------------------------------------------------- */
 

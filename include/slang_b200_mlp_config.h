@@ -51,6 +51,15 @@ enum MlpLoss { MLP_LOSS_MSE_MEAN = 0, MLP_LOSS_L2_SUM = 1 };
  * u-major, then k, then (sin, cos). */
 enum MlpEncoding { MLP_ENC_NONE = 0, MLP_ENC_FREQ2D = 1 };
 
+/* Order and rounding of a layer's scalar sums where one thread (or the CPU) adds the terms one at a
+ * time.  NEURAL is what the neural module's InlineVector and the cooperative-vector software fallback
+ * do: the sum starts at zero, every product is rounded before it is added, the bias is added after the
+ * last term (source/standard-modules/neural/inline-vector.slang:101-110, 131-132;
+ * source/slang/hlsl.meta.slang:32866, 33266-33274).  BIAS_FIRST_FUSED is the example's order, the sum
+ * starting from the bias (examples/mlp-training/mlvec_sw.slang:31-34), with each term a fused
+ * multiply-add.  The tensor-core kernels accumulate in fp32 in the hardware's own order and ignore it. */
+enum MlpSumOrder { MLP_SUM_NEURAL = 0, MLP_SUM_BIAS_FIRST_FUSED = 1 };
+
 typedef struct MlpConfig {
     int32_t n_layers;                  /* number of linear layers, 1..MLP_MAX_LAYERS */
     int32_t dims[MLP_MAX_LAYERS + 1];  /* dims[0] = width entering layer 0 (after encoding), dims[n_layers] = outputs */
@@ -65,7 +74,8 @@ typedef struct MlpConfig {
     int32_t input_width;               /* values per sample in the inputs buffer (2 for FREQ2D, else dims[0]) */
     float lr, beta1, beta2, eps;       /* Adam constants (adam.slang:15-19) */
     int32_t adam_master;               /* 1: Adam keeps an fp32 copy of each parameter in its state */
-    int32_t reserved[3];
+    int32_t sum_order;                 /* MlpSumOrder of the one-thread-per-sample kernels */
+    int32_t reserved[2];
 } MlpConfig;
 
 /* Optimiser state per parameter for the configurable path: the fp32 widening of the reference's

@@ -11,9 +11,16 @@
  *   - accumulation: plain load-add-store, as in the software fallbacks of
  *     coopVecOuterProductAccumulate / coopVecReduceSumAccumulate
  *     (source/slang/hlsl.meta.slang:33261-33315, 33344-33351);
- *   - layer math: y = W x + b with W row-major [out][in], the sum starting from the bias and running
- *     over the inputs in ascending order (examples/mlp-training/mlvec_sw.slang:24-37,
- *     source/slang/hlsl.meta.slang:32835-32912, source/standard-modules/neural/inline-vector.slang:91-200);
+ *   - layer math: y = W x + b with W row-major [out][in], the terms added in ascending input order.
+ *     MlpConfig.sum_order picks between the two orders the reference itself uses:
+ *       MLP_SUM_NEURAL (default): the sum starts at zero, each product is rounded before it is added
+ *       and the bias is added after the last term, as InlineVector.linearTransform and the
+ *       cooperative-vector software fallback do (source/standard-modules/neural/inline-vector.slang:101-110,
+ *       131-132; source/slang/hlsl.meta.slang:32866 and the bias loop after it); dx sums rounded
+ *       products from zero (inline-vector.slang:149-159) and dW adds a rounded product
+ *       (inline-vector.slang:163-175, hlsl.meta.slang:33266-33274);
+ *       MLP_SUM_BIAS_FIRST_FUSED: the example's order, the sum starting from the bias
+ *       (examples/mlp-training/mlvec_sw.slang:31-34), with every term a fused multiply-add;
  *     dW = dy (x) x, db = dy, dx = W^T dy (examples/mlp-training/mlp_sw.slang:28-58);
  *   - activations and their derivatives: source/standard-modules/neural/activations.slang:8-228 and
  *     the max tie rule of source/slang/diff.meta.slang:2268-2273;
@@ -210,15 +217,22 @@ bool config_ok(const MlpConfig* c)
 }
 
 // Accumulating a * b into acc in the chosen accumulation type.
-//   acc_mode 0: float with a fused multiply-add (one rounding per term)
+//   acc_mode 0: float; a rounded product then a rounded add (MLP_SUM_NEURAL) or one fused
+//               multiply-add per term (MLP_SUM_BIAS_FIRST_FUSED)
 //   acc_mode 1: double
 //   acc_mode 2: the storage type (the literal CoopVec fallback, hlsl.meta.slang:32858-32869)
+// This file is compiled with -ffp-contract=off: `acc + a * b` below is two roundings.
 template <typename Acc> struct AccOps;
 template <> struct AccOps<float> {
-    static inline float mac(float acc, float a, float b) { return std::fmaf(a, b, acc); }
+    static inline float mac(float acc, float a, float b, bool fused)
+    {
+        if (fused) return std::fmaf(a, b, acc);
+        const float prod = a * b;
+        return acc + prod;
+    }
 };
 template <> struct AccOps<double> {
-    static inline double mac(double acc, float a, float b) { return acc + double(a) * double(b); }
+    static inline double mac(double acc, float a, float b, bool) { return acc + double(a) * double(b); }
 };
 
 const float kPi = 3.14159265358979323846f;
@@ -270,6 +284,7 @@ void forward_sample(const MlpConfig& c, const Layout& L, const float* params, co
                     Scratch& sc, int acc_mode)
 {
     encode_input(c, inputs, s, sc.a[0].data());
+    const bool bias_first = c.sum_order == MLP_SUM_BIAS_FIRST_FUSED;
     for (int l = 0; l < c.n_layers; ++l) {
         const int in = c.dims[l], out = c.dims[l + 1];
         const bool last = (l == c.n_layers - 1);
@@ -279,15 +294,16 @@ void forward_sample(const MlpConfig& c, const Layout& L, const float* params, co
             const float* ain = sc.a[l].data();
             float zf;
             if (acc_mode == 2) {
-                float r = bias;
+                float r = bias_first ? bias : 0.0f;
                 for (int i = 0; i < in; ++i) {
                     float prod = round_to(c.dtype, wrow[i] * ain[i]);
                     r = round_to(c.dtype, r + prod);
                 }
-                zf = r;
+                zf = bias_first ? r : round_to(c.dtype, r + bias);
             } else {
-                Acc r = Acc(bias);
-                for (int i = 0; i < in; ++i) r = AccOps<Acc>::mac(r, wrow[i], ain[i]);
+                Acc r = bias_first ? Acc(bias) : Acc(0);
+                for (int i = 0; i < in; ++i) r = AccOps<Acc>::mac(r, wrow[i], ain[i], bias_first);
+                if (!bias_first) r = r + Acc(bias);
                 zf = float(r);
             }
             float zs = round_to(c.dtype, zf);
@@ -307,6 +323,7 @@ float learn_sample(const MlpConfig& c, const Layout& L, const float* params, flo
     const int od = c.dims[nl];
     // Loss and its gradient with respect to the last pre-activation.
     float loss = 0.0f;
+    const bool fused = c.sum_order == MLP_SUM_BIAS_FIRST_FUSED;
     const float scale = (c.loss == MLP_LOSS_MSE_MEAN) ? 1.0f / float(od) : 1.0f;
     for (int j = 0; j < od; ++j) {
         float t = load_as_f32(c.target_dtype, targets, s * od + j);
@@ -322,7 +339,14 @@ float learn_sample(const MlpConfig& c, const Layout& L, const float* params, flo
         for (int j = 0; j < out; ++j) {
             const float g = sc.dz[j];
             float* gw = grads + L.w[l] + int64_t(j) * in;
-            for (int i = 0; i < in; ++i) gw[i] = std::fmaf(g, sc.a[l][i], gw[i]);
+            if (fused) {
+                for (int i = 0; i < in; ++i) gw[i] = std::fmaf(g, sc.a[l][i], gw[i]);
+            } else {
+                for (int i = 0; i < in; ++i) {
+                    const float prod = sc.a[l][i] * g;  // T prod = x * dy; then the add
+                    gw[i] = gw[i] + prod;
+                }
+            }
             grads[L.b[l] + j] += g;
         }
         if (l == 0) {
@@ -333,7 +357,7 @@ float learn_sample(const MlpConfig& c, const Layout& L, const float* params, flo
                 for (int i = 0; i < in; ++i) {
                     Acc r = Acc(0);
                     const float* wcol = params + L.w[0] + i;
-                    for (int j = 0; j < out; ++j) r = AccOps<Acc>::mac(r, wcol[int64_t(j) * in], sc.dz[j]);
+                    for (int j = 0; j < out; ++j) r = AccOps<Acc>::mac(r, wcol[int64_t(j) * in], sc.dz[j], fused);
                     input_grads[s * in + i] = round_to(c.dtype, float(r));
                 }
             }
@@ -352,7 +376,7 @@ float learn_sample(const MlpConfig& c, const Layout& L, const float* params, flo
             } else {
                 Acc r = Acc(0);
                 const float* wcol = params + L.w[l] + i;
-                for (int j = 0; j < out; ++j) r = AccOps<Acc>::mac(r, wcol[int64_t(j) * in], sc.dz[j]);
+                for (int j = 0; j < out; ++j) r = AccOps<Acc>::mac(r, wcol[int64_t(j) * in], sc.dz[j], fused);
                 v = float(r);
             }
             float d = round_to(c.dtype, act_deriv(c.hidden_act, c.act_alpha, sc.z[l - 1][i]));

@@ -189,6 +189,11 @@ class Comm:
                                          trainer.loss.address if with_loss else 0,
                                          COMM_RANK_ORDERED_SUM if rank_ordered else 0))
 
+    def wait(self, timeout_ms=30000):
+        """Host wait for the stream with the collective library's asynchronous errors polled; raises
+        MlpError (MLP_E_COMM) after an error or the time limit, with the communicator aborted."""
+        check(load().mlp_comm_wait(self.device.handle, self.handle, timeout_ms))
+
     def destroy(self):
         if self.handle:
             load().mlp_comm_destroy(self.handle)

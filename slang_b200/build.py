@@ -2,15 +2,17 @@
 
     python -m slang_b200.build [--force] [--verbose]
 
-Each translation unit is compiled to an object with its own flags and the objects are linked into
-slang_b200/libslang_b200_mlp.so; the literal example entry points are also built into a stand-alone
-device module, slang_b200/mlp_training_kernels.cubin.  The CUDA runtime is linked statically so the library has no
-dependency beyond the driver.
+Each translation unit is compiled to an object with its own flags (stale units side by side, one nvcc
+process each) and the objects are linked into slang_b200/libslang_b200_mlp.so; the literal example
+entry points are also built into a stand-alone device module, slang_b200/mlp_training_kernels.cubin.
+A unit is stale when its source, or any header its last compile read (nvcc -MD), is newer than its
+object.  The CUDA runtime is linked statically so the library has no dependency beyond the driver.
 """
 import os
 import shutil
 import subprocess
 import sys
+from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
@@ -24,19 +26,20 @@ ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
           "--expt-relaxed-constexpr"]
 
-# (source, extra flags).  The one-thread-per-sample kernels must not contract a*b+c into an fma on
-# their own: their fp32 results are compared bit for bit with a sequential CPU.
+# (object name, source, extra flags).  The one-thread-per-sample kernels must not contract a*b+c into
+# an fma on their own: their fp32 results are compared bit for bit with a sequential CPU.  The padded
+# tensor-core kernel is instantiated some fifty times; its source is compiled in eight parts.
 UNITS = [
-    ("abi.cu", []),
-    ("simt_kernels.cu", ["-fmad=false"]),
-    ("layout_convert.cu", []),
-    ("tc_kernels.cu", []),
-    ("tc_forward.cu", []),
-    ("tc_train_narrow.cu", []),
-    ("comm.cu", []),
-    ("matrix_convert.cu", []),
-    ("permuto.cu", ["-fmad=false"]),
-]
+    ("abi", "abi.cu", []),
+    ("simt_kernels", "simt_kernels.cu", ["-fmad=false"]),
+    ("layout_convert", "layout_convert.cu", []),
+    ("tc_kernels", "tc_kernels.cu", []),
+    ("tc_forward", "tc_forward.cu", []),
+    ("comm", "comm.cu", []),
+    ("matrix_convert", "matrix_convert.cu", []),
+    ("permuto", "permuto.cu", ["-fmad=false"]),
+    ("selftest", "selftest.cu", []),
+] + [("tc_train_narrow_%d" % i, "tc_train_narrow.cu", ["-DMLPB200_NARROW_PART=%d" % i]) for i in range(8)]
 
 
 def _nvcc():
@@ -46,37 +49,72 @@ def _nvcc():
     raise RuntimeError("nvcc not found")
 
 
-def _headers():
-    hs = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
-    inc = os.path.join(os.path.dirname(HERE), "include")
-    hs += [os.path.join(inc, f) for f in os.listdir(inc)]
-    return hs
+def _deps(depfile):
+    """Prerequisites listed in a make-style dependency file written by nvcc -MD."""
+    try:
+        text = open(depfile).read()
+    except OSError:
+        return None
+    text = text.replace("\\\n", " ")
+    if ":" not in text:
+        return None
+    return [t for t in text.split(":", 1)[1].split() if t]
 
 
-def build(force=False, verbose=False):
+def _stale(obj, src, depfile):
+    if not os.path.exists(obj):
+        return True
+    t = os.path.getmtime(obj)
+    if os.path.getmtime(src) > t:
+        return True
+    deps = _deps(depfile)
+    if deps is None:
+        return True
+    for d in deps:
+        if d.startswith(("/usr/", "/opt/")):
+            continue  # toolkit and system headers
+        if not os.path.exists(d) or os.path.getmtime(d) > t:
+            return True
+    return False
+
+
+def build(force=False, verbose=False, jobs=None):
     nvcc = _nvcc()
     os.makedirs(OBJDIR, exist_ok=True)
-    newest_header = max(os.path.getmtime(h) for h in _headers())
-    objs = []
-    rebuilt = False
-    for src, extra in UNITS:
+    objs, todo = [], []
+    for name, src, extra in UNITS:
         s = os.path.join(CSRC, src)
-        o = os.path.join(OBJDIR, src.replace(".cu", ".o"))
+        o = os.path.join(OBJDIR, name + ".o")
+        d = os.path.join(OBJDIR, name + ".d")
         objs.append(o)
-        if force or not os.path.exists(o) or os.path.getmtime(o) < max(os.path.getmtime(s), newest_header):
-            more = os.environ.get("MLPB200_NVCC_FLAGS", "").split()  # experiments only, e.g. -DMLPB200_CH=64
-            cmd = [nvcc] + ARCH + COMMON + extra + more + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
-            if verbose:
-                print(" ".join(cmd), flush=True)
-            subprocess.check_call(cmd)
-            rebuilt = True
+        if force or _stale(o, s, d):
+            cmd = [nvcc] + ARCH + COMMON + extra + (["-Xptxas", "-v"] if verbose else []) + ["-MD", "-MF", d, "-c", s, "-o", o]
+            todo.append(cmd)
+
+    def run(cmd):
+        if verbose:
+            print(" ".join(cmd), flush=True)
+        r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        return cmd, r.returncode, r.stdout
+
+    if todo:
+        with ThreadPoolExecutor(max_workers=jobs or min(len(todo), os.cpu_count() or 4)) as pool:
+            results = list(pool.map(run, todo))
+        failed = [(c, out) for c, rc, out in results if rc != 0]
+        if verbose or failed:
+            for c, rc, out in results:
+                if out.strip() and (verbose or rc != 0):
+                    print(out, flush=True)
+        if failed:
+            raise subprocess.CalledProcessError(1, failed[0][0], output=failed[0][1])
     cs = os.path.join(CSRC, CUBIN_SRC)
-    if force or not os.path.exists(CUBIN) or os.path.getmtime(CUBIN) < max(os.path.getmtime(cs), newest_header):
-        cmd = [nvcc, "-arch=sm_100a", "-cubin", "-O3", "-std=c++17", "-lineinfo", "-fmad=false", cs, "-o", CUBIN]
+    cd = os.path.join(OBJDIR, "example_module.d")
+    if force or _stale(CUBIN, cs, cd):
+        cmd = [nvcc, "-arch=sm_100a", "-cubin", "-O3", "-std=c++17", "-lineinfo", "-fmad=false", "-MD", "-MF", cd, cs, "-o", CUBIN]
         if verbose:
             print(" ".join(cmd), flush=True)
         subprocess.check_call(cmd)
-    if rebuilt or not os.path.exists(OUT):
+    if todo or not os.path.exists(OUT):
         cmd = [nvcc] + ARCH + ["-shared", "-cudart", "static", "-o", OUT] + objs + ["-ldl"]
         if verbose:
             print(" ".join(cmd), flush=True)

@@ -20,6 +20,9 @@ F32, F16, BF16 = 0, 1, 2
  ACT_QUICK_GELU, ACT_GELU_TANH, ACT_LEAKY_MAX) = range(11)
 LOSS_MSE_MEAN, LOSS_L2_SUM = 0, 1
 ENC_NONE, ENC_FREQ2D = 0, 1
+# MlpSumOrder: neural module / cooperative-vector fallback order (zero start, rounded products, bias
+# last) and the example's order (bias first, fused multiply-adds).
+SUM_NEURAL, SUM_BIAS_FIRST_FUSED = 0, 1
 
 DTYPE_SIZE = {F32: 4, F16: 2, BF16: 2}
 DTYPE_NAME = {F32: "f32", F16: "f16", BF16: "bf16"}
@@ -43,7 +46,8 @@ class MlpConfig(ctypes.Structure):
         ("beta2", ctypes.c_float),
         ("eps", ctypes.c_float),
         ("adam_master", ctypes.c_int32),
-        ("reserved", ctypes.c_int32 * 3),
+        ("sum_order", ctypes.c_int32),
+        ("reserved", ctypes.c_int32 * 2),
     ]
 
     @property
@@ -81,7 +85,7 @@ EXAMPLE_ADAM_STATE_DTYPE = np.dtype([("mean", "<u2"), ("variance", "<u2"), ("ite
 
 def make_config(dims, dtype=F32, hidden_act=ACT_RELU, output_act=ACT_IDENTITY, act_alpha=0.01,
                 loss=LOSS_MSE_MEAN, encoding=ENC_NONE, input_dtype=F32, target_dtype=F32,
-                lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, adam_master=0):
+                lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, adam_master=0, sum_order=SUM_NEURAL):
     dims = list(dims)
     if not (1 <= len(dims) - 1 <= MLP_MAX_LAYERS):
         raise ValueError("layer count out of range")
@@ -95,6 +99,7 @@ def make_config(dims, dtype=F32, hidden_act=ACT_RELU, output_act=ACT_IDENTITY, a
     c.input_width = 2 if encoding == ENC_FREQ2D else dims[0]
     c.lr, c.beta1, c.beta2, c.eps = lr, beta1, beta2, eps
     c.adam_master = adam_master
+    c.sum_order = sum_order
     return c
 
 

@@ -75,6 +75,13 @@ const char* cu_error(CUresult r)
     return "unknown driver error";
 }
 
+}  // namespace
+
+namespace mlpb200 {
+// Lets the other translation units report through mlp_last_error_string().
+void set_last_error(const char* text) { g_last_error = text ? text : ""; }
+
+// The one validity check of a problem description; every entry point that takes an MlpConfig runs it.
 bool config_ok(const MlpConfig* c, std::string* why)
 {
     if (!c) { *why = "null config"; return false; }
@@ -83,6 +90,10 @@ bool config_ok(const MlpConfig* c, std::string* why)
         if (c->dims[l] < 1 || c->dims[l] > 1024) { *why = "layer width out of range"; return false; }
     if (c->dtype < MLP_F32 || c->dtype > MLP_BF16 || c->input_dtype < MLP_F32 || c->input_dtype > MLP_BF16 ||
         c->target_dtype < MLP_F32 || c->target_dtype > MLP_BF16) { *why = "unknown dtype"; return false; }
+    if (c->hidden_act < MLP_ACT_IDENTITY || c->hidden_act > MLP_ACT_LEAKY_MAX || c->output_act < MLP_ACT_IDENTITY ||
+        c->output_act > MLP_ACT_LEAKY_MAX) { *why = "unknown activation"; return false; }
+    if (c->loss != MLP_LOSS_MSE_MEAN && c->loss != MLP_LOSS_L2_SUM) { *why = "unknown loss"; return false; }
+    if (c->sum_order != MLP_SUM_NEURAL && c->sum_order != MLP_SUM_BIAS_FIRST_FUSED) { *why = "unknown sum_order"; return false; }
     if (c->encoding == MLP_ENC_FREQ2D && (c->dims[0] != 32 || c->input_width != 2)) {
         *why = "frequency encoding needs dims[0] = 32 and input_width = 2"; return false;
     }
@@ -90,12 +101,6 @@ bool config_ok(const MlpConfig* c, std::string* why)
     if (c->encoding != MLP_ENC_NONE && c->encoding != MLP_ENC_FREQ2D) { *why = "unknown encoding"; return false; }
     return true;
 }
-
-}  // namespace
-
-namespace mlpb200 {
-// Lets the other translation units report through mlp_last_error_string().
-void set_last_error(const char* text) { g_last_error = text ? text : ""; }
 }  // namespace mlpb200
 
 struct MlpBuffer {

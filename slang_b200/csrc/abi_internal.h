@@ -5,6 +5,7 @@
 
 #include <cstddef>
 #include <cstdint>
+#include <string>
 
 #include "launchers.h"
 
@@ -21,4 +22,6 @@ struct MlpDevice {
 namespace mlpb200 {
 // Sets the text mlp_last_error_string() returns on this thread (abi.cu).
 void set_last_error(const char* text);
+// Validity of a problem description: ranges of every enumerated field, widths, encoding consistency.
+bool config_ok(const MlpConfig* c, std::string* why);
 }  // namespace mlpb200

@@ -7,10 +7,13 @@
 #include <dlfcn.h>
 #include <nccl.h>  // types and enumerators only; the functions are resolved at run time
 
+#include <chrono>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
+#include <thread>
 
 #include "abi_internal.h"
 
@@ -27,6 +30,8 @@ struct NcclApi {
     ncclResult_t (*groupStart)() = nullptr;
     ncclResult_t (*groupEnd)() = nullptr;
     const char* (*getErrorString)(ncclResult_t) = nullptr;
+    ncclResult_t (*commGetAsyncError)(ncclComm_t, ncclResult_t*) = nullptr;  // optional
+    ncclResult_t (*commAbort)(ncclComm_t) = nullptr;                         // optional
     bool ok = false;
     std::string why;
 };
@@ -36,10 +41,18 @@ const NcclApi& nccl_api()
     static NcclApi api;
     static std::once_flag once;
     std::call_once(once, [] {
+        // SLANG_B200_NCCL_LIBRARY names the library file to bind instead of the default search.
         // A process that already holds an NCCL (a host framework's bundled copy) gets that one back.
-        void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
-        if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
-        if (!h) { api.why = std::string("libnccl.so.2 could not be loaded: ") + dlerror(); return; }
+        const char* override_path = getenv("SLANG_B200_NCCL_LIBRARY");
+        void* h = nullptr;
+        if (override_path && *override_path) {
+            h = dlopen(override_path, RTLD_NOW | RTLD_GLOBAL);
+            if (!h) { api.why = std::string(override_path) + " could not be loaded: " + dlerror(); return; }
+        } else {
+            h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+            if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+            if (!h) { api.why = std::string("libnccl.so.2 could not be loaded: ") + dlerror(); return; }
+        }
         bool all = true;
         auto get = [&](const char* name, void** fn) { *fn = dlsym(h, name); if (!*fn) { all = false; api.why = std::string("missing NCCL symbol ") + name; } };
         get("ncclGetUniqueId", (void**)&api.getUniqueId);
@@ -51,6 +64,8 @@ const NcclApi& nccl_api()
         get("ncclGroupEnd", (void**)&api.groupEnd);
         get("ncclGetErrorString", (void**)&api.getErrorString);
         api.ok = all;
+        api.commGetAsyncError = (ncclResult_t (*)(ncclComm_t, ncclResult_t*))dlsym(h, "ncclCommGetAsyncError");
+        api.commAbort = (ncclResult_t (*)(ncclComm_t))dlsym(h, "ncclCommAbort");
     });
     return api;
 }
@@ -81,6 +96,8 @@ struct MlpComm {
     float* gather = nullptr;      // nranks x count floats for the rank-ordered sum
     size_t gather_floats = 0;
     float* loss_tmp = nullptr;    // two floats: the loss words leave through here
+    cudaEvent_t done = nullptr;   // recorded by mlp_comm_wait behind the collectives it watches
+    bool aborted = false;         // mlp_comm_wait gave up on it: only mlp_comm_destroy is valid now
 };
 
 #define NCCL_TRY(expr)                                                                                     \
@@ -134,7 +151,8 @@ int32_t mlp_comm_destroy(MlpComm* c)
 {
     if (!c) return MLP_OK;
     cudaSetDevice(c->ordinal);
-    if (c->comm) nccl_api().commDestroy(c->comm);
+    if (c->comm && !c->aborted) nccl_api().commDestroy(c->comm);
+    if (c->done) cudaEventDestroy(c->done);
     if (c->gather) cudaFree(c->gather);
     if (c->loss_tmp) cudaFree(c->loss_tmp);
     delete c;
@@ -147,6 +165,7 @@ int32_t mlp_allreduce_grads(MlpDevice* d, MlpComm* c, uint64_t gradients, size_t
     if (d->ordinal != c->ordinal) return comm_fail(MLP_E_INVALID_ARG, "the communicator belongs to another device");
     if (count && !gradients) return comm_fail(MLP_E_INVALID_ARG, "null gradient address");
     if (flags & ~uint32_t(MLP_COMM_RANK_ORDERED_SUM)) return comm_fail(MLP_E_INVALID_ARG, "unknown flag");
+    if (c->aborted) return comm_fail(MLP_E_COMM, "the communicator was aborted after an earlier failure");
     const NcclApi& api = nccl_api();
     CU_TRY(cudaSetDevice(d->ordinal));
     float* g = (float*)gradients;
@@ -180,6 +199,46 @@ int32_t mlp_allreduce_grads(MlpDevice* d, MlpComm* c, uint64_t gradients, size_t
     }
     if (lw) CU_TRY(cudaMemcpyAsync(lw, c->loss_tmp, 2 * sizeof(float), cudaMemcpyDeviceToDevice, d->stream));
     return MLP_OK;
+}
+
+// Host-side watch over the collectives queued so far: returns when the stream has drained, when the
+// collective library reports an asynchronous error (a peer died, a link failed), or when the time limit
+// passes.  In the last two cases the communicator is aborted, which releases kernels of the library that
+// would otherwise wait for the missing peer, and the handle is good for mlp_comm_destroy only.
+int32_t mlp_comm_wait(MlpDevice* d, MlpComm* c, uint32_t timeout_ms)
+{
+    if (!d || !c) return comm_fail(MLP_E_INVALID_ARG, "null argument");
+    if (d->ordinal != c->ordinal) return comm_fail(MLP_E_INVALID_ARG, "the communicator belongs to another device");
+    if (c->aborted) return comm_fail(MLP_E_COMM, "the communicator was aborted after an earlier failure");
+    const NcclApi& api = nccl_api();
+    CU_TRY(cudaSetDevice(d->ordinal));
+    if (!c->done) CU_TRY(cudaEventCreateWithFlags(&c->done, cudaEventDisableTiming));
+    CU_TRY(cudaEventRecord(c->done, d->stream));
+    const auto t0 = std::chrono::steady_clock::now();
+    std::string why;
+    for (;;) {
+        const cudaError_t q = cudaEventQuery(c->done);
+        ncclResult_t async = ncclSuccess;
+        if (api.commGetAsyncError) {
+            const ncclResult_t r = api.commGetAsyncError(c->comm, &async);
+            if (r != ncclSuccess) async = r;
+        }
+        if (async != ncclSuccess && async != ncclInProgress) {
+            why = std::string("the collective library reported an asynchronous error: ") + api.getErrorString(async);
+            break;
+        }
+        if (q == cudaSuccess) return MLP_OK;
+        if (q != cudaErrorNotReady) return comm_fail(MLP_E_CUDA, std::string("cudaEventQuery failed: ") + cudaGetErrorString(q));
+        const auto ms = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
+        if (ms > (long long)timeout_ms) {
+            why = "the collectives did not finish within the time limit of " + std::to_string(timeout_ms) + " ms";
+            break;
+        }
+        std::this_thread::sleep_for(std::chrono::microseconds(50));
+    }
+    if (api.commAbort) api.commAbort(c->comm);
+    c->aborted = true;
+    return comm_fail(MLP_E_COMM, why + "; the communicator was aborted");
 }
 
 }  // extern "C"

@@ -46,12 +46,21 @@ __device__ __forceinline__ void encode_input(const MlpConfig& c, const void* inp
     }
 }
 
+// One term of a scalar sum in the order MlpConfig.sum_order names: a fused multiply-add, or a rounded
+// product followed by a rounded add (this file is compiled with -fmad=false, so `acc + a * b` is two
+// roundings).
+__device__ __forceinline__ float mac(float a, float b, float acc, bool fused)
+{
+    return fused ? fmaf(a, b, acc) : acc + __fmul_rn(a, b);
+}
+
 // Forward of one sample; a holds every layer's input vector, z every pre-activation (both rounded to
 // the storage type); the last slot of a holds the fp32 outputs.
 __device__ void simt_forward(const SimtNet& net, const MlpLayerPointers* __restrict__ lp, const void* inputs, int64_t s,
                              float* a, float* z)
 {
     const MlpConfig& c = net.cfg;
+    const bool fused = c.sum_order == MLP_SUM_BIAS_FIRST_FUSED;
     encode_input(c, inputs, s, a);
     for (int l = 0; l < c.n_layers; ++l) {
         const int in = c.dims[l], out = c.dims[l + 1];
@@ -62,8 +71,16 @@ __device__ void simt_forward(const SimtNet& net, const MlpLayerPointers* __restr
         const void* W = (const void*)lp[l].weights;
         const void* B = (const void*)lp[l].biases;
         for (int j = 0; j < out; ++j) {
-            float r = load_as_f32(c.dtype, B, j);
-            for (int i = 0; i < in; ++i) r = fmaf(load_as_f32(c.dtype, W, int64_t(j) * in + i), ain[i], r);
+            const float bias = load_as_f32(c.dtype, B, j);
+            float r;
+            if (fused) {
+                r = bias;
+                for (int i = 0; i < in; ++i) r = fmaf(load_as_f32(c.dtype, W, int64_t(j) * in + i), ain[i], r);
+            } else {
+                r = 0.0f;
+                for (int i = 0; i < in; ++i) r = mac(load_as_f32(c.dtype, W, int64_t(j) * in + i), ain[i], r, false);
+                r = r + bias;
+            }
             const float zs = round_to(c.dtype, r);
             zl[j] = zs;
             aout[j] = last ? act_value(c.output_act, c.act_alpha, zs)
@@ -105,6 +122,7 @@ learn_gradient_simt_kernel(SimtNet net, const MlpLayerPointers* __restrict__ lp,
     float zd[kMaxActFloats];  // pre-activations going forward, overwritten by dz going backward
     float loss = 0.0f;
     const int od = c.dims[nl];
+    const bool fused = c.sum_order == MLP_SUM_BIAS_FIRST_FUSED;
     if (valid) {
         simt_forward(net, lp, inputs, tid, a, zd);
         const float scale = (c.loss == MLP_LOSS_MSE_MEAN) ? 1.0f / float(od) : 1.0f;
@@ -125,7 +143,7 @@ learn_gradient_simt_kernel(SimtNet net, const MlpLayerPointers* __restrict__ lp,
             const void* W = (const void*)lp[l].weights;
             for (int i = 0; i < in; ++i) {
                 float r = 0.0f;
-                for (int j = 0; j < out; ++j) r = fmaf(load_as_f32(c.dtype, W, int64_t(j) * in + i), dz[j], r);
+                for (int j = 0; j < out; ++j) r = mac(load_as_f32(c.dtype, W, int64_t(j) * in + i), dz[j], r, fused);
                 const float d = round_to(c.dtype, act_deriv(c.hidden_act, c.act_alpha, zprev[i]));
                 zprev[i] = round_to(c.dtype, r * d);
             }
@@ -137,7 +155,7 @@ learn_gradient_simt_kernel(SimtNet net, const MlpLayerPointers* __restrict__ lp,
             const void* W = (const void*)lp[0].weights;
             for (int i = 0; i < in; ++i) {
                 float r = 0.0f;
-                for (int j = 0; j < out; ++j) r = fmaf(load_as_f32(c.dtype, W, int64_t(j) * in + i), dz[j], r);
+                for (int j = 0; j < out; ++j) r = mac(load_as_f32(c.dtype, W, int64_t(j) * in + i), dz[j], r, fused);
                 input_grads[int64_t(tid) * in + i] = round_to(c.dtype, r);
             }
         }
@@ -189,7 +207,7 @@ learn_gradient_simt_kernel(SimtNet net, const MlpLayerPointers* __restrict__ lp,
                 float acc = 0.0f;
                 if (p < in * out) {
                     const int j = p / in, i = p % in;
-                    for (int s = 0; s < gn; ++s) acc = fmaf(smem[s * stride + in + j], smem[s * stride + i], acc);
+                    for (int s = 0; s < gn; ++s) acc = mac(smem[s * stride + in + j], smem[s * stride + i], acc, fused);
                     atomicAdd(dW + p, acc);
                 } else {
                     const int j = p - in * out;
@@ -208,6 +226,7 @@ sequential_sum_kernel(SimtNet net, const MlpLayerPointers* __restrict__ lp, cons
                       uint32_t count, int layer)
 {
     const MlpConfig& c = net.cfg;
+    const bool fused = c.sum_order == MLP_SUM_BIAS_FIRST_FUSED;
     const int in = c.dims[layer], out = c.dims[layer + 1];
     const int p = blockIdx.x * blockDim.x + threadIdx.x;
     if (p >= in * out + out) return;
@@ -220,7 +239,7 @@ sequential_sum_kernel(SimtNet net, const MlpLayerPointers* __restrict__ lp, cons
         const int j = p / in, i = p % in;
         float* dst = (float*)lp[layer].weightsGrad + p;
         float acc = *dst;
-        for (uint32_t s = 0; s < count; ++s) acc = fmaf(zbase[s * stride + j], abase[s * stride + i], acc);
+        for (uint32_t s = 0; s < count; ++s) acc = mac(zbase[s * stride + j], abase[s * stride + i], acc, fused);
         *dst = acc;
     } else {
         const int j = p - in * out;
@@ -376,7 +395,8 @@ static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
 constexpr int kMaxDevices = 64;
 static float* g_static_scratch_addr[kMaxDevices] = {};
 
-void set_last_error(const char* text);  // abi.cu
+void set_last_error(const char* text);                    // abi.cu
+bool config_ok(const MlpConfig* c, std::string* why);     // abi.cu
 
 }  // namespace mlpb200
 
@@ -385,12 +405,19 @@ using namespace mlpb200;
 extern "C" int32_t mlp_learn_gradient_ordered_noalloc(int32_t device_ordinal, void* cuda_stream, const MlpConfig* config,
                                                       const MlpLearnGradParamsEx* args)
 {
+    // Everything that can be refused is refused here, before the first CUDA call.
     if (!config || !args) { set_last_error("null argument"); return MLP_E_INVALID_ARG; }
     if (device_ordinal < 0 || device_ordinal >= kMaxDevices) { set_last_error("device ordinal out of range"); return MLP_E_INVALID_ARG; }
+    {
+        std::string why;
+        if (!config_ok(config, &why)) { set_last_error(("bad config: " + why).c_str()); return MLP_E_INVALID_ARG; }
+    }
     const MlpConfig& c = *config;
-    if (c.n_layers < 1 || c.n_layers > MLP_MAX_LAYERS) { set_last_error("bad config: n_layers out of range"); return MLP_E_INVALID_ARG; }
-    for (int l = 0; l <= c.n_layers; ++l)
-        if (c.dims[l] < 1 || c.dims[l] > 1024) { set_last_error("bad config: layer width out of range"); return MLP_E_INVALID_ARG; }
+    if (args->flags & MLP_FLAG_INPUT_GRADIENT) {
+        set_last_error("this entry point takes MlpLearnGradParamsEx, which has no input-gradient address: MLP_FLAG_INPUT_GRADIENT is not available here");
+        return MLP_E_NOT_AVAILABLE;
+    }
+    if (args->flags & ~MLP_FLAG_SEQUENTIAL_SUM) { set_last_error("unknown flag bits"); return MLP_E_INVALID_ARG; }
     if (!args->networkBuffer || !args->lossBuffer || (args->count && (!args->inputs || !args->targets))) {
         set_last_error("null device address in the argument struct");
         return MLP_E_INVALID_ARG;
@@ -405,28 +432,33 @@ extern "C" int32_t mlp_learn_gradient_ordered_noalloc(int32_t device_ordinal, vo
         set_last_error(buf);
         return MLP_E_INVALID_ARG;
     }
-    cudaError_t e = cudaSetDevice(device_ordinal);
+    // The work runs with device_ordinal current; the caller's current device is put back on return.
+    int prev_device = -1;
+    cudaError_t e = cudaGetDevice(&prev_device);
+    if (e == cudaSuccess && prev_device != device_ordinal) e = cudaSetDevice(device_ordinal);
     if (e == cudaSuccess && !g_static_scratch_addr[device_ordinal]) {
         // First call on this device: look the array's device address up once and keep it.
         float* addr = nullptr;
         e = cudaGetSymbolAddress((void**)&addr, g_static_scratch);
         if (e == cudaSuccess) g_static_scratch_addr[device_ordinal] = addr;
     }
+    int32_t rc = MLP_OK;
     if (e != cudaSuccess) {
         std::string msg = std::string("CUDA set-up for the built-in scratch area failed: ") + cudaGetErrorString(e);
         set_last_error(msg.c_str());
-        return MLP_E_CUDA;
+        rc = MLP_E_CUDA;
+    } else if (args->count != 0) {
+        MlpLearnGradParamsEx a = *args;
+        a.flags |= MLP_FLAG_SEQUENTIAL_SUM;
+        int launches = 0;
+        std::string err;
+        e = launch_learn_gradient_simt((cudaStream_t)cuda_stream, c, a, g_static_scratch_addr[device_ordinal], &launches, &err);
+        if (e != cudaSuccess) {
+            if (err.empty()) err = std::string("kernel launch failed: ") + cudaGetErrorString(e);
+            set_last_error(err.c_str());
+            rc = e == cudaErrorInvalidValue ? MLP_E_NOT_AVAILABLE : MLP_E_CUDA;
+        }
     }
-    if (args->count == 0) return MLP_OK;
-    MlpLearnGradParamsEx a = *args;
-    a.flags |= MLP_FLAG_SEQUENTIAL_SUM;
-    int launches = 0;
-    std::string err;
-    e = launch_learn_gradient_simt((cudaStream_t)cuda_stream, c, a, g_static_scratch_addr[device_ordinal], &launches, &err);
-    if (e != cudaSuccess) {
-        if (err.empty()) err = std::string("kernel launch failed: ") + cudaGetErrorString(e);
-        set_last_error(err.c_str());
-        return e == cudaErrorInvalidValue ? MLP_E_NOT_AVAILABLE : MLP_E_CUDA;
-    }
-    return MLP_OK;
+    if (prev_device >= 0 && prev_device != device_ordinal) cudaSetDevice(prev_device);
+    return rc;
 }

@@ -71,17 +71,26 @@ __device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, v
     return false;
 }
 
-// Bounded wait.  Returns false when the CTA is aborting (this waiter timed out, or another did).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                          uint32_t* status, uint32_t code)
+// Bounded wait with the poll limit as an argument.  Returns false when the CTA is aborting (this
+// waiter ran out of polls, or another did): the flag is raised, the code is recorded in the device
+// status word, and every later wait of the CTA returns at once.
+__device__ __forceinline__ bool mbar_wait_limited(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                                  uint32_t* status, uint32_t code, uint32_t max_polls)
 {
-    for (uint32_t i = 0; i < kMaxPolls; ++i) {
+    for (uint32_t i = 0; i < max_polls; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 63u) == 63u && *abort_flag) return false;
     }
     *abort_flag = 1u;
     atomicOr(status, code);
     return false;
+}
+
+// Bounded wait with the production limit.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                          uint32_t* status, uint32_t code)
+{
+    return mbar_wait_limited(bar, parity, abort_flag, status, code, kMaxPolls);
 }
 
 // Wait used only while tearing down after an abort: bounded, ignores the abort flag.

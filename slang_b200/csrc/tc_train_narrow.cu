@@ -581,6 +581,7 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
 
 }  // namespace narrow
 
+#if MLPB200_NARROW_PART == 0
 bool tc_train_narrow_supported(const MlpConfig& c)
 {
     if (c.n_layers < 2 || c.n_layers > 5) return false;
@@ -590,6 +591,7 @@ bool tc_train_narrow_supported(const MlpConfig& c)
     if (c.encoding == MLP_ENC_FREQ2D && c.dims[0] != 32) return false;
     return true;
 }
+#endif
 
 template <int NL, int FMT, int HACT, int OACT, int CS, int NCH = 1, bool DFA = false, int H = narrow::HMAX>
 static cudaError_t launch_narrow_cs(cudaStream_t st, TcWorkspace* ws, const narrow::Params& p)
@@ -613,7 +615,115 @@ static cudaError_t launch_narrow(cudaStream_t st, TcWorkspace* ws, const narrow:
     return launch_narrow_cs<NL, FMT, HACT, OACT, 1>(st, ws, p);
 }
 
-static cudaError_t launch_narrow_any(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const narrow::Params& p);
+// The kernel is instantiated some fifty times (layer counts, formats, column splits, tiles in flight).
+// This file is compiled once per MLPB200_NARROW_PART (0..7) so that the instantiations build side by
+// side: part 0 holds the host entry points and the dispatcher, every part holds one group of builds.
+#ifndef MLPB200_NARROW_PART
+#error "compile with -DMLPB200_NARROW_PART=0..7 (slang_b200/build.py does)"
+#endif
+
+cudaError_t launch_narrow_fits32(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const narrow::Params& p);
+cudaError_t launch_narrow_named(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const narrow::Params& p);
+cudaError_t launch_narrow_relu2(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const narrow::Params& p);
+
+#if MLPB200_NARROW_PART == 1
+// Networks whose every width fits 32 (and whose outputs fit one 16-column epilogue group) run the
+// 32-wide build: operand tiles a quarter of the size, so two tiles are in flight with every buffer kept.
+cudaError_t launch_narrow_fits32(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const narrow::Params& p)
+{
+    cudaError_t e = cudaErrorInvalidValue;
+    // the benchmark shape gets its activations as compile-time constants
+    if (c.n_layers == 5 && c.dtype == MLP_F16 && c.hidden_act == MLP_ACT_LEAKY_RELU && c.output_act == MLP_ACT_IDENTITY)
+        return launch_narrow_cs<5, MLP_F16, MLP_ACT_LEAKY_RELU, MLP_ACT_IDENTITY, 2, 2, false, 32>(st, ws, p);
+#define MLPB200_NARROW32(NL_) \
+    if (c.n_layers == NL_) e = c.dtype == MLP_BF16 ? launch_narrow_cs<NL_, MLP_BF16, -1, -1, 2, 2, false, 32>(st, ws, p) \
+                                                   : launch_narrow_cs<NL_, MLP_F16, -1, -1, 2, 2, false, 32>(st, ws, p);
+    MLPB200_NARROW32(2) MLPB200_NARROW32(3) MLPB200_NARROW32(4) MLPB200_NARROW32(5)
+#undef MLPB200_NARROW32
+    return e;
+}
+#endif
+
+#if MLPB200_NARROW_PART == 2
+// The two 64-wide benchmark shapes with their activations as compile-time constants.
+cudaError_t launch_narrow_named(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const narrow::Params& p)
+{
+    if (c.n_layers == 5) return launch_narrow<5, MLP_F16, MLP_ACT_LEAKY_RELU, MLP_ACT_IDENTITY>(st, ws, p);
+    // ReLU, four layers, few outputs: two tiles in flight per CTA (two column groups each)
+    if (c.dims[4] <= narrow::HMAX / 2 && p.n_tiles > (uint32_t)ws->sm_count)
+        return launch_narrow_cs<4, MLP_F16, MLP_ACT_RELU, MLP_ACT_SIGMOID, 2, 2, true>(st, ws, p);
+    return launch_narrow<4, MLP_F16, MLP_ACT_RELU, MLP_ACT_SIGMOID>(st, ws, p);
+}
+#endif
+
+#if MLPB200_NARROW_PART == 3
+// Any ReLU network of up to four layers with few outputs: two tiles in flight per CTA.
+cudaError_t launch_narrow_relu2(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const narrow::Params& p)
+{
+    cudaError_t e = cudaErrorInvalidValue;
+#define MLPB200_NARROW2(NL_) \
+    if (c.n_layers == NL_) e = c.dtype == MLP_BF16 ? launch_narrow_cs<NL_, MLP_BF16, MLP_ACT_RELU, -1, 2, 2, true>(st, ws, p) \
+                                                   : launch_narrow_cs<NL_, MLP_F16, MLP_ACT_RELU, -1, 2, 2, true>(st, ws, p);
+    MLPB200_NARROW2(2) MLPB200_NARROW2(3) MLPB200_NARROW2(4)
+#undef MLPB200_NARROW2
+    return e;
+}
+#endif
+
+#if MLPB200_NARROW_PART >= 4
+// One tile in flight, activations chosen at run time: layer counts 2..5 in either 16-bit format.  Part 4
+// builds bf16 with 2 or 3 layers, part 5 bf16 with 4 or 5, parts 6 and 7 the same for fp16.
+#define MLPB200_NARROW(NL_, FMT_) if (c.n_layers == NL_ && c.dtype == FMT_) return launch_narrow<NL_, FMT_, -1, -1>(st, ws, p);
+#if MLPB200_NARROW_PART == 4
+cudaError_t launch_narrow_generic_a(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const narrow::Params& p)
+{
+    MLPB200_NARROW(2, MLP_BF16) MLPB200_NARROW(3, MLP_BF16)
+    return cudaErrorInvalidValue;
+}
+#elif MLPB200_NARROW_PART == 5
+cudaError_t launch_narrow_generic_b(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const narrow::Params& p)
+{
+    MLPB200_NARROW(4, MLP_BF16) MLPB200_NARROW(5, MLP_BF16)
+    return cudaErrorInvalidValue;
+}
+#elif MLPB200_NARROW_PART == 6
+cudaError_t launch_narrow_generic_c(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const narrow::Params& p)
+{
+    MLPB200_NARROW(2, MLP_F16) MLPB200_NARROW(3, MLP_F16)
+    return cudaErrorInvalidValue;
+}
+#else
+cudaError_t launch_narrow_generic_d(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const narrow::Params& p)
+{
+    MLPB200_NARROW(4, MLP_F16) MLPB200_NARROW(5, MLP_F16)
+    return cudaErrorInvalidValue;
+}
+#endif
+#undef MLPB200_NARROW
+#endif
+
+#if MLPB200_NARROW_PART == 0
+cudaError_t launch_narrow_generic_a(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const narrow::Params& p);
+cudaError_t launch_narrow_generic_b(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const narrow::Params& p);
+cudaError_t launch_narrow_generic_c(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const narrow::Params& p);
+cudaError_t launch_narrow_generic_d(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const narrow::Params& p);
+
+// Picks the build of the kernel for the shape: padded width, tiles in flight, column split, activations.
+static cudaError_t launch_narrow_any(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const narrow::Params& p)
+{
+    bool fits32 = c.dims[c.n_layers] <= 16;
+    for (int l = 0; l <= c.n_layers; ++l) fits32 = fits32 && c.dims[l] <= 32;
+    if (fits32) return launch_narrow_fits32(st, ws, c, p);
+    if (c.n_layers == 5 && c.dtype == MLP_F16 && c.hidden_act == MLP_ACT_LEAKY_RELU && c.output_act == MLP_ACT_IDENTITY)
+        return launch_narrow_named(st, ws, c, p);
+    if (c.n_layers == 4 && c.dtype == MLP_F16 && c.hidden_act == MLP_ACT_RELU && c.output_act == MLP_ACT_SIGMOID)
+        return launch_narrow_named(st, ws, c, p);
+    if (c.hidden_act == MLP_ACT_RELU && c.n_layers >= 2 && c.n_layers <= 4 && c.dims[c.n_layers] <= narrow::HMAX / 2 &&
+        p.n_tiles > (uint32_t)ws->sm_count)
+        return launch_narrow_relu2(st, ws, c, p);
+    if (c.dtype == MLP_BF16) return c.n_layers <= 3 ? launch_narrow_generic_a(st, ws, c, p) : launch_narrow_generic_b(st, ws, c, p);
+    return c.n_layers <= 3 ? launch_narrow_generic_c(st, ws, c, p) : launch_narrow_generic_d(st, ws, c, p);
+}
 
 cudaError_t launch_forward_narrow(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const MlpForwardParams& a,
                                   int* launches, std::string* err)
@@ -655,48 +765,6 @@ cudaError_t launch_learn_gradient_narrow(cudaStream_t st, TcWorkspace* ws, const
     return launch_narrow_any(st, ws, c, p);
 }
 
-// Picks the build of the kernel for the shape: padded width, tiles in flight, column split, activations.
-static cudaError_t launch_narrow_any(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const narrow::Params& p)
-{
-    cudaError_t e = cudaErrorInvalidValue;
-    // Networks whose every width fits 32 (and whose outputs fit one 16-column epilogue group) run the
-    // 32-wide build: operand tiles a quarter of the size, so two tiles are in flight with every buffer kept.
-    bool fits32 = c.dims[c.n_layers] <= 16;
-    for (int l = 0; l <= c.n_layers; ++l) fits32 = fits32 && c.dims[l] <= 32;
-    // the two benchmark shapes get their activations as compile-time constants
-    if (fits32 && c.n_layers == 5 && c.dtype == MLP_F16 && c.hidden_act == MLP_ACT_LEAKY_RELU && c.output_act == MLP_ACT_IDENTITY)
-        e = launch_narrow_cs<5, MLP_F16, MLP_ACT_LEAKY_RELU, MLP_ACT_IDENTITY, 2, 2, false, 32>(st, ws, p);
-    else if (fits32) {
-#define MLPB200_NARROW32(NL_) \
-    if (c.n_layers == NL_) e = c.dtype == MLP_BF16 ? launch_narrow_cs<NL_, MLP_BF16, -1, -1, 2, 2, false, 32>(st, ws, p) \
-                                                   : launch_narrow_cs<NL_, MLP_F16, -1, -1, 2, 2, false, 32>(st, ws, p);
-        MLPB200_NARROW32(2) MLPB200_NARROW32(3) MLPB200_NARROW32(4) MLPB200_NARROW32(5)
-#undef MLPB200_NARROW32
-    }
-    else if (c.n_layers == 5 && c.dtype == MLP_F16 && c.hidden_act == MLP_ACT_LEAKY_RELU && c.output_act == MLP_ACT_IDENTITY)
-        e = launch_narrow<5, MLP_F16, MLP_ACT_LEAKY_RELU, MLP_ACT_IDENTITY>(st, ws, p);
-    else if (c.n_layers == 4 && c.dtype == MLP_F16 && c.hidden_act == MLP_ACT_RELU && c.output_act == MLP_ACT_SIGMOID) {
-        // ReLU, four layers, few outputs: two tiles in flight per CTA (two column groups each)
-        if (c.dims[4] <= narrow::HMAX / 2 && p.n_tiles > (uint32_t)ws->sm_count)
-            e = launch_narrow_cs<4, MLP_F16, MLP_ACT_RELU, MLP_ACT_SIGMOID, 2, 2, true>(st, ws, p);
-        else
-            e = launch_narrow<4, MLP_F16, MLP_ACT_RELU, MLP_ACT_SIGMOID>(st, ws, p);
-    }
-    else if (c.hidden_act == MLP_ACT_RELU && c.n_layers >= 2 && c.n_layers <= 4 && c.dims[c.n_layers] <= narrow::HMAX / 2 &&
-             p.n_tiles > (uint32_t)ws->sm_count) {
-        // any ReLU network of up to four layers with few outputs: two tiles in flight per CTA
-#define MLPB200_NARROW2(NL_) \
-    if (c.n_layers == NL_) e = c.dtype == MLP_BF16 ? launch_narrow_cs<NL_, MLP_BF16, MLP_ACT_RELU, -1, 2, 2, true>(st, ws, p) \
-                                                   : launch_narrow_cs<NL_, MLP_F16, MLP_ACT_RELU, -1, 2, 2, true>(st, ws, p);
-        MLPB200_NARROW2(2) MLPB200_NARROW2(3) MLPB200_NARROW2(4)
-#undef MLPB200_NARROW2
-    } else {
-#define MLPB200_NARROW(NL_) \
-    if (c.n_layers == NL_) e = c.dtype == MLP_BF16 ? launch_narrow<NL_, MLP_BF16, -1, -1>(st, ws, p) : launch_narrow<NL_, MLP_F16, -1, -1>(st, ws, p);
-        MLPB200_NARROW(2) MLPB200_NARROW(3) MLPB200_NARROW(4) MLPB200_NARROW(5)
-#undef MLPB200_NARROW
-    }
-    return e;
-}
+#endif  // part 0
 
 }  // namespace mlpb200

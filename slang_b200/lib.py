@@ -18,11 +18,11 @@ EXPORTS = [
     "mlp_buffer_read", "mlp_buffer_write",
     "mlp_kernel_get", "mlp_kernel_load", "mlp_kernel_get_for_config", "mlp_kernel_destroy", "mlp_kernel_implementation",
     "mlp_dispatch", "mlp_device_launch_count", "mlp_param_layout", "mlp_last_error_string",
-    "mlp_learn_gradient_ordered_noalloc",
+    "mlp_learn_gradient_ordered_noalloc", "mlp_selftest_bounded_wait",
     "mlp_layout_sizes", "mlp_layout_to_optimal", "mlp_layout_to_portable",
     "mlp_matrix_size", "mlp_matrix_convert",
     "mlp_permuto_prepare", "mlp_grid_hash", "mlp_permuto_encode", "mlp_permuto_backward",
-    "mlp_comm_unique_id", "mlp_comm_init", "mlp_comm_destroy", "mlp_allreduce_grads",
+    "mlp_comm_unique_id", "mlp_comm_init", "mlp_comm_destroy", "mlp_allreduce_grads", "mlp_comm_wait",
 ]
 
 # Stand-alone device module with the literal example entry points (built next to the library).
@@ -71,6 +71,7 @@ def load():
     L.mlp_comm_init.argtypes = [vp, i32, i32, vp, sz, pp]
     L.mlp_comm_destroy.argtypes = [vp]
     L.mlp_allreduce_grads.argtypes = [vp, vp, u64, sz, u64, u32]
+    L.mlp_comm_wait.argtypes = [vp, vp, u32]
     L.mlp_kernel_load.argtypes = [vp, ctypes.c_char_p, sz, ctypes.c_char_p, pp]
     L.mlp_kernel_get_for_config.argtypes = [vp, ctypes.POINTER(MlpConfig), ctypes.c_char_p, pp]
     L.mlp_kernel_destroy.argtypes = [vp]
@@ -85,6 +86,7 @@ def load():
     L.mlp_layout_sizes.argtypes = [vp, ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64)]
     L.mlp_layout_to_optimal.argtypes = [vp, vp, u64, u64]
     L.mlp_layout_to_portable.argtypes = [vp, vp, u64, u64]
+    L.mlp_selftest_bounded_wait.argtypes = [vp, u32]
     L.mlp_learn_gradient_ordered_noalloc.argtypes = [i32, vp, ctypes.POINTER(MlpConfig), vp]
     for name in EXPORTS:
         fn = getattr(L, name)

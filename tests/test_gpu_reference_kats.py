@@ -1,0 +1,148 @@
+"""The reference's own known answers and activation set through the GPU entry points.
+
+* tests/neural/fflayer-wavetangled-vector-test.slang:95-153 (the tensor-core matvec's test: 4 -> 2 layer,
+  W = [[1..4],[5..8]], b = [9,10], x = [1..4]; forward [39, 80], dX = [6,8,10,12], dW = B * [1..4] per
+  row, db = B for B = 32, 64, 128) through the tcgen05 entry point "learnGradient" in fp16 and bf16.
+* source/standard-modules/neural/activations.slang:27-228 (all nine activations) plus the two this
+  library adds (GELU-tanh, the cooperative-vector example's max form): value and derivative through
+  "forward" and "learnGradient" on the one-thread-per-sample kernels and on the padded tcgen05 kernel,
+  against the oracle, which tests/test_oracle_kat.py pins on activation-functions-test.slang:31-154.
+* config 2 at its stated 1000 steps on a reduced batch.
+"""
+import numpy as np
+import pytest
+
+from slang_b200 import config as C
+
+from mlp_testlib import gpu_trajectory, layer_rel_errs, make_problem, oracle_trajectory, per_layer_rel_errs
+
+pytestmark = pytest.mark.gpu
+
+ALL_ACTS = [C.ACT_IDENTITY, C.ACT_RELU, C.ACT_LEAKY_RELU, C.ACT_SIGMOID, C.ACT_TANH, C.ACT_EXP, C.ACT_SINE,
+            C.ACT_SILU, C.ACT_QUICK_GELU, C.ACT_GELU_TANH, C.ACT_LEAKY_MAX]
+ACT_NAME = {C.ACT_IDENTITY: "identity", C.ACT_RELU: "relu", C.ACT_LEAKY_RELU: "leaky", C.ACT_SIGMOID: "sigmoid",
+            C.ACT_TANH: "tanh", C.ACT_EXP: "exp", C.ACT_SINE: "sine", C.ACT_SILU: "silu",
+            C.ACT_QUICK_GELU: "quickgelu", C.ACT_GELU_TANH: "gelu_tanh", C.ACT_LEAKY_MAX: "leaky_max"}
+
+
+@pytest.fixture(scope="module")
+def device():
+    from slang_b200.api import Device
+    d = Device(0)
+    yield d
+    d.destroy()
+
+
+@pytest.mark.parametrize("dtype", [C.F16, C.BF16])
+@pytest.mark.parametrize("batch", [32, 64, 128])
+def test_wavetangled_known_answers_through_tcgen05(device, dtype, batch):
+    """Identity layer 4 -> 4 in front of the test's 4 -> 2 layer so that dX of the tested layer shows up
+    as the bias gradient of the layer before it (the learnGradient contract returns parameter
+    gradients).  L2 loss with targets [38.5, 79.5] makes the output gradient exactly 1 per component."""
+    from slang_b200.api import Trainer
+    cfg = C.make_config([4, 4, 2], dtype, C.ACT_IDENTITY, loss=C.LOSS_L2_SUM, input_dtype=C.F32, target_dtype=C.F32)
+    w_off, b_off, total = C.param_layout(cfg)
+    p = np.zeros(total, dtype=np.float32)
+    p[w_off[0]:w_off[0] + 16] = np.eye(4).reshape(-1)
+    p[w_off[1]:w_off[1] + 8] = np.arange(1, 9)
+    p[b_off[1]:b_off[1] + 2] = [9, 10]
+    tr = Trainer(device, cfg, C.to_storage(p, dtype))
+    assert tr.k_learn.implementation == "tcgen05" and tr.k_forward.implementation == "tcgen05"
+    xs = np.tile(np.array([1, 2, 3, 4], dtype=np.float32), (batch, 1))
+    ts = np.tile(np.array([38.5, 79.5], dtype=np.float32), (batch, 1))
+    xb = device.create_buffer(xs.nbytes, xs); tb = device.create_buffer(ts.nbytes, ts)
+    yb = device.create_buffer(batch * 2 * 4)
+    tr.forward(xb.address, yb.address, batch)
+    y = yb.read(np.float32).reshape(batch, 2)
+    assert np.all(y[:, 0] == 39.0) and np.all(y[:, 1] == 80.0)
+    tr.learn_gradient(xb.address, tb.address, batch)
+    g = tr.read_grads()
+    assert list(g[w_off[1]:w_off[1] + 8]) == [batch * v for v in [1, 2, 3, 4, 1, 2, 3, 4]]   # dW = B * x per row
+    assert list(g[b_off[1]:b_off[1] + 2]) == [batch, batch]                                   # db = B
+    assert list(g[b_off[0]:b_off[0] + 4]) == [batch * v for v in [6, 8, 10, 12]]              # B * dX
+    mx, sm = tr.read_loss()
+    assert mx == 0.5 and sm == 0.5 * batch
+
+
+def _act_problem(hidden, output, dtype, count, seed):
+    rng = np.random.default_rng(seed)
+    dims = [6, 24, 17, 5]
+    cfg = C.make_config(dims, dtype=dtype, hidden_act=hidden, output_act=output, act_alpha=0.05, adam_master=1)
+    p0 = C.from_storage(C.init_params(cfg, seed=seed, scheme="xavier"), dtype).copy()
+    w_off, b_off, _ = C.param_layout(cfg)
+    for l in range(cfg.n_layers):  # non-zero biases so that pre-activations are not centred on the tie points
+        p0[b_off[l]:b_off[l] + dims[l + 1]] = rng.uniform(-0.3, 0.3, dims[l + 1])
+    p0 = C.to_storage(p0, dtype)
+    x = rng.uniform(-1.5, 1.5, (count, dims[0])).astype(np.float32)
+    t = rng.uniform(-1, 1, (count, dims[-1])).astype(np.float32)
+    return cfg, p0, x, t
+
+
+@pytest.mark.parametrize("act", ALL_ACTS, ids=[ACT_NAME[a] for a in ALL_ACTS])
+def test_every_activation_one_thread_per_sample(device, act):
+    """fp32, hidden and output activation both `act`: bit-identical gradients with ordered sums (the
+    kernels evaluate expf/sinf/tanhf with the CUDA math library, the oracle with glibc: the last-bit
+    differences of those functions are what the 2e-6 below allows; piecewise-linear ones are exact)."""
+    from oracle import oracle
+    from slang_b200.api import FLAG_SEQUENTIAL_SUM, Trainer
+    count = 300
+    cfg, p0, x, t = _act_problem(act, act, C.F32, count, 100 + act)
+    _, l_ref, g_ref, _ = oracle_trajectory(cfg, p0, [(x, t)])
+    _, l_gpu, g_gpu, _, tr = gpu_trajectory(device, cfg, p0, [(x, t)], "learnGradient_simt", FLAG_SEQUENTIAL_SUM)
+    assert tr.k_learn.implementation == "simt"
+    err = max(layer_rel_errs(cfg, g_gpu, g_ref))
+    exact = act in (C.ACT_IDENTITY, C.ACT_RELU, C.ACT_LEAKY_RELU, C.ACT_LEAKY_MAX)
+    print(ACT_NAME[act], "simt fp32 gradient rel err %.3g" % err)
+    assert err == 0.0 if exact else err < 2e-6
+    assert abs(l_gpu[0][1] - l_ref[0][1]) <= 2e-6 * abs(l_ref[0][1])
+    yb = device.create_buffer(count * cfg.out_dim * 4)
+    xb = device.create_buffer(x.nbytes, x)
+    tr2 = Trainer(device, cfg, p0, forward_entry="forward_simt")
+    tr2.forward(xb.address, yb.address, count)
+    y = yb.read(np.float32).reshape(count, cfg.out_dim)
+    y_ref = oracle.forward(cfg, p0, x, count)
+    assert np.max(np.abs(y - y_ref)) <= 2e-6 * max(1.0, float(np.max(np.abs(y_ref))))
+
+
+@pytest.mark.parametrize("dtype", [C.F16, C.BF16], ids=["f16", "bf16"])
+@pytest.mark.parametrize("act", ALL_ACTS, ids=[ACT_NAME[a] for a in ALL_ACTS])
+def test_every_activation_on_the_padded_tensor_core_kernel(device, act, dtype):
+    """16-bit storage, hidden and output activation both `act`, through "learnGradient" and "forward" of
+    the padded tcgen05 kernel: gradients per tensor within 1e-2, loss within 1e-2, outputs within one
+    storage rounding step of the oracle."""
+    from oracle import oracle
+    from slang_b200.api import Trainer
+    count = 128 * 3 + 9
+    cfg, p0, x, t = _act_problem(act, act, dtype, count, 200 + act)
+    _, l_ref, g_ref, _ = oracle_trajectory(cfg, p0, [(x, t)])
+    _, l_gpu, g_gpu, _, tr = gpu_trajectory(device, cfg, p0, [(x, t)])
+    assert tr.k_learn.implementation == "tcgen05" and tr.k_forward.implementation == "tcgen05"
+    err = max(layer_rel_errs(cfg, g_gpu, g_ref))
+    print(ACT_NAME[act], "tcgen05 gradient rel err %.3g" % err)
+    assert err < 1e-2
+    assert abs(l_gpu[0][1] - l_ref[0][1]) <= 1e-2 * abs(l_ref[0][1])
+    assert abs(l_gpu[0][0] - l_ref[0][0]) <= 1e-2 * abs(l_ref[0][0])
+    xb = device.create_buffer(x.nbytes, x)
+    yb = device.create_buffer(count * cfg.out_dim * 4)
+    tr.forward(xb.address, yb.address, count)
+    y = yb.read(np.float32).reshape(count, cfg.out_dim)
+    y_ref = oracle.forward(cfg, p0, x, count)
+    step = 2.0 ** -7 if dtype == C.BF16 else 2.0 ** -10
+    assert np.max(np.abs(y - y_ref)) <= 4 * step * max(1.0, float(np.max(np.abs(y_ref))))
+
+
+def test_config2_trajectory_at_its_stated_length(device):
+    """Config 2 (fp16 4-32-32-32-32-4, LeakyReLU, Adam 1e-3) for the 1000 steps the configuration names,
+    on a batch of 4096: per-step loss within 1e-2 relative at every step, final parameters within 2e-2
+    relative per layer."""
+    count, steps = 4096, 1000
+    cfg, p0, batches = make_problem("c2", count, seed=21, steps=steps)
+    p_ref, l_ref, _, _ = oracle_trajectory(cfg, p0, batches, n_threads=8)
+    p_gpu, l_gpu, _, _, tr = gpu_trajectory(device, cfg, p0, batches)
+    assert tr.k_learn.implementation == "tcgen05"
+    worst = max(abs(sg - sr) / abs(sr) for (_, sg), (_, sr) in zip(l_gpu, l_ref))
+    errs = per_layer_rel_errs(cfg, C.from_storage(p_gpu, cfg.dtype), C.from_storage(p_ref, cfg.dtype))
+    print("c2 x %d steps: worst per-step loss rel err %.3g, worst per-layer parameter rel err %.3g; loss %.4f -> %.4f"
+          % (steps, worst, max(errs), l_ref[0][1], l_ref[-1][1]))
+    assert worst <= 1e-2
+    assert max(errs) < 2e-2

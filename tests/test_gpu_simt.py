@@ -20,11 +20,15 @@ def device():
     d.destroy()
 
 
-def test_c1_sequential_sum_is_bit_exact(device):
+@pytest.mark.parametrize("order", [C.SUM_NEURAL, C.SUM_BIAS_FIRST_FUSED], ids=["neural_order", "bias_first_fused"])
+def test_c1_sequential_sum_is_bit_exact(device, order):
     """fp32 2-16-16-16-1, batch 4096, 100 steps with a fresh seeded batch each step.
     With the sequential-sum flag the GPU performs the same rounded operations in the same order as the
-    oracle, so parameters, gradients and Adam states agree bit for bit (bar: 1e-5 relative)."""
+    oracle, so parameters, gradients and Adam states agree bit for bit (bar: 1e-5 relative).  Both
+    summation orders of MlpConfig.sum_order: the neural module's (zero start, rounded products, bias
+    last; the default) and the example's (bias first, fused multiply-adds)."""
     cfg, p0, batches = make_problem("c1", 4096, seed=0, steps=100)
+    cfg.sum_order = order
     p_ref, l_ref, g_ref, s_ref = oracle_trajectory(cfg, p0, batches)
     from slang_b200.api import FLAG_SEQUENTIAL_SUM
     p_gpu, l_gpu, g_gpu, s_gpu, _ = gpu_trajectory(device, cfg, p0, batches, "learnGradient_simt", FLAG_SEQUENTIAL_SUM)
@@ -64,6 +68,29 @@ def test_16bit_configs_simt(device, name, count, steps):
     errs = per_layer_rel_errs(cfg, C.from_storage(p_gpu, cfg.dtype), C.from_storage(p_ref, cfg.dtype))
     print(name, "worst per-layer rel err", max(errs))
     assert max(errs) < 2e-2
+
+
+def test_sum_order_known_answers_on_gpu(device):
+    """The order-sensitive cases of tests/test_oracle_kat.py through forward_simt: bias 2^27 with four
+    terms of 3, and -1 + (1 + 2^-12)^2 (inline-vector.slang:101-110, 131-132 against mlvec_sw.slang:31-34)."""
+    from slang_b200.api import Trainer
+    e = np.float32(2.0 ** -12)
+    big = float(2 ** 27)
+    cases = [([[1, 1, 1, 1]], [big], [3, 3, 3, 3], {C.SUM_NEURAL: big + 16.0, C.SUM_BIAS_FIRST_FUSED: big}),
+             ([[-1, 1 + e, 0, 0]], [0], [1, 1 + e, 0, 0],
+              {C.SUM_NEURAL: np.float32(2.0 ** -11), C.SUM_BIAS_FIRST_FUSED: np.float32(2.0 ** -11 + 2.0 ** -24)})]
+    for w, b, x, expect in cases:
+        for order, want in expect.items():
+            cfg = C.make_config([4, 1], C.F32, C.ACT_IDENTITY, loss=C.LOSS_L2_SUM, sum_order=order)
+            w_off, b_off, total = C.param_layout(cfg)
+            p = np.zeros(total, dtype=np.float32)
+            p[w_off[0]:w_off[0] + 4] = np.asarray(w, dtype=np.float32).reshape(-1)
+            p[b_off[0]] = b[0]
+            tr = Trainer(device, cfg, p, learn_entry="learnGradient_simt", forward_entry="forward_simt")
+            xb = device.create_buffer(16, np.asarray(x, dtype=np.float32))
+            yb = device.create_buffer(4)
+            tr.forward(xb.address, yb.address, 1)
+            assert yb.read(np.float32)[0] == want, (order, w)
 
 
 @pytest.mark.parametrize("count", [0, 1, 31, 32, 33, 255, 256, 257])

@@ -269,3 +269,64 @@ def test_example_cpu_entry_point_flavours_agree():
         assert np.array_equal(got[0], ref[0]), mode
         assert got[1].tobytes() == ref[1].tobytes(), mode
         assert np.array_equal(got[2], ref[2]), mode
+
+
+# ---- summation order (MlpConfig.sum_order) -------------------------------------------------------
+def _order_cfg(order):
+    cfg = C.make_config([4, 1], C.F32, C.ACT_IDENTITY, loss=C.LOSS_L2_SUM, sum_order=order)
+    return cfg
+
+
+def test_neural_order_sums_from_zero_and_adds_the_bias_last():
+    """source/standard-modules/neural/inline-vector.slang:101-110, 131-132: `output[row] += data[col] *
+    rowAddr[col]` from a zero vector, then `output[i] + biasAddress[i]`.  With bias 2^27 (spacing 16) and
+    four terms of 3 the order is visible: 12 + 2^27 rounds up to 2^27 + 16, while a sum that starts at the
+    bias loses every term (examples/mlp-training/mlvec_sw.slang:31-34 starts from the bias)."""
+    x = np.array([[3, 3, 3, 3]], dtype=np.float32)
+    big = float(2 ** 27)
+    for order, expect in ((C.SUM_NEURAL, big + 16.0), (C.SUM_BIAS_FIRST_FUSED, big)):
+        cfg = _order_cfg(order)
+        p = _params(cfg, [([[1, 1, 1, 1]], [big])])
+        assert oracle.forward(cfg, p, x, 1)[0, 0] == expect
+
+
+def test_neural_order_rounds_each_product_before_adding():
+    """inline-vector.slang:108 multiplies and adds as two operations (and :156-157, :171-173 name the
+    product `prod` before the add); source/slang/hlsl.meta.slang:33266-33274 does the same for the outer
+    product.  -1 + (1 + 2^-12)^2: the rounded product is 1 + 2^-11, so the two-operation sum is 2^-11;
+    a fused multiply-add keeps the 2^-24."""
+    e = np.float32(2.0 ** -12)
+    x = np.array([[1, 1 + e, 0, 0]], dtype=np.float32)
+    w = [[-1, 1 + e, 0, 0]]
+    for order, expect in ((C.SUM_NEURAL, 2.0 ** -11), (C.SUM_BIAS_FIRST_FUSED, 2.0 ** -11 + 2.0 ** -24)):
+        cfg = _order_cfg(order)
+        p = _params(cfg, [(w, [0])])
+        assert oracle.forward(cfg, p, x, 1)[0, 0] == np.float32(expect)
+    # dW = x * dy as a rounded product added to the running gradient: start the gradient at -1.
+    for order, expect in ((C.SUM_NEURAL, 2.0 ** -11), (C.SUM_BIAS_FIRST_FUSED, 2.0 ** -11 + 2.0 ** -24)):
+        cfg = C.make_config([1, 1], C.F32, C.ACT_IDENTITY, loss=C.LOSS_L2_SUM, sum_order=order)
+        p = _params(cfg, [([[0]], [0])])
+        w_off, _, total = C.param_layout(cfg)
+        g = np.zeros(total, dtype=np.float32)
+        g[w_off[0]] = -1.0
+        # output 0, target -(1+e)/2  ->  dy = 2 * (0 + (1+e)/2) = 1 + e ; x = 1 + e
+        oracle.learn_gradient(cfg, p, g, np.array([[1 + e]], dtype=np.float32), np.array([[-(1 + e) / 2]], dtype=np.float32), 1)
+        assert g[w_off[0]] == np.float32(expect)
+
+
+def test_config1_under_both_orders_stays_within_the_bar():
+    """Config 1, 100 steps x 4096: the two orders are different roundings of the same sums; their
+    parameters differ in the last bits and agree within the 1e-5 bar of the fp32 configuration."""
+    import sys, os
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from mlp_testlib import layer_rel_errs, make_problem, oracle_trajectory
+    cfg, p0, batches = make_problem("c1", 4096, seed=0, steps=100)
+    assert cfg.sum_order == C.SUM_NEURAL
+    p_neural, l_neural, _, _ = oracle_trajectory(cfg, p0, batches)
+    cfg.sum_order = C.SUM_BIAS_FIRST_FUSED
+    p_fused, l_fused, _, _ = oracle_trajectory(cfg, p0, batches)
+    errs = layer_rel_errs(cfg, p_fused, p_neural)
+    print("config 1 after 100 steps: bias-first/fused vs neural order, worst per-tensor rel diff %.3g; final mean loss %.6g vs %.6g"
+          % (max(errs), l_fused[-1][1], l_neural[-1][1]))
+    assert not np.array_equal(p_fused.view(np.uint32), p_neural.view(np.uint32))
+    assert max(errs) < 1e-5
