@@ -109,10 +109,11 @@ def oracle_rate(cfg, name, threads, target_seconds):
         return time.perf_counter() - t0
 
     n = 256 * threads
+    run(n)  # first touch of the library, the thread pool and the pages
     dt = run(n)
-    n_big = int(max(n, min(1 << 20, n * target_seconds / max(dt, 1e-6))))
+    n_big = int(max(n, min(1 << 20, n * 0.5 * target_seconds / max(dt, 1e-6))))
     n_big = (n_big + 255) // 256 * 256
-    dt = run(n_big)
+    dt = 0.5 * (run(n_big) + run(n_big))  # two passes: a single pass moved by a third between runs on one box
     return n_big / dt, n_big, dt
 
 
@@ -169,29 +170,21 @@ def teacher_targets(torch, cfg, x, seed):
     return out
 
 
-def sweep_forward(args):
-    """Forward-only inference sweep: depth-4 ReLU networks of constant width 16/32/64/128 (fp16 weights,
-    Kaiming-uniform, seed 7; inputs uniform in [-1, 1]; fp32 outputs), batch 2^20 .. 2^26 in powers of 4.
-    Each point: samples/s, achieved HBM GB/s over the algorithmic 6w bytes per sample against the
-    measured copy bandwidth, and TFLOP/s.  L2 is flushed between timed iterations."""
-    import torch
+def measure_forward_points(torch, device, dev_t, widths, batches, warmup, steps):
+    """Forward-only points: depth-4 ReLU networks of constant width (fp16 weights, Kaiming-uniform, seed 7;
+    inputs uniform in [-1, 1]; fp32 outputs).  Each point: samples/s, achieved HBM GB/s over the
+    algorithmic 6w bytes per sample against the measured copy bandwidth, and TFLOP/s.  L2 is flushed
+    between timed iterations."""
     from slang_b200 import config as C
-    from slang_b200.api import Device, Trainer
-    torch.cuda.set_device(0)
-    dev_t = torch.device("cuda", 0)
-    stream = torch.cuda.Stream(device=dev_t)
-    torch.cuda.set_stream(stream)
-    device = Device(0, stream.cuda_stream)
+    from slang_b200.api import Trainer
     peaks = measured_peaks()
     flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev_t)
     points = []
-    single = args.config.startswith("c5_w")  # one point: --config c5_w64 --batch N
-    widths = (int(args.config[4:]),) if single else (16, 32, 64, 128)
     for w in widths:
         cfg = C.named_config("c5_w%d" % w)
         tr = Trainer(device, cfg, C.init_params(cfg, seed=7, scheme="kaiming"))
         assert tr.k_forward.implementation == "tcgen05"
-        for n in ((args.batch,) if single else (1 << 20, 1 << 22, 1 << 24, 1 << 26)):
+        for n in batches:
             gen = torch.Generator(device=dev_t); gen.manual_seed(7)
             x = torch.empty((n, w), dtype=torch.float16, device=dev_t)
             piece = 1 << 22
@@ -199,22 +192,41 @@ def sweep_forward(args):
                 x[i0:i0 + piece] = (torch.rand((min(piece, n - i0), w), device=dev_t, generator=gen) * 2 - 1).to(torch.float16)
             out = torch.empty((n, w), dtype=torch.float32, device=dev_t)
             times = []
-            for it in range(args.warmup + args.steps):
+            for it in range(warmup + steps):
                 flush.zero_()
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
                 tr.forward(x.data_ptr(), out.data_ptr(), n)
                 e1.record()
                 torch.cuda.synchronize()
-                if it >= args.warmup:
+                if it >= warmup:
                     times.append(e0.elapsed_time(e1))
             ms = float(np.median(times))
             sps = n / (ms * 1e-3)
             gbs = sps * 6 * w / 1e9
             points.append({"width": w, "batch": n, "ms": ms, "samples_per_s": sps, "hbm_gbs": gbs,
-                           "hbm_frac": gbs / peaks["hbm_gbs"], "tflops": sps * 8 * w * w / 1e12})
+                           "hbm_frac": gbs / peaks["hbm_gbs"], "tflops": sps * 8 * w * w / 1e12,
+                           "tensor_frac_of_burst": sps * 8 * w * w / 1e12 / peaks["bf16_burst"]})
             del x, out
     device.wait()
+    del flush
+    return points
+
+
+def sweep_forward(args):
+    """Forward-only inference sweep: widths 16/32/64/128, batch 2^20 .. 2^26 in powers of 4."""
+    import torch
+    from slang_b200.api import Device
+    torch.cuda.set_device(0)
+    dev_t = torch.device("cuda", 0)
+    stream = torch.cuda.Stream(device=dev_t)
+    torch.cuda.set_stream(stream)
+    device = Device(0, stream.cuda_stream)
+    peaks = measured_peaks()
+    single = args.config.startswith("c5_w")  # one point: --config c5_w64 --batch N
+    widths = (int(args.config[4:]),) if single else (16, 32, 64, 128)
+    batches = (args.batch,) if single else (1 << 20, 1 << 22, 1 << 24, 1 << 26)
+    points = measure_forward_points(torch, device, dev_t, widths, batches, args.warmup, args.steps)
     best = max(points, key=lambda p: p["hbm_frac"])
     line = {"metric": "MLP forward samples/sec (depth-4 constant width)", "value": best["samples_per_s"], "unit": UNIT,
             "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": best["ms"], "higher_is_better": True,
@@ -231,16 +243,25 @@ def sweep_forward(args):
 def bench_narrow(args):
     """Configurations 2 and 3 at their stated sizes on one GPU (resident inputs, CUDA events)."""
     import torch
-    from slang_b200 import config as C
-    from slang_b200.api import Device, Trainer
+    from slang_b200.api import Device
     torch.cuda.set_device(0)
     dev_t = torch.device("cuda", 0)
     stream = torch.cuda.Stream(device=dev_t)
     torch.cuda.set_stream(stream)
     device = Device(0, stream.cuda_stream)
     name = args.config
-    cfg = C.named_config(name)
     count = args.batch if args.batch != (1 << 26) else (1 << 20 if name == "c2" else 1 << 24)
+    line = measure_narrow(torch, device, dev_t, name, count, args.warmup, args.steps)
+    print(json.dumps(line), flush=True)
+    device.destroy()
+
+
+def measure_narrow(torch, device, dev_t, name, count, warmup, steps):
+    """One of configurations 2 and 3: learnGradient + adjustParameters per step with resident inputs,
+    and the forward entry point of the same network; returns the JSON line as a dict."""
+    from slang_b200 import config as C
+    from slang_b200.api import Trainer
+    cfg = C.named_config(name)
     gen = torch.Generator(device=dev_t); gen.manual_seed(11)
     if name == "c2":
         x = torch.rand((count, 4), device=dev_t, generator=gen)
@@ -268,12 +289,12 @@ def bench_narrow(args):
         tr.learn_gradient(x.data_ptr(), t.data_ptr(), count)
         tr.adjust_parameters()
 
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         step()
     torch.cuda.synchronize()
     times, ktimes = [], []
     launches0 = device.launch_count
-    for _ in range(args.steps):
+    for _ in range(steps):
         flush.zero_()
         e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
         e0.record()
@@ -290,20 +311,20 @@ def bench_narrow(args):
     # the forward entry point of the same network (outputs fp32), timed the same way
     out = torch.empty((count, cfg.out_dim), dtype=torch.float32, device=dev_t)
     ftimes = []
-    for i in range(args.warmup + args.steps):
+    for i in range(warmup + steps):
         flush.zero_()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         tr.forward(x.data_ptr(), out.data_ptr(), count)
         e1.record()
         torch.cuda.synchronize()
-        if i >= args.warmup:
+        if i >= warmup:
             ftimes.append(e0.elapsed_time(e1))
     fms = float(np.mean(ftimes))
     peaks = measured_peaks()
     flops = C.flops_per_sample(cfg, training=True)
     achieved = flops * count / (kms * 1e-3) / 1e12
-    line = {"metric": METRIC, "value": count / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+    line = {"metric": METRIC, "value": count / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": steps, "warmup": warmup,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": workload, "global_batch": count, "l2": "512 MB written between timed steps"},
             "gpu_launches": launches, "implementation": impl,
@@ -312,8 +333,8 @@ def bench_narrow(args):
                          "frac": achieved / peaks["bf16_burst"], "traffic": None, "kernel": "learn_gradient_narrow_kernel",
                          "kernel_ms": kms, "flop_per_sample": flops, "peak_source": peaks["source"] + " (burst; kernel timed alone)"},
             "loss": {"max": mx, "mean": sm / count}}
-    print(json.dumps(line), flush=True)
-    device.destroy()
+    del x, t, out, flush
+    return line
 
 
 def bench_permuto(args):
@@ -462,7 +483,8 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--config", default="c4")
     ap.add_argument("--batch", type=int, default=1 << 26, help="global batch (samples per step over all GPUs)")
-    ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--e2e-steps", type=int, default=10)
+    ap.add_argument("--no-sub", action="store_true", help="N=1: skip the block of the other configurations")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--deterministic-sum", action="store_true",
@@ -537,12 +559,20 @@ def main():
         ts.append(teacher_targets(torch, cfg, x, seed=2))
     torch.cuda.synchronize()
 
-    from slang_b200.dist import allreduce_gradients
+    # The gradient exchange goes through the library's own collective entry points (mlp_comm_init /
+    # mlp_allreduce_grads, NCCL bound inside the library): the call a C++ host loop makes between its
+    # two dispatches.  torch.distributed only carries the communicator id and the timing reductions.
+    comm = None
+    if world > 1:
+        from slang_b200.api import Comm, comm_unique_id
+        box = [comm_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        comm = Comm(device, world, rank, box[0])
 
     def allreduce():
-        if world > 1:
-            # fp32 sum of the flat gradient segment (NCCL over NVLink)
-            allreduce_gradients(grads_t, deterministic=args.deterministic_sum)
+        if comm is not None:
+            # fp32 sum of the flat gradient segment (NCCL over NVLink), stream ordered
+            comm.allreduce_grads(trainer, with_loss=False, rank_ordered=args.deterministic_sum)
 
     def step(i):
         b = i % n_batches
@@ -602,6 +632,19 @@ def main():
         xh = torch.empty((count, 64), dtype=torch.bfloat16, pin_memory=True)
         xh.copy_(xs[0])
         torch.cuda.synchronize()
+        # Ceiling of the host-to-device link as this rank sees it while every rank copies at once: the
+        # same pinned buffer into device memory with plain cudaMemcpyAsync, nothing else running.
+        if world > 1:
+            dist.barrier()
+        l0, l1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        xs[1].copy_(xh, non_blocking=True)  # warm-up pass
+        l0.record()
+        for _ in range(2):
+            xs[1].copy_(xh, non_blocking=True)
+        l1.record()
+        torch.cuda.synchronize()
+        link_ms = l0.elapsed_time(l1) / 2
+        # (batch 1's inputs are overwritten; the timed region that used them is over)
         stepper.step(xh)  # warm-up
         torch.cuda.synchronize()
         if world > 1:
@@ -616,12 +659,17 @@ def main():
         e2e_ms = e0.elapsed_time(e1)
         wall_ms = (time.perf_counter() - t0) * 1e3
         if world > 1:
-            tt = torch.tensor([e2e_ms], dtype=torch.float64, device=dev_t)
+            tt = torch.tensor([e2e_ms, link_ms], dtype=torch.float64, device=dev_t)
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-            e2e_ms = float(tt[0])
+            e2e_ms, link_ms = float(tt[0]), float(tt[1])
+        link_ceiling = stepper.h2d_bytes / (link_ms * 1e-3) / 1e9          # GB/s per rank, slowest rank
+        link_used = stepper.h2d_bytes * args.e2e_steps / (e2e_ms * 1e-3) / 1e9
         e2e = {"value": args.batch * args.e2e_steps / (e2e_ms * 1e-3), "unit": UNIT,
                "h2d_bytes_per_step": int(stepper.h2d_bytes) * world, "d2h_bytes_per_step": int(stepper.d2h_bytes) * world,
                "steps": args.e2e_steps, "wall_ms_per_step": wall_ms / args.e2e_steps,
+               "link_gbs": link_used, "link_ceiling_gbs": link_ceiling, "link_frac": link_used / link_ceiling,
+               "link_note": "GB/s per rank (slowest rank): link_gbs inside the timed end-to-end steps, link_ceiling_gbs a plain "
+                            "pinned cudaMemcpyAsync of the same buffer with all ranks copying at once",
                "api": "slang_b200.host_step.HostStepper.step (pinned host inputs, chunked copies overlapped with the "
                       "teacher's forward kernel and learnGradient; targets computed on the device)"}
         del xh
@@ -635,13 +683,16 @@ def main():
             "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": workload_name(args), "global_batch": args.batch, "per_gpu_batch": count,
-                       "parallelism": "dp%d" % world, "gradient_sum": "rank-ordered gather" if args.deterministic_sum else "all-reduce", "l2": "inputs (%.1f GB per step per GPU) larger than L2; two batches alternate" % (count * 256 / 1e9)},
+                       "parallelism": "dp%d" % world, "gradient_sum": ("rank-ordered gather" if args.deterministic_sum else "all-reduce") + " through mlp_allreduce_grads (NCCL bound inside the library)", "l2": "inputs (%.1f GB per step per GPU) larger than L2; two batches alternate" % (count * 256 / 1e9)},
             "clocks": clocks, "gpu_launches": launches, "e2e": e2e,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_sustained"], "unit": "TFLOP/s",
                          "frac": achieved / peaks["bf16_sustained"], "frac_of_burst": achieved / peaks["bf16_burst"],
-                         # dram read + write bytes of one launch: 275.1 MB captured by ncu on a 2^20-sample launch
-                         # (profiles/learn_gradient_wide_c4.md), scaled by the samples of this launch
-                         "traffic": int(round(275.1e6 / 1048576 * count)), "traffic_source": "ncu capture at 2^20 samples, scaled per sample",
+                         # DRAM read + write bytes of one launch: a constant from one profiler capture of a
+                         # 2^20-sample launch (275.1 MB; the algorithmic bytes are 268.4 MB), scaled by this
+                         # launch's samples.  Not measured in this run.
+                         "traffic": int(round(275.1e6 / 1048576 * count)), "traffic_static": True,
+                         "traffic_source": "static: ncu capture of a 2^20-sample launch, scaled per sample",
+                         "algorithmic_bytes": count * 256,
                          "peak_source": peaks["source"] + " (sustained bf16 GEMM; kernel timed inside the step loop)",
                          "kernel": "learn_gradient_wide_kernel", "kernel_ms": kernel_ms, "flop_per_sample": flops,
                          "hbm_gbs": count * 256 / (kernel_ms * 1e-3) / 1e9},
@@ -668,7 +719,26 @@ def main():
             line["gpu_baseline"] = {"value": n_simt / (e0.elapsed_time(e1) * 1e-3), "unit": UNIT,
                                     "kind": "one thread per sample on the same GPU (the example kernels' structure, this library's learnGradient_simt)",
                                     "sample": "%d samples, learnGradient + adjustParameters once" % n_simt}
+        if world == 1 and not args.no_sub:
+            # The other configurations under the same clock, in this process: configurations 2 and 3
+            # at their stated sizes (training step and forward), configuration 5 at two batch sizes per width.
+            del xs, ts
+            torch.cuda.empty_cache()
+            sub = {}
+            for name, n in (("c2", 1 << 20), ("c3", 1 << 24)):
+                r = measure_narrow(torch, device, dev_t, name, n, 3, 5)
+                sub[name] = {"samples_per_s": r["value"], "ms_per_step": r["ms_per_step"], "kernel_ms": r["roofline"]["kernel_ms"],
+                             "tflops": r["roofline"]["achieved"], "roofline_frac_of_burst": r["roofline"]["frac"],
+                             "forward_samples_per_s": r["forward"]["samples_per_s"], "global_batch": n,
+                             "implementation": r["implementation"], "workload": r["config"]["workload"]}
+            pts = measure_forward_points(torch, device, dev_t, (16, 32, 64, 128), (1 << 20, 1 << 24), 3, 5)
+            sub["c5"] = {"points": [{k: p[k] for k in ("width", "batch", "samples_per_s", "hbm_frac", "tflops", "tensor_frac_of_burst")} for p in pts],
+                         "workload": "forward only, depth-4 ReLU, fp16 weights, fp32 outputs; hbm_frac = 6w bytes per sample over the measured copy bandwidth"}
+            line["sub"] = sub
         print(json.dumps(line), flush=True)
+    if comm is not None:
+        comm.wait(60000)  # drains the stream with the collective library's asynchronous errors polled
+        comm.destroy()
     device.destroy()
     if world > 1:
         dist.destroy_process_group()

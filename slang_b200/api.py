@@ -88,6 +88,9 @@ class Device:
             check(load().mlp_device_create_on_stream(ordinal, ctypes.c_void_p(stream), ctypes.byref(h)))
         self.handle = h
         self.ordinal = ordinal
+        # the cudaStream_t the kernels run on when the caller supplied it; None when the library
+        # created its own stream, which a caller cannot order other work against
+        self.stream = stream
 
     def create_buffer(self, size, init=None):
         h = ctypes.c_void_p()

@@ -26,6 +26,15 @@ class HostStepper:
         self.chunk = chunk_samples
         self.allreduce = allreduce
         dev = torch.device("cuda", trainer.device.ordinal)
+        # The copies are ordered against the kernels with events, so the kernels' stream must be one
+        # this class can record on and wait on: the stream the Device was created on.
+        if trainer.device.stream is None:
+            raise ValueError("HostStepper needs a Device created on a caller's stream (Device(ordinal, stream=...)): "
+                             "the library's own private stream cannot be ordered against the copies")
+        if teacher is not None and teacher.device is not trainer.device:
+            raise ValueError("the teacher must run on the trainer's Device (same stream)")
+        self.compute = (torch.cuda.default_stream(dev) if trainer.device.stream == 0
+                        else torch.cuda.ExternalStream(trainer.device.stream, device=dev))
         self.x_dev = [torch.empty((chunk_samples, cfg.input_width), dtype=_TORCH_DTYPE[cfg.input_dtype], device=dev) for _ in range(2)]
         self.t_dev = [torch.empty((chunk_samples, cfg.out_dim), dtype=_TORCH_DTYPE[cfg.target_dtype], device=dev) for _ in range(2)]
         self.copy_stream = torch.cuda.Stream(device=dev)
@@ -39,7 +48,7 @@ class HostStepper:
         Returns (max loss, mean loss) of this rank's samples."""
         from .api import FLAG_OUTPUT_STORAGE_TYPE
         count = x_host.shape[0]
-        compute = torch.cuda.current_stream()
+        compute = self.compute
         self.h2d_bytes = x_host.numel() * x_host.element_size()
         if self.teacher is None:
             self.h2d_bytes += t_host.numel() * t_host.element_size()

@@ -70,6 +70,8 @@ def _act_problem(hidden, output, dtype, count, seed):
     cfg = C.make_config(dims, dtype=dtype, hidden_act=hidden, output_act=output, act_alpha=0.05, adam_master=1)
     p0 = C.from_storage(C.init_params(cfg, seed=seed, scheme="xavier"), dtype).copy()
     w_off, b_off, _ = C.param_layout(cfg)
+    if hidden == C.ACT_EXP or output == C.ACT_EXP:
+        p0 *= 0.25  # exp of exp of exp: keep the pre-activations small enough to stay finite
     for l in range(cfg.n_layers):  # non-zero biases so that pre-activations are not centred on the tie points
         p0[b_off[l]:b_off[l] + dims[l + 1]] = rng.uniform(-0.3, 0.3, dims[l + 1])
     p0 = C.to_storage(p0, dtype)
@@ -93,6 +95,7 @@ def test_every_activation_one_thread_per_sample(device, act):
     err = max(layer_rel_errs(cfg, g_gpu, g_ref))
     exact = act in (C.ACT_IDENTITY, C.ACT_RELU, C.ACT_LEAKY_RELU, C.ACT_LEAKY_MAX)
     print(ACT_NAME[act], "simt fp32 gradient rel err %.3g" % err)
+    assert np.all(np.isfinite(g_ref)) and np.any(g_ref != 0)
     assert err == 0.0 if exact else err < 2e-6
     assert abs(l_gpu[0][1] - l_ref[0][1]) <= 2e-6 * abs(l_ref[0][1])
     yb = device.create_buffer(count * cfg.out_dim * 4)
@@ -119,6 +122,7 @@ def test_every_activation_on_the_padded_tensor_core_kernel(device, act, dtype):
     assert tr.k_learn.implementation == "tcgen05" and tr.k_forward.implementation == "tcgen05"
     err = max(layer_rel_errs(cfg, g_gpu, g_ref))
     print(ACT_NAME[act], "tcgen05 gradient rel err %.3g" % err)
+    assert np.all(np.isfinite(g_ref)) and np.any(g_ref != 0)
     assert err < 1e-2
     assert abs(l_gpu[0][1] - l_ref[0][1]) <= 1e-2 * abs(l_ref[0][1])
     assert abs(l_gpu[0][0] - l_ref[0][0]) <= 1e-2 * abs(l_ref[0][0])
