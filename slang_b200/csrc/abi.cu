@@ -527,15 +527,16 @@ int32_t mlp_layout_to_portable(MlpDevice* d, const MlpNetworkShape* shape, uint6
     return layout_convert(d, shape, false, optimal, portable);
 }
 
-// Diagnostics, not part of the public header: cycle counts recorded by CTA 0 of the last
-// tensor-core learnGradient (control thread total / waiting, tiles, epilogue warp total / waiting).
-int32_t mlpb200_debug_tc_timing(MlpDevice* d, unsigned long long* out8)
+#ifdef MLPB200_TRACE
+// Developer builds only: the time stamps CTA 0 of the last wide tensor-core learnGradient recorded.
+int32_t mlpb200_debug_tc_timing(MlpDevice* d, unsigned long long* out256)
 {
-    if (!d || !out8) return fail(MLP_E_INVALID_ARG, "null argument");
+    if (!d || !out256) return fail(MLP_E_INVALID_ARG, "null argument");
     CUDA_TRY(cudaSetDevice(d->ordinal));
-    CUDA_TRY(tc_read_timing(d->stream, d->tc, out8));
+    CUDA_TRY(tc_read_timing(d->stream, d->tc, out256));
     return MLP_OK;
 }
+#endif
 
 int32_t mlp_param_layout(const MlpConfig* config, int64_t* w_off, int64_t* b_off, int64_t* total)
 {

@@ -51,8 +51,8 @@ cudaError_t launch_learn_gradient_narrow(cudaStream_t st, TcWorkspace* ws, const
 // frequency encoding); fp32 outputs.
 cudaError_t launch_forward_narrow(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const MlpForwardParams& a,
                                   int* launches, std::string* err);
-// Cycle counts CTA 0 of the last tensor-core learnGradient recorded (diagnostics).
-cudaError_t tc_read_timing(cudaStream_t st, TcWorkspace* ws, unsigned long long* out8);
+// Developer builds (-DMLPB200_TRACE) only: time stamps CTA 0 of the last wide learnGradient recorded.
+cudaError_t tc_read_timing(cudaStream_t st, TcWorkspace* ws, unsigned long long* out256);
 // Reads and clears the device status word (0 = no kernel gave up on a bounded wait).
 cudaError_t tc_read_status(cudaStream_t st, TcWorkspace* ws, uint32_t* status);
 

@@ -17,7 +17,7 @@ struct TcWorkspace {
     int sm_count = 0;
     uint32_t* status = nullptr;            // device word, set by kernels that give up on a wait
     uint32_t* status_host = nullptr;       // pinned copy
-    unsigned long long* timing = nullptr;  // device, 8 words of kernel diagnostics
+    unsigned long long* timing = nullptr;  // device; allocated by developer trace builds only
     EncodeTiledFn encode = nullptr;        // cuTensorMapEncodeTiled, fetched through the runtime
 };
 

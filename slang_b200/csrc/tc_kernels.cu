@@ -44,26 +44,24 @@ enum : uint32_t {
     kStatusCtrlAcc = 1u, kStatusCtrlX = 2u, kStatusEpiAcc = 4u, kStatusEpiTarget = 8u, kStatusEpiLoss = 16u, kStatusAlign = 32u,
 };
 
-#ifdef MLPB200_SPIN
-#define MLPB200_CTRL_WAIT mbar_wait_spin
+// Developer builds (-DMLPB200_TRACE, never the shipped library) record clock64() time stamps of one
+// tile's hand-offs in CTA 0 into WideTrainParams::timing; the shipped kernel reads no clock.
+#ifdef MLPB200_TRACE
+#define MLPB200_TRACE_AT(cond, slot) do { if (cond) p.timing[slot] = (unsigned long long)clock64(); } while (0)
 #else
-#define MLPB200_CTRL_WAIT mbar_wait
+#define MLPB200_TRACE_AT(cond, slot) do { } while (0)
 #endif
 
 namespace wide {
 constexpr int NS = 64;            // samples per tile
-#ifndef MLPB200_CH
-#define MLPB200_CH 32
-#endif
-constexpr int CH = MLPB200_CH;    // samples per chain (MMA N of the forward / input-gradient products)
+constexpr int CH = 32;            // samples per chain (MMA N of the forward / input-gradient products)
 constexpr int NCH = NS / CH;      // chains per tile
 constexpr int D0 = 64, H = 128, DOUT = 64, NL = 5;
-#ifndef MLPB200_CPT
-#define MLPB200_CPT 16
+constexpr int CPT = 8;            // sample columns of EACH chain per epilogue thread
+#ifdef MLPB200_TRACE
+constexpr uint32_t kTraceTile = 3;  // which of CTA 0's tiles a trace build records
 #endif
-constexpr int CPT = MLPB200_CPT;  // sample columns per epilogue thread
-constexpr int kEpiWarps = 4 * (NS / CPT);      // one warp per TMEM lane quarter and column group
-constexpr int kWarpsPerChain = 4 * (CH / CPT);
+constexpr int kEpiWarps = 16;     // 4 TMEM lane quarters x 4 column groups; every warp serves both chains
 constexpr int kThreads = 64 + 32 * kEpiWarps;  // warp 0: TMA + MMA issue, warp 1: TMEM owner, then the epilogue warps
 
 // Shared-memory map (bytes from a 1024-aligned base).  Operand buffers are panels of
@@ -77,11 +75,12 @@ constexpr uint32_t kX = kW4 + 16384;         // 2 buffers x [64 rows x 1 panel]
 constexpr uint32_t kA1 = kX + 2 * 8192;      // A_1..A_4: [128 feature rows][64 samples] each, 128-byte rows
 constexpr uint32_t kDZ4 = kA1 + 4 * 16384;   // [64 rows x 1 panel]: targets land here, dZ_4 replaces them
 constexpr uint32_t kBias = kDZ4 + 8192;      // fp32 [5][128]
-constexpr uint32_t kLossPart = kBias + 5 * 128 * 4;  // fp32 [2][64]
-constexpr uint32_t kBars = kLossPart + 2 * 64 * 4;   // mbarriers: x_full[2], t_full, acc_full[2], acc_free[2], loss_bar[2]
-constexpr uint32_t kTmemPtr = kBars + 14 * 8;
+constexpr uint32_t kLossPart = kBias + 5 * 128 * 4;  // fp32 [8 feature groups][64 samples]
+constexpr uint32_t kBars = kLossPart + 8 * 64 * 4;   // mbarriers: x_full[2], t_full, acc_full[2], acc_free[2], out_full, out_free
+constexpr uint32_t kTmemPtr = kBars + 12 * 8;
 constexpr uint32_t kAbort = kTmemPtr + 4;
 constexpr uint32_t kSmemBytes = kAbort + 4;   // the dynamic shared-memory base must be 1024-byte aligned (checked at run time)
+static_assert(kSmemBytes <= 232448, "shared-memory map exceeds the per-CTA limit");
 
 // Tensor-memory columns.
 constexpr uint32_t kColDW1 = 0, kColDW4T = 384, kColAcc = 448, kTmemCols = 512;
@@ -154,15 +153,18 @@ __device__ __forceinline__ void act_pair2(float2 z, float alpha, float2& a, floa
 {
     if constexpr (ACT == MLP_ACT_GELU_TANH) {
         const float c0 = MLPB200_SQRT_2_OVER_PI, c1 = MLPB200_SQRT_2_OVER_PI * MLPB200_GELU_C;
-        const float2 C0 = make_float2(c0, c0), C1 = make_float2(c1, c1), C3 = make_float2(3.0f * c1, 3.0f * c1);
-        const float2 HALF = make_float2(0.5f, 0.5f), ONE = make_float2(1.0f, 1.0f);
+        const float2 C0 = make_float2(c0, c0), C1 = make_float2(c1, c1), C3 = make_float2(6.0f * c1, 6.0f * c1), C2 = make_float2(2.0f * c0, 2.0f * c0);
+        const float2 HALF = make_float2(0.5f, 0.5f), NHALF = make_float2(-0.5f, -0.5f);
+        // With s = (1 + tanh u) / 2 and u = z (c0 + c1 z^2): gelu = z s and, because 1 - tanh^2 = 4 s (1 - s),
+        // gelu' = s + z s' = s + (z s) (1 - s) (2 c0 + 6 c1 z^2): nine packed operations and two tanh.
         const float2 z2 = __fmul2_rn(z, z);
         const float2 u = __fmul2_rn(z, __ffma2_rn(C1, z2, C0));
         const float2 t = make_float2(tanh_approx(u.x), tanh_approx(u.y));
-        const float2 hz = __fmul2_rn(z, HALF);
-        a = __ffma2_rn(hz, t, hz);
-        const float2 oms = __ffma2_rn(make_float2(-t.x, -t.y), t, ONE);
-        d = __ffma2_rn(__fmul2_rn(hz, oms), __ffma2_rn(C3, z2, C0), __ffma2_rn(HALF, t, HALF));
+        const float2 sg = __ffma2_rn(HALF, t, HALF);
+        a = __fmul2_rn(z, sg);
+        const float2 om = __ffma2_rn(NHALF, t, HALF);
+        const float2 w = __ffma2_rn(C3, z2, C2);
+        d = __ffma2_rn(__fmul2_rn(a, om), w, sg);
     } else {
         act_pair<ACT>(z.x, alpha, a.x, d.x);
         act_pair<ACT>(z.y, alpha, a.y, d.y);
@@ -177,7 +179,7 @@ struct WideTrainParams {
     uint32_t n_tiles;
     float loss_scale;  // 1 / outputs for the mean-squared error, 1 for the sum of squares
     float act_alpha;
-    unsigned long long* timing;  // diagnostics written by CTA 0: cycles spent waiting / issuing / computing
+    unsigned long long* timing;  // trace builds only: time stamps written by CTA 0
 };
 
 template <int FMT, int ACT>
@@ -199,7 +201,8 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
     uint64_t* t_full = bars + 2;
     uint64_t* acc_full = bars + 3;  // [2], one per chain
     uint64_t* acc_free = bars + 5;  // [2]
-    uint64_t* loss_bar = bars + 7;  // [2]
+    uint64_t* out_full = bars + 7;  // the output layer's accumulator (whole tile) is complete
+    uint64_t* out_free = bars + 8;  // ... has been consumed, dZ_4 and the loss terms are in shared memory
     uint32_t* tmem_ptr = (uint32_t*)(smem + kTmemPtr);
     volatile uint32_t* abort_flag = (volatile uint32_t*)(smem + kAbort);
     float* s_bias = (float*)(smem + kBias);
@@ -215,9 +218,10 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
         mbar_init(t_full, 1);
         for (int h = 0; h < NCH; ++h) {
             mbar_init(&acc_full[h], 1);
-            mbar_init(&acc_free[h], kWarpsPerChain);       // the chain's epilogue warps
-            mbar_init(&loss_bar[h], kWarpsPerChain / 2);   // ... of which those that hold output features
+            mbar_init(&acc_free[h], kEpiWarps);  // every epilogue warp works on every chain
         }
+        mbar_init(out_full, 1);
+        mbar_init(out_free, kEpiWarps);
         *abort_flag = 0u;
         fence_mbar_init();
         prefetch_tmap(&tmap_x);
@@ -249,33 +253,39 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
 
     if (warp == 0) {
         // =================================== control warp ==========================================
-        // The 64 samples of a tile run as two independent chains of 32 (h = 0, 1): while the epilogue
-        // warps of one chain work on their accumulator half, the tensor pipe runs the other chain's
-        // product.  Both chains share the operand buffers (rows 32h..32h+31) and the weight-gradient
-        // accumulators; they meet once per tile, at the dW_0 product.
-        // The whole warp walks the schedule so that addresses stay warp-uniform; one elected lane
-        // issues the TMA loads, the MMAs and the commits.  (One control warp per chain was measured
-        // slower: the products of both chains share one tensor pipe either way.)
+        // The 64 samples of a tile run as two chains of 32 (h = 0, 1) through the hidden layers: while the
+        // epilogue warps work on one chain's accumulator, the tensor pipe runs the other chain's product.
+        // Both chains share the operand buffers (sample columns 32h..32h+31) and the weight-gradient
+        // accumulators.  They meet twice per tile: at the output layer, whose product covers the whole
+        // tile with the samples on the TMEM lanes (see the epilogue), and at the dW_0 product.
+        // The whole warp walks the schedule (the waits); one elected lane issues the TMA loads, the MMAs
+        // and the commits as straight-line code: the fewer instructions this warp needs per product, the
+        // less its issue rate suffers from the four busy epilogue warps on its scheduler.
         if (n_my_tiles > 0) {
             const bool leader = elect_one();
             constexpr uint32_t F = E::kUmmaFmt;
             constexpr uint32_t kIdescFwd0 = umma_idesc(F, 0, 0, 128, CH);   // W_0 (K) x input tile (K)
             constexpr uint32_t kIdescFwd = umma_idesc(F, 0, 1, 128, CH);    // W (K) x act (MN: samples contiguous)
+            constexpr uint32_t kIdescOut = umma_idesc(F, 1, 0, 128, 64);    // A_4 (MN: samples on the lanes) x W_4 (K)
             constexpr uint32_t kIdescDx4 = umma_idesc(F, 1, 0, 128, CH);    // W_4^T (MN) x dZ_4 (K: features contiguous)
             constexpr uint32_t kIdescDx = umma_idesc(F, 1, 1, 128, CH);     // W^T (MN) x dZ (MN)
             constexpr uint32_t kIdescDw = umma_idesc(F, 0, 0, 128, 128);    // dZ (K = samples) x act (K = samples)
             constexpr uint32_t kIdescDw64 = umma_idesc(F, 0, 1, 128, 64);   // act or dZ_0 (K) x dZ_4 or input tile (MN)
-            uint32_t step = 0;   // both chains are at the same step whenever this warp looks
+            uint32_t n_free0 = 0, n_free1 = 0;  // phases of acc_free[h] this warp has consumed
             bool ok = true;
-            long long t_wait = 0;
-            const long long t_start = clock64();
+#ifdef MLPB200_TRACE
+            bool tr_on = false;  // this lane records the traced tile
+            uint32_t tr_step = 0;
+#endif
             // Every phase of a barrier is observed in order: a parity wait only means something if
             // the waiter has seen all earlier phases complete.
             auto chain_wait = [&](int h) {
-                const long long t0 = clock64();
-                if (step > 0) ok = ok && MLPB200_CTRL_WAIT(&acc_free[h], (step - 1) & 1u, abort_flag, p.status, kStatusCtrlAcc);
+                MLPB200_TRACE_AT(tr_on, (tr_step * 2 + h) * 3 + 0);
+                uint32_t& n = h == 0 ? n_free0 : n_free1;
+                ok = ok && mbar_wait(&acc_free[h], n & 1u, abort_flag, p.status, kStatusCtrlAcc);
+                ++n;
                 tc_fence_after();
-                t_wait += clock64() - t0;
+                MLPB200_TRACE_AT(tr_on, (tr_step * 2 + h) * 3 + 1);
             };
             // Descriptors cost one 32-bit add each: the high word (8-row groups 1024 bytes apart,
             // version 1, 128-byte swizzle) is the same for every operand and the low word is the
@@ -306,40 +316,70 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                 const uint32_t next_tile = blockIdx.x + (it + 1) * gridDim.x;
                 const bool has_next = it + 1 < n_my_tiles;
                 const uint32_t xbuf = kX + b * 8192u;
+#ifdef MLPB200_TRACE
+                tr_on = leader && blockIdx.x == 0 && it == kTraceTile && p.timing;
+                tr_step = 0;
+#endif
                 // ---- forward, layer 0 ----
 #pragma unroll
                 for (int h = 0; h < NCH; ++h) {
-                    chain_wait(h);
+                    if (it > 0) chain_wait(h);  // the previous tile's dW_0 has left the accumulator
                     if (h == 0) ok = ok && mbar_wait(&x_full[b], (it >> 1) & 1u, abort_flag, p.status, kStatusCtrlX);
-                    if (ok) {
+                    if (ok && leader) {
                         const uint32_t acc = tmem_base + kColAcc + (uint32_t)(h * CH);
 #pragma unroll
                         for (int k = 0; k < D0 / 16; ++k)
-                            umma_f16_warp(acc, desc_k(kW0, 16384u, k), desc_k(xbuf + (uint32_t)h * (uint32_t)(CH * 128), 8192u, k), kIdescFwd0, k > 0);
-                        umma_commit_warp(&acc_full[h]);
+                            umma_f16(acc, desc_k(kW0, 16384u, k), desc_k(xbuf + (uint32_t)h * (uint32_t)(CH * 128), 8192u, k), kIdescFwd0, k > 0);
+                        umma_commit(&acc_full[h]);
+                        MLPB200_TRACE_AT(tr_on, (tr_step * 2 + h) * 3 + 2);
                     }
                 }
-                ++step;
-                // ---- forward, layers 1..4 ----
+#ifdef MLPB200_TRACE
+                ++tr_step;
+#endif
+                // ---- forward, layers 1..3 ----
 #pragma unroll
-                for (int l = 1; l < NL; ++l) {
+                for (int l = 1; l < NL - 1; ++l) {
                     const uint32_t wpanel = (uint32_t)out_dim(l) * 128u;
                     const uint32_t abuf = kA1 + (uint32_t)(l - 1) * 16384u;
 #pragma unroll
                     for (int h = 0; h < NCH; ++h) {
                         chain_wait(h);
-                        if (ok) {
+                        if (ok && leader) {
                             const uint32_t acc = tmem_base + kColAcc + (uint32_t)(h * CH);
                             const uint32_t half = (uint32_t)h * (uint32_t)(CH * 2);  // the chain's samples inside a feature row
 #pragma unroll
                             for (int k = 0; k < H / 16; ++k)
-                                umma_f16_warp(acc, desc_k(w_off(l), wpanel, k), desc_mn(abuf + half, 8192u, k), kIdescFwd, k > 0);
-                            umma_commit_warp(&acc_full[h]);
+                                umma_f16(acc, desc_k(w_off(l), wpanel, k), desc_mn(abuf + half, 8192u, k), kIdescFwd, k > 0);
+                            umma_commit(&acc_full[h]);
+                            MLPB200_TRACE_AT(tr_on, (tr_step * 2 + h) * 3 + 2);
                         }
                     }
-                    ++step;
+#ifdef MLPB200_TRACE
+                    ++tr_step;
+#endif
                 }
+                // ---- output layer, whole tile: Z_4 [samples x 64] = A_4 [samples x 128] . W_4^T with the samples
+                //      on the TMEM lanes.  A_4's rows hold 64 samples; the second half of the 128 lanes reads the
+                //      same 64 samples again (panel stride 0), so lanes 64..127 mirror lanes 0..63 and all four
+                //      lane quarters can share the output-layer epilogue ----
+#pragma unroll
+                for (int h = 0; h < NCH; ++h) chain_wait(h);
+                if (ok && leader) {
+#pragma unroll
+                    for (int k = 0; k < H / 16; ++k)
+                        umma_f16(tmem_base + kColAcc, desc_mn(kA1 + 3u * 16384u, 0u, k), desc_k(kW4, 8192u, k), kIdescOut, k > 0);
+                    umma_commit(out_full);
+                    MLPB200_TRACE_AT(tr_on, (tr_step * 2 + 0) * 3 + 2);
+                }
+#ifdef MLPB200_TRACE
+                ++tr_step;
+#endif
                 // ---- backward ----
+                MLPB200_TRACE_AT(tr_on, (tr_step * 2 + 0) * 3 + 0);
+                ok = ok && mbar_wait(out_free, it & 1u, abort_flag, p.status, kStatusCtrlAcc);  // dZ_4 is in place
+                tc_fence_after();
+                MLPB200_TRACE_AT(tr_on, (tr_step * 2 + 0) * 3 + 1);
 #pragma unroll
                 for (int l = NL - 1; l >= 1; --l) {
                     const uint32_t wpanel = (uint32_t)out_dim(l) * 128u;
@@ -347,47 +387,49 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                     const uint32_t abuf = kA1 + (uint32_t)(l - 1) * 16384u;                   // A_l
 #pragma unroll
                     for (int h = 0; h < NCH; ++h) {
-                        chain_wait(h);
-                        if (ok) {
+                        if (l < NL - 1) chain_wait(h);
+                        if (ok && leader) {
                             const uint32_t acc = tmem_base + kColAcc + (uint32_t)(h * CH);
                             const uint32_t row = (uint32_t)h * (uint32_t)(CH * 128);  // sample-major tiles: 32 rows of 128 bytes
                             const uint32_t half = (uint32_t)h * (uint32_t)(CH * 2);   // feature-major tiles: 64 bytes inside a row
                             const uint32_t prior = (it > 0 || h > 0) ? 1u : 0u;  // the launch's first product overwrites
-                            {
-                                if (l == NL - 1) {
+                            if (l == NL - 1) {
 #pragma unroll
-                                    for (int k = 0; k < out_dim(l) / 16; ++k)
-                                        umma_f16_warp(acc, desc_mn(w_off(l), wpanel, k), desc_k(dzbuf + row, 8192u, k), kIdescDx4, k > 0);
+                                for (int k = 0; k < out_dim(l) / 16; ++k)
+                                    umma_f16(acc, desc_mn(w_off(l), wpanel, k), desc_k(dzbuf + row, 8192u, k), kIdescDx4, k > 0);
 #pragma unroll
-                                    for (int k = 0; k < CH / 16; ++k)
-                                        umma_f16_warp(tmem_base + kColDW4T, desc_k(abuf + half, 0u, k), desc_mn(dzbuf + row, 8192u, k),
-                                                 kIdescDw64, prior | (uint32_t)(k > 0));
-                                } else {
+                                for (int k = 0; k < CH / 16; ++k)
+                                    umma_f16(tmem_base + kColDW4T, desc_k(abuf + half, 0u, k), desc_mn(dzbuf + row, 8192u, k),
+                                             kIdescDw64, prior | (uint32_t)(k > 0));
+                            } else {
 #pragma unroll
-                                    for (int k = 0; k < out_dim(l) / 16; ++k)
-                                        umma_f16_warp(acc, desc_mn(w_off(l), wpanel, k), desc_mn(dzbuf + half, 8192u, k), kIdescDx, k > 0);
+                                for (int k = 0; k < out_dim(l) / 16; ++k)
+                                    umma_f16(acc, desc_mn(w_off(l), wpanel, k), desc_mn(dzbuf + half, 8192u, k), kIdescDx, k > 0);
 #pragma unroll
-                                    for (int k = 0; k < CH / 16; ++k)
-                                        umma_f16_warp(tmem_base + kColDW1 + (uint32_t)(l - 1) * 128u, desc_k(dzbuf + half, 0u, k),
-                                                 desc_k(abuf + half, 0u, k), kIdescDw, prior | (uint32_t)(k > 0));
-                                }
-                                umma_commit_warp(&acc_full[h]);
+                                for (int k = 0; k < CH / 16; ++k)
+                                    umma_f16(tmem_base + kColDW1 + (uint32_t)(l - 1) * 128u, desc_k(dzbuf + half, 0u, k),
+                                             desc_k(abuf + half, 0u, k), kIdescDw, prior | (uint32_t)(k > 0));
                             }
+                            umma_commit(&acc_full[h]);
+                            MLPB200_TRACE_AT(tr_on, (tr_step * 2 + h) * 3 + 2);
                         }
                     }
-                    ++step;
+#ifdef MLPB200_TRACE
+                    ++tr_step;
+#endif
                 }
-                // ---- dW_0 of the whole tile into the 64 accumulator columns (both chains' epilogues
-                //      add their columns to registers); then the next tile's loads ----
+                // ---- dW_0 of the whole tile into the 64 accumulator columns (the epilogue adds them to
+                //      registers); then the next tile's loads ----
 #pragma unroll
                 for (int h = 0; h < NCH; ++h) chain_wait(h);
                 if (ok) {
-#pragma unroll
-                    for (int k = 0; k < NS / 16; ++k)
-                        umma_f16_warp(tmem_base + kColAcc, desc_k(kA1, 0u, k), desc_mn(xbuf, 8192u, k), kIdescDw64, k > 0);
-#pragma unroll
-                    for (int h = 0; h < NCH; ++h) umma_commit_warp(&acc_full[h]);
                     if (leader) {
+#pragma unroll
+                        for (int k = 0; k < NS / 16; ++k)
+                            umma_f16(tmem_base + kColAcc, desc_k(kA1, 0u, k), desc_mn(xbuf, 8192u, k), kIdescDw64, k > 0);
+#pragma unroll
+                        for (int h = 0; h < NCH; ++h) umma_commit(&acc_full[h]);
+                        MLPB200_TRACE_AT(tr_on, (tr_step * 2 + 0) * 3 + 2);
                         if (has_next) {
                             // Both chains are past every product that read the other X buffer and dZ_4.
                             mbar_expect_tx(&x_full[b ^ 1u], 8192);
@@ -399,12 +441,6 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                     if (has_next) ++loads_issued;
                     __syncwarp();
                 }
-                ++step;
-            }
-            if (blockIdx.x == 0 && p.timing && leader) {
-                p.timing[0] = (unsigned long long)(clock64() - t_start);  // control warp: whole tile loop
-                p.timing[1] = (unsigned long long)t_wait;                 // ... of which waiting for epilogues
-                p.timing[2] = n_my_tiles;
             }
             if (*abort_flag && leader) {
                 // Give the copies still in flight a bounded time to land before the CTA exits.
@@ -412,234 +448,301 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                 mbar_drain(t_full, (loads_issued - 1) & 1u);
             }
         }
+#ifdef MLPB200_TRACE
+    } else if (warp == 1) {
+        // Trace builds: the otherwise idle warp watches the accumulator barriers and stamps the moment each
+        // chain's products complete, independent of what the epilogue warps are busy with.
+        if (blockIdx.x == 0 && p.timing && n_my_tiles > kTraceTile) {
+            uint32_t nf[2] = {0, 0};
+            bool ok = true;
+            for (uint32_t it = 0; it <= kTraceTile && ok; ++it) {
+                uint32_t st = 0;
+                for (int ph = 0; ph < 10 && ok; ++ph) {
+                    if (ph == 4) {
+                        ok = mbar_wait(out_full, it & 1u, abort_flag, p.status, kStatusEpiAcc);
+                        if (it == kTraceTile && lane == 0) p.timing[200 + st] = (unsigned long long)clock64();
+                        st += 2;
+                        continue;
+                    }
+                    for (int h = 0; h < 2 && ok; ++h) {
+                        ok = mbar_wait(&acc_full[h], nf[h] & 1u, abort_flag, p.status, kStatusEpiAcc);
+                        ++nf[h];
+                        if (it == kTraceTile && lane == 0) p.timing[200 + st + h] = (unsigned long long)clock64();
+                    }
+                    st += 2;
+                }
+            }
+        }
+#endif
     } else if (warp >= 2) {
         // =================================== epilogue warps ========================================
+        // Hidden layers: a thread owns one feature (TMEM lane f) and, of each chain, the eight sample columns
+        // of its column group e, so every warp takes a share of every chain step.  The bias is a
+        // per-thread constant and the hidden bias gradients are per-thread sums.
         const int q = warp & 3;                // TMEM lane quarter this warp may read
-        const int e = (warp - 2) >> 2;         // which group of CPT sample columns
+        const int e = (warp - 2) >> 2;         // column group 0..3
         const int f = q * 32 + lane;           // the feature (TMEM lane) this thread owns
-        const int col0 = e * CPT;
-        const int h = col0 / CH;               // the chain those columns belong to
-        const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16) + kColAcc + (uint32_t)col0;
-        // Sample-major tiles ([64 samples][64 features], the target / dZ_4 buffer): byte offset of
-        // (row col0, feature f) minus the swizzled chunk.  Row s of this thread's column group puts feature
-        // f in 16-byte chunk ((f & 63) >> 3) ^ (s & 7); bits 4..6 of the base are that chunk for row 0, so
-        // the other rows' chunks are an XOR away.
-        const uint32_t pbase = (uint32_t)(f >> 6) * 8192u + (uint32_t)col0 * 128u + (uint32_t)(f & 7) * 2u;
-        const uint32_t xo0 = pbase + (uint32_t)(((f & 63) >> 3) << 4);
-        // Feature-major tiles ([128 features][64 samples]): this thread's CPT samples are CPT / 8
-        // consecutive 16-byte chunks of row f, chunk c stored at c ^ (f & 7).
-        static_assert(CPT % 8 == 0, "a thread's samples fill whole 16-byte chunks");
+        const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
+        // Feature-major tiles ([128 features][64 samples]): this thread's eight samples of chain h are the
+        // 16-byte chunk 4h + e of row f, stored at chunk (4h + e) ^ (f & 7).
         const uint32_t frow = (uint32_t)f * 128u;
-        const uint32_t fchunk0 = (uint32_t)(col0 >> 3);
-        auto store_row = [&](uint8_t* buf, const uint32_t* w) {
-#pragma unroll
-            for (int c = 0; c < CPT / 8; ++c)
-                *(uint4*)(buf + frow + (((fchunk0 + (uint32_t)c) ^ (uint32_t)(f & 7)) << 4)) =
-                    make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
-        };
+        auto chunk_of = [&](int h) -> uint32_t { return frow + ((((uint32_t)(h * 4 + e)) ^ (uint32_t)(f & 7)) << 4); };
 
-        uint32_t dreg[NL - 1][CPT / 2];  // activation derivatives of the four hidden layers, two per register
-        float dw0[CPT];                  // this thread's slice of dW_0 (row f, columns col0..), summed over tiles
-        float db[NL];                    // bias-gradient partial sums
+        uint32_t dreg[NCH][NL - 1][CPT / 2];  // activation derivatives of the four hidden layers, two per register
+        float dw0[16];                        // this thread's slice of dW_0 (row f, columns 16e..16e+15), summed over tiles
+        float db[NL - 1];                     // hidden bias-gradient partial sums (feature f)
+        float db_out = 0.0f;                  // output bias-gradient partial sum (see the output layer)
 #pragma unroll
-        for (int i = 0; i < CPT; ++i) dw0[i] = 0.0f;
+        for (int i = 0; i < 16; ++i) dw0[i] = 0.0f;
 #pragma unroll
-        for (int l = 0; l < NL; ++l) db[l] = 0.0f;
-        float run_max = 0.0f, run_sum = 0.0f;
-        uint32_t step = 0;
+        for (int l = 0; l < NL - 1; ++l) db[l] = 0.0f;
+        float run_max = 0.0f, run_sum = 0.0f;  // per-lane (per sample slot) in the two warps that total the losses
+        uint32_t n_full0 = 0, n_full1 = 0;     // phases of acc_full[h] this warp has consumed
         bool ok = true;
-        long long e_wait = 0;
-        const long long e_start = clock64();
-        auto wait_acc = [&]() {
-            const long long t0 = clock64();
-            ok = ok && mbar_wait(&acc_full[h], step & 1u, abort_flag, p.status, kStatusEpiAcc);
-            ++step;
-            e_wait += clock64() - t0;
+#ifdef MLPB200_TRACE
+        bool tr_on = false;
+        uint32_t tr_step = 0;
+#endif
+        auto wait_acc = [&](int h) {
+            uint32_t& n = h == 0 ? n_full0 : n_full1;
+            ok = ok && mbar_wait(&acc_full[h], n & 1u, abort_flag, p.status, kStatusEpiAcc);
+            ++n;
+            MLPB200_TRACE_AT(tr_on, 64u + (uint32_t)h * 64u + tr_step * 4 + 0);
         };
-        auto release_acc = [&]() {
+        auto release = [&](uint64_t* bar) {
             tc_fence_before();
             fence_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_free[h]);
+            if (lane == 0) mbar_arrive(bar);
         };
 
         for (uint32_t it = 0; it < n_my_tiles && ok; ++it) {
             const uint32_t tile = blockIdx.x + it * gridDim.x;
+#ifdef MLPB200_TRACE
+            tr_on = blockIdx.x == 0 && it == kTraceTile && p.timing && q == 0 && e == 0 && lane == 0;
+            tr_step = 0;
+#endif
             // ---- forward, hidden layers ----
 #pragma unroll
             for (int l = 0; l < NL - 1; ++l) {
-                wait_acc();
-                if (ok) {
-                    tc_fence_after();
-                    uint32_t v[CPT];
-                    tmem_ld_cols(t_acc, v);
-                    tmem_ld_wait();
-                    uint8_t* dst = smem + kA1 + (uint32_t)l * 16384u;
-                    const float bl = s_bias[l * 128 + f];
-                    const float2 bias2 = make_float2(bl, bl);
-                    uint32_t aw[CPT / 2];
+                const float bl = s_bias[l * 128 + f];
+                const float2 bias2 = make_float2(bl, bl);
 #pragma unroll
-                    for (int s = 0; s < CPT; s += 2) {
-                        // bias, storage rounding of the pre-activation (one paired conversion), activation
-                        const float2 zf = __fadd2_rn(make_float2(__uint_as_float(v[s]), __uint_as_float(v[s + 1])), bias2);
-                        const uint32_t zr = E::pack2(zf.x, zf.y);
-                        float2 a, d;
-                        act_pair2<ACT>(make_float2(E::unpack_lo(zr), E::unpack_hi(zr)), p.act_alpha, a, d);
-                        aw[s >> 1] = E::pack2(a.x, a.y);
-                        dreg[l][s >> 1] = E::pack2(d.x, d.y);
+                for (int h = 0; h < NCH; ++h) {
+                    wait_acc(h);
+                    if (ok) {
+                        tc_fence_after();
+                        uint32_t v[CPT];
+                        tmem_ld_cols(lane_base + kColAcc + (uint32_t)(h * CH + e * CPT), v);
+                        tmem_ld_wait();
+                        MLPB200_TRACE_AT(tr_on, 64u + (uint32_t)h * 64u + tr_step * 4 + 1);
+                        uint32_t aw[CPT / 2];
+#pragma unroll
+                        for (int s = 0; s < CPT; s += 2) {
+                            // bias, storage rounding of the pre-activation (one paired conversion), activation
+                            const float2 zf = __fadd2_rn(make_float2(__uint_as_float(v[s]), __uint_as_float(v[s + 1])), bias2);
+                            const uint32_t zr = E::pack2(zf.x, zf.y);
+                            float2 a, d;
+                            act_pair2<ACT>(make_float2(E::unpack_lo(zr), E::unpack_hi(zr)), p.act_alpha, a, d);
+                            aw[s >> 1] = E::pack2(a.x, a.y);
+                            dreg[h][l][s >> 1] = E::pack2(d.x, d.y);
+                        }
+                        *(uint4*)(smem + kA1 + (uint32_t)l * 16384u + chunk_of(h)) = make_uint4(aw[0], aw[1], aw[2], aw[3]);
+                        MLPB200_TRACE_AT(tr_on, 64u + (uint32_t)h * 64u + tr_step * 4 + 2);
+                        release(&acc_free[h]);
+                        MLPB200_TRACE_AT(tr_on, 64u + (uint32_t)h * 64u + tr_step * 4 + 3);
                     }
-                    store_row(dst, aw);
-                    release_acc();
                 }
+#ifdef MLPB200_TRACE
+                ++tr_step;
+#endif
             }
             if (!ok) break;
-            // ---- output layer, loss and dZ_4 ----
+            // ---- output layer, loss and dZ_4: samples on the lanes.  Lane L of the accumulator holds sample
+            //      L % 64 (lanes 64..127 mirror lanes 0..63), so the lane quarters 0, 1 take output features
+            //      0..31 and the quarters 2, 3 features 32..63 of the same 64 samples; a thread owns one sample
+            //      and eight features: one 16-byte chunk of the target row, replaced in place by dZ_4 ----
             {
-                wait_acc();
+                ok = ok && mbar_wait(out_full, it & 1u, abort_flag, p.status, kStatusEpiAcc);
                 ok = ok && mbar_wait(t_full, it & 1u, abort_flag, p.status, kStatusEpiTarget);
                 if (!ok) break;
+                MLPB200_TRACE_AT(tr_on, 64u + tr_step * 4 + 0);
                 tc_fence_after();
-                if (q < 2) {
-                    uint32_t v[CPT];
-                    tmem_ld_cols(t_acc, v);
-                    tmem_ld_wait();
-                    uint8_t* dst = smem + kDZ4;
-                    const float bias_out = s_bias[(NL - 1) * 128 + f];
-                    float lsq[CPT];
+                const int s = (q & 1) * 32 + lane;             // sample slot inside the tile
+                const int fb = (q >> 1) * 32 + e * 8;          // first of this thread's eight output features
+                uint32_t v[8];
+                tmem_ld_cols(lane_base + kColAcc + (uint32_t)fb, v);
+                tmem_ld_wait();
+                MLPB200_TRACE_AT(tr_on, 64u + tr_step * 4 + 1);
+                uint4* slot = (uint4*)(smem + kDZ4 + (uint32_t)s * 128u + ((((uint32_t)(fb >> 3)) ^ (uint32_t)(s & 7)) << 4));
+                const uint4 tq = *slot;
+                const uint32_t tw[4] = {tq.x, tq.y, tq.z, tq.w};
+                const float4 b0 = *(const float4*)(s_bias + (NL - 1) * 128 + fb);
+                const float4 b1 = *(const float4*)(s_bias + (NL - 1) * 128 + fb + 4);
+                const float bo[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+                const bool valid = tile * NS + (uint32_t)s < p.count;
+                const float two_scale = 2.0f * p.loss_scale;
+                float dzf[8];
+                uint32_t zw[4];
+                float loss = 0.0f;
 #pragma unroll
-                    for (int s = 0; s < CPT; ++s) {
-                        const bool valid = tile * NS + col0 + s < p.count;
-                        uint16_t* slot = (uint16_t*)(dst + (xo0 ^ (uint32_t)((s & 7) << 4)) + s * 128);
-                        const float out = E::round(__uint_as_float(v[s]) + bias_out);
-                        const float diff = out - E::unpack(*slot);
-                        const float dz = valid ? E::round((2.0f * p.loss_scale) * diff) : 0.0f;
-                        lsq[s] = valid ? (diff * p.loss_scale) * diff : 0.0f;
-                        *slot = E::pack(dz);
-                        db[NL - 1] += dz;
+                for (int j = 0; j < 8; j += 2) {
+                    const uint32_t op = E::pack2(__uint_as_float(v[j]) + bo[j], __uint_as_float(v[j + 1]) + bo[j + 1]);  // storage rounding
+                    const float d0 = E::unpack_lo(op) - E::unpack_lo(tw[j >> 1]);
+                    const float d1 = E::unpack_hi(op) - E::unpack_hi(tw[j >> 1]);
+                    const uint32_t zp = valid ? E::pack2(two_scale * d0, two_scale * d1) : 0u;
+                    zw[j >> 1] = zp;
+                    dzf[j] = E::unpack_lo(zp);
+                    dzf[j + 1] = E::unpack_hi(zp);
+                    if (valid) {
+                        loss = fmaf(d0 * p.loss_scale, d0, loss);
+                        loss = fmaf(d1 * p.loss_scale, d1, loss);
                     }
-                    release_acc();  // dZ_4 is in place: the backward products can start
-                    // Sum over this warp's 32 features for each sample column: every exchange round
-                    // halves the number of columns a lane carries; afterwards lane c * (32 / CPT)
-                    // holds the sum of column c.
-                    int cnt = CPT;
-#pragma unroll
-                    for (int w = 16; w >= 1; w >>= 1) {
-                        if (cnt > 1) {
-                            const int half = cnt / 2;
-                            const bool upper = (lane & w) != 0;
-#pragma unroll
-                            for (int i = 0; i < half; ++i) {
-                                const float keep = upper ? lsq[i + half] : lsq[i];
-                                const float send = upper ? lsq[i] : lsq[i + half];
-                                lsq[i] = keep + __shfl_xor_sync(0xffffffffu, send, w);
-                            }
-                            cnt = half;
-                        } else {
-                            lsq[0] += __shfl_xor_sync(0xffffffffu, lsq[0], w);
-                        }
-                    }
-                    if ((lane % (32 / CPT)) == 0) s_loss_part[q * 64 + col0 + lane / (32 / CPT)] = lsq[0];
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&loss_bar[h]);
-                } else {
-                    release_acc();
                 }
-                if (q == 0) {
-                    // The other feature half of these samples comes from the warp of quarter 1.
-                    ok = ok && mbar_wait(&loss_bar[h], it & 1u, abort_flag, p.status, kStatusEpiLoss);
-                    if (!ok) break;
-                    float tot = lane < CPT ? s_loss_part[col0 + lane] + s_loss_part[64 + col0 + lane] : 0.0f;
-                    float mx = tot;
+                *slot = make_uint4(zw[0], zw[1], zw[2], zw[3]);
+                s_loss_part[((q >> 1) * 4 + e) * 64 + s] = loss;
+                MLPB200_TRACE_AT(tr_on, 64u + tr_step * 4 + 2);
+                release(out_free);  // dZ_4 and this warp's loss terms are in place
+                MLPB200_TRACE_AT(tr_on, 64u + tr_step * 4 + 3);
+                // Output bias gradient: sum each of the eight features over the warp's 32 samples.  Every
+                // exchange round halves the number of features a lane carries; after three rounds and two
+                // full rounds, lane carries the total of feature fb + 4 * bit4 + 2 * bit3 + bit2 of its index.
+                {
+                    const bool u16 = (lane & 16) != 0, u8 = (lane & 8) != 0, u4 = (lane & 4) != 0;
 #pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) {
-                        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-                        tot += __shfl_xor_sync(0xffffffffu, tot, o);
+                    for (int i = 0; i < 4; ++i) {
+                        const float keep = u16 ? dzf[i + 4] : dzf[i];
+                        const float send = u16 ? dzf[i] : dzf[i + 4];
+                        dzf[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
                     }
-                    run_max = fmaxf(run_max, mx);
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        const float keep = u8 ? dzf[i + 2] : dzf[i];
+                        const float send = u8 ? dzf[i] : dzf[i + 2];
+                        dzf[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+                    }
+                    {
+                        const float keep = u4 ? dzf[1] : dzf[0];
+                        const float send = u4 ? dzf[0] : dzf[1];
+                        dzf[0] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+                    }
+                    dzf[0] += __shfl_xor_sync(0xffffffffu, dzf[0], 2);
+                    dzf[0] += __shfl_xor_sync(0xffffffffu, dzf[0], 1);
+                    db_out += dzf[0];
+                }
+                if (e == 0 && q < 2) {
+                    // This warp totals the per-sample losses of its 32 samples once every warp has written its terms.
+                    ok = ok && mbar_wait(out_free, it & 1u, abort_flag, p.status, kStatusEpiLoss);
+                    if (!ok) break;
+                    float tot = 0.0f;
+#pragma unroll
+                    for (int g = 0; g < 8; ++g) tot += s_loss_part[g * 64 + s];
+                    run_max = fmaxf(run_max, tot);
                     run_sum += tot;
                 }
+#ifdef MLPB200_TRACE
+                ++tr_step;
+#endif
             }
             // ---- backward: dA_l arrives in the accumulator, dZ_{l-1} replaces A_l in shared memory ----
 #pragma unroll
             for (int l = NL - 1; l >= 1; --l) {
-                wait_acc();
-                if (ok) {
-                    tc_fence_after();
-                    uint32_t v[CPT];
-                    tmem_ld_cols(t_acc, v);
-                    tmem_ld_wait();
-                    uint8_t* dst = smem + kA1 + (uint32_t)(l - 1) * 16384u;
-                    float2 dbp = make_float2(0.0f, 0.0f);
-                    uint32_t zw[CPT / 2];
 #pragma unroll
-                    for (int s = 0; s < CPT; s += 2) {
-                        const uint32_t dd = dreg[l - 1][s >> 1];
-                        const float2 g = __fmul2_rn(make_float2(__uint_as_float(v[s]), __uint_as_float(v[s + 1])),
-                                                    make_float2(E::unpack_lo(dd), E::unpack_hi(dd)));
-                        const uint32_t zp = E::pack2(g.x, g.y);
-                        zw[s >> 1] = zp;
-                        dbp = __fadd2_rn(dbp, make_float2(E::unpack_lo(zp), E::unpack_hi(zp)));
+                for (int h = 0; h < NCH; ++h) {
+                    wait_acc(h);
+                    if (ok) {
+                        tc_fence_after();
+                        uint32_t v[CPT];
+                        tmem_ld_cols(lane_base + kColAcc + (uint32_t)(h * CH + e * CPT), v);
+                        tmem_ld_wait();
+                        MLPB200_TRACE_AT(tr_on, 64u + (uint32_t)h * 64u + tr_step * 4 + 1);
+                        float2 dbp = make_float2(0.0f, 0.0f);
+                        uint32_t zw[CPT / 2];
+#pragma unroll
+                        for (int s = 0; s < CPT; s += 2) {
+                            const uint32_t dd = dreg[h][l - 1][s >> 1];
+                            const float2 g = __fmul2_rn(make_float2(__uint_as_float(v[s]), __uint_as_float(v[s + 1])),
+                                                        make_float2(E::unpack_lo(dd), E::unpack_hi(dd)));
+                            const uint32_t zp = E::pack2(g.x, g.y);
+                            zw[s >> 1] = zp;
+                            dbp = __fadd2_rn(dbp, make_float2(E::unpack_lo(zp), E::unpack_hi(zp)));
+                        }
+                        *(uint4*)(smem + kA1 + (uint32_t)(l - 1) * 16384u + chunk_of(h)) = make_uint4(zw[0], zw[1], zw[2], zw[3]);
+                        db[l - 1] += dbp.x + dbp.y;
+                        MLPB200_TRACE_AT(tr_on, 64u + (uint32_t)h * 64u + tr_step * 4 + 2);
+                        release(&acc_free[h]);
+                        MLPB200_TRACE_AT(tr_on, 64u + (uint32_t)h * 64u + tr_step * 4 + 3);
                     }
-                    store_row(dst, zw);
-                    db[l - 1] += dbp.x + dbp.y;
-                    release_acc();
                 }
+#ifdef MLPB200_TRACE
+                ++tr_step;
+#endif
             }
             if (!ok) break;
             // ---- dW_0 of this tile: add the accumulator to the register slice ----
             {
-                wait_acc();
+                wait_acc(0);
+                wait_acc(1);
                 if (!ok) break;
                 tc_fence_after();
-                uint32_t v[CPT];
-                tmem_ld_cols(t_acc, v);
+                uint32_t v[16];
+                tmem_ld_cols(lane_base + kColAcc + (uint32_t)(e * 16), v);
                 tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < CPT; ++i) dw0[i] += __uint_as_float(v[i]);
-                release_acc();
+                for (int i = 0; i < 16; ++i) dw0[i] += __uint_as_float(v[i]);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&acc_free[0]);
+                    mbar_arrive(&acc_free[1]);
+                }
+                MLPB200_TRACE_AT(tr_on, 64u + tr_step * 4 + 3);
             }
         }
 
-        if (blockIdx.x == 0 && warp == 2 && lane == 0 && p.timing) {
-            p.timing[3] = (unsigned long long)(clock64() - e_start);  // epilogue warp: whole tile loop
-            p.timing[4] = (unsigned long long)e_wait;                 // ... of which waiting for the tensor pipe
-        }
         // ---- one add per parameter per CTA ----
         if (ok && !*abort_flag && n_my_tiles > 0) {
             tc_fence_after();
-            constexpr int NE = NS / CPT;  // column groups: each takes 1/NE of every accumulator's columns
-            const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
             for (int l = 1; l <= 3; ++l) {
                 float* dW = (float*)p.net[l].weightsGrad + (size_t)f * 128;
-                for (int c = 0; c < 128 / NE; c += 32) {
-                    const int col = e * (128 / NE) + c;
-                    uint32_t v[32];
-                    tmem_ld_cols(lane_base + kColDW1 + (uint32_t)(l - 1) * 128u + (uint32_t)col, v);
-                    tmem_ld_wait();
+                const int col = e * 32;
+                uint32_t v[32];
+                tmem_ld_cols(lane_base + kColDW1 + (uint32_t)(l - 1) * 128u + (uint32_t)col, v);
+                tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) atomicAdd(dW + col + i, __uint_as_float(v[i]));
-                }
+                for (int i = 0; i < 32; ++i) atomicAdd(dW + col + i, __uint_as_float(v[i]));
             }
             {
                 // dW_4^T: lane = input feature, column = output feature.
                 float* dW = (float*)p.net[4].weightsGrad;
-                uint32_t v[CPT];
-                tmem_ld_cols(lane_base + kColDW4T + (uint32_t)col0, v);
+                uint32_t v[16];
+                tmem_ld_cols(lane_base + kColDW4T + (uint32_t)(e * 16), v);
                 tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < CPT; ++i) atomicAdd(dW + (size_t)(col0 + i) * 128 + f, __uint_as_float(v[i]));
+                for (int i = 0; i < 16; ++i) atomicAdd(dW + (size_t)(e * 16 + i) * 128 + f, __uint_as_float(v[i]));
             }
             {
-                float* dW = (float*)p.net[0].weightsGrad + (size_t)f * 64 + col0;
+                float* dW = (float*)p.net[0].weightsGrad + (size_t)f * 64 + e * 16;
 #pragma unroll
-                for (int i = 0; i < CPT; ++i) atomicAdd(dW + i, dw0[i]);
+                for (int i = 0; i < 16; ++i) atomicAdd(dW + i, dw0[i]);
             }
 #pragma unroll
-            for (int l = 0; l < NL; ++l)
-                if (l < NL - 1 || f < DOUT) atomicAdd((float*)p.net[l].biasesGrad + f, db[l]);
-            if (q == 0 && lane == 0) {
-                atomicMax(p.loss_words, __float_as_uint(run_max));
-                atomicAdd((float*)(p.loss_words + 1), run_sum);
+            for (int l = 0; l < NL - 1; ++l) atomicAdd((float*)p.net[l].biasesGrad + f, db[l]);
+            if ((lane & 3) == 0) {
+                const int j = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+                atomicAdd((float*)p.net[NL - 1].biasesGrad + (q >> 1) * 32 + e * 8 + j, db_out);
+            }
+            if (e == 0 && q < 2) {
+                float mx = run_max, tot = run_sum;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+                    tot += __shfl_xor_sync(0xffffffffu, tot, o);
+                }
+                if (lane == 0) {
+                    atomicMax(p.loss_words, __float_as_uint(mx));
+                    atomicAdd((float*)(p.loss_words + 1), tot);
+                }
             }
         }
     }
@@ -680,8 +783,10 @@ TcWorkspace* tc_workspace_create(int ordinal, std::string* err)
     if (e == cudaSuccess) e = cudaMalloc((void**)&ws->status, sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMemset(ws->status, 0, sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMallocHost((void**)&ws->status_host, sizeof(uint32_t));
-    if (e == cudaSuccess) e = cudaMalloc((void**)&ws->timing, 8 * sizeof(unsigned long long));
-    if (e == cudaSuccess) e = cudaMemset(ws->timing, 0, 8 * sizeof(unsigned long long));
+#ifdef MLPB200_TRACE
+    if (e == cudaSuccess) e = cudaMalloc((void**)&ws->timing, 256 * sizeof(unsigned long long));
+    if (e == cudaSuccess) e = cudaMemset(ws->timing, 0, 256 * sizeof(unsigned long long));
+#endif
     if (e == cudaSuccess) {
         void* fn = nullptr;
         cudaDriverEntryPointQueryResult qres;
@@ -706,12 +811,14 @@ void tc_workspace_destroy(TcWorkspace* ws)
     delete ws;
 }
 
-cudaError_t tc_read_timing(cudaStream_t st, TcWorkspace* ws, unsigned long long* out8)
+#ifdef MLPB200_TRACE
+cudaError_t tc_read_timing(cudaStream_t st, TcWorkspace* ws, unsigned long long* out256)
 {
     cudaError_t e = cudaStreamSynchronize(st);
     if (e != cudaSuccess) return e;
-    return cudaMemcpy(out8, ws->timing, 8 * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
+    return cudaMemcpy(out256, ws->timing, 256 * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
 }
+#endif
 
 cudaError_t tc_read_status(cudaStream_t st, TcWorkspace* ws, uint32_t* status)
 {

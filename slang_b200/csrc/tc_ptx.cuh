@@ -57,20 +57,6 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity)
     return ok != 0;
 }
 
-// Bounded spinning wait without the hardware's suspended polling: lower wake-up latency, for a
-// single control warp whose reaction time is on the critical path.
-__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                               uint32_t* status, uint32_t code)
-{
-    for (uint32_t i = 0; i < 8u * kMaxPolls; ++i) {
-        if (mbar_test_wait(bar, parity)) return true;
-        if ((i & 255u) == 255u && *abort_flag) return false;
-    }
-    *abort_flag = 1u;
-    atomicOr(status, code);
-    return false;
-}
-
 // Bounded wait with the poll limit as an argument.  Returns false when the CTA is aborting (this
 // waiter ran out of polls, or another did): the flag is raised, the code is recorded in the device
 // status word, and every later wait of the CTA returns at once.
@@ -206,6 +192,15 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16])
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ void tmem_ld_32x8(uint32_t taddr, uint32_t (&r)[8])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[8]) { tmem_ld_32x8(taddr, r); }
 __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[32]) { tmem_ld_32x32(taddr, r); }
 __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[16]) { tmem_ld_32x16(taddr, r); }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
