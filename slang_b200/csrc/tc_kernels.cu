@@ -1,7 +1,9 @@
 // Tensor-core (tcgen05 / TMEM / TMA) kernels for sm_100a.
 //
-// learnGradient for the wide network 64 -> 128 -> 128 -> 128 -> 128 -> 64 (16-bit storage, fp32
-// accumulate): one persistent CTA per SM walks 64-sample tiles.  All five weight matrices stay in
+// learnGradient for wide networks (16-bit storage, fp32 accumulate): two to five layers, up to 64 inputs,
+// hidden widths up to 128, up to 64 outputs, every width zero-padded to the shape
+// 64 -> 128 -> ... -> 128 -> 64 that the benchmark network has exactly.  One persistent CTA per SM walks
+// 64-sample tiles.  All five weight matrices stay in
 // shared memory for the whole launch, every layer product of the forward and backward pass is a
 // tcgen05.mma with the accumulator in tensor memory, the weight-gradient products accumulate in
 // tensor memory across all of the CTA's tiles, and each parameter receives one atomic add per CTA at
@@ -56,7 +58,8 @@ namespace wide {
 constexpr int NS = 64;            // samples per tile
 constexpr int CH = 32;            // samples per chain (MMA N of the forward / input-gradient products)
 constexpr int NCH = NS / CH;      // chains per tile
-constexpr int D0 = 64, H = 128, DOUT = 64, NL = 5;
+constexpr int D0 = 64, H = 128, DOUT = 64;  // padded widths: inputs, hidden layers, outputs
+constexpr int kMaxLayers = 5;
 constexpr int CPT = 8;            // sample columns of EACH chain per epilogue thread
 #ifdef MLPB200_TRACE
 constexpr uint32_t kTraceTile = 3;  // which of CTA 0's tiles a trace build records
@@ -74,7 +77,7 @@ constexpr uint32_t kW4 = kW3 + 32768;        // 64 rows x 2 panels (panel stride
 constexpr uint32_t kX = kW4 + 16384;         // 2 buffers x [64 rows x 1 panel]
 constexpr uint32_t kA1 = kX + 2 * 8192;      // A_1..A_4: [128 feature rows][64 samples] each, 128-byte rows
 constexpr uint32_t kDZ4 = kA1 + 4 * 16384;   // [64 rows x 1 panel]: targets land here, dZ_4 replaces them
-constexpr uint32_t kBias = kDZ4 + 8192;      // fp32 [5][128]
+constexpr uint32_t kBias = kDZ4 + 8192;      // fp32 [5][128]; row 4 holds the output layer's biases whatever the layer count
 constexpr uint32_t kLossPart = kBias + 5 * 128 * 4;  // fp32 [8 feature groups][64 samples]
 constexpr uint32_t kBars = kLossPart + 8 * 64 * 4;   // mbarriers: x_full[2], t_full, acc_full[2], acc_free[2], out_full, out_free
 constexpr uint32_t kTmemPtr = kBars + 12 * 8;
@@ -85,9 +88,11 @@ static_assert(kSmemBytes <= 232448, "shared-memory map exceeds the per-CTA limit
 // Tensor-memory columns.
 constexpr uint32_t kColDW1 = 0, kColDW4T = 384, kColAcc = 448, kTmemCols = 512;
 
-__host__ __device__ constexpr uint32_t w_off(int l) { return l == 0 ? kW0 : l == 1 ? kW1 : l == 2 ? kW2 : l == 3 ? kW3 : kW4; }
+// Layer l of an NL-layer network: layer 0 and the output layer have their own regions, the hidden-to-hidden
+// layers take W1..W3 in order (unused regions stay idle for shorter networks).
+__host__ __device__ constexpr uint32_t w_off(int l, int NL) { return l == 0 ? kW0 : l == NL - 1 ? kW4 : kW1 + (uint32_t)(l - 1) * 32768u; }
 __host__ __device__ constexpr int in_dim(int l) { return l == 0 ? D0 : H; }
-__host__ __device__ constexpr int out_dim(int l) { return l == NL - 1 ? DOUT : H; }
+__host__ __device__ constexpr int out_dim(int l, int NL) { return l == NL - 1 ? DOUT : H; }
 }  // namespace wide
 
 template <int FMT> struct Elem;
@@ -145,6 +150,12 @@ __device__ __forceinline__ void act_pair(float z, float alpha, float& a, float& 
         d = 1.0f;
     }
 }
+// Activation chosen at run time (any of the library's activations).
+__device__ __forceinline__ void act_pair_rt(int act, float z, float alpha, float& a, float& d)
+{
+    a = act_value(act, alpha, z);
+    d = act_deriv(act, alpha, z);
+}
 
 // The same on two samples at once with the packed fp32 instructions of sm_100 (two results per
 // issued instruction): the epilogue is bound by instruction issue, not by the arithmetic units.
@@ -172,6 +183,11 @@ __device__ __forceinline__ void act_pair2(float2 z, float alpha, float2& a, floa
 }
 
 struct WideTrainParams {
+    int dims[wide::kMaxLayers + 1];  // the network's real widths
+    int hidden_act;                  // used when the kernel is built for a run-time activation
+    int t_direct;                    // 1: the epilogue reads targets from global memory itself (no tensor map)
+    int target_dtype;
+    const void* targets;             // for t_direct
     const MlpLayerPointers* net;
     uint32_t* loss_words;
     uint32_t* status;
@@ -182,7 +198,7 @@ struct WideTrainParams {
     unsigned long long* timing;  // trace builds only: time stamps written by CTA 0
 };
 
-template <int FMT, int ACT>
+template <int FMT, int ACT, int NL>
 __global__ void __launch_bounds__(wide::kThreads, 1)
 learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_t,
                            const WideTrainParams p)
@@ -232,18 +248,34 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
         tmem_relinquish();
     }
     for (int l = 0; l < NL; ++l) {
-        const int in = in_dim(l), out = out_dim(l);
-        const uint4* src = (const uint4*)p.net[l].weights;  // 16-byte chunks: 8 elements
-        const int chunks_per_row = in / 8;
-        const uint32_t panel_stride = (uint32_t)out * 128u;
-        for (int idx = threadIdx.x; idx < out * chunks_per_row; idx += kThreads) {
+        // Real widths in x out, padded to inp x outp with zeros (padded rows, columns and biases are zero, so
+        // padded features carry no signal forward and receive no gradient).
+        const int in = p.dims[l], out = p.dims[l + 1];
+        const int inp = in_dim(l), outp = out_dim(l, NL);
+        const uint16_t* w16 = (const uint16_t*)p.net[l].weights;
+        const int chunks_per_row = inp / 8;  // 16-byte chunks: 8 elements
+        const uint32_t panel_stride = (uint32_t)outp * 128u;
+        const bool rows_aligned = (in & 7) == 0;
+        for (int idx = threadIdx.x; idx < outp * chunks_per_row; idx += kThreads) {
             const int o = idx / chunks_per_row, c = idx % chunks_per_row;
-            const uint4 v = src[idx];
-            const uint32_t off = w_off(l) + (uint32_t)(c >> 3) * panel_stride + (uint32_t)o * 128u + (uint32_t)(((c & 7) ^ (o & 7)) << 4);
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (o < out && c * 8 < in) {
+                if (rows_aligned) {
+                    v = *(const uint4*)(w16 + (size_t)o * in + c * 8);
+                } else {
+                    uint16_t hw[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) hw[j] = c * 8 + j < in ? w16[(size_t)o * in + c * 8 + j] : (uint16_t)0;
+                    v = make_uint4(hw[0] | ((uint32_t)hw[1] << 16), hw[2] | ((uint32_t)hw[3] << 16), hw[4] | ((uint32_t)hw[5] << 16),
+                                   hw[6] | ((uint32_t)hw[7] << 16));
+                }
+            }
+            const uint32_t off = w_off(l, NL) + (uint32_t)(c >> 3) * panel_stride + (uint32_t)o * 128u + (uint32_t)(((c & 7) ^ (o & 7)) << 4);
             *(uint4*)(smem + off) = v;
         }
+        const int brow = l == NL - 1 ? kMaxLayers - 1 : l;
         for (int j = threadIdx.x; j < 128; j += kThreads)
-            s_bias[l * 128 + j] = j < out ? load_as_f32(FMT, (const void*)p.net[l].biases, j) : 0.0f;
+            s_bias[brow * 128 + j] = j < out ? load_as_f32(FMT, (const void*)p.net[l].biases, j) : 0.0f;
     }
     fence_async_smem();
     tc_fence_before();
@@ -306,8 +338,10 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
             if (leader) {
                 mbar_expect_tx(&x_full[0], 8192);
                 tma_load_2d(smem + kX, &tmap_x, 0, (int32_t)(blockIdx.x * NS), &x_full[0]);
-                mbar_expect_tx(t_full, 8192);
-                tma_load_2d(smem + kDZ4, &tmap_t, 0, (int32_t)(blockIdx.x * NS), t_full);
+                if (!p.t_direct) {
+                    mbar_expect_tx(t_full, 8192);
+                    tma_load_2d(smem + kDZ4, &tmap_t, 0, (int32_t)(blockIdx.x * NS), t_full);
+                }
             }
             uint32_t loads_issued = 1;  // tiles whose X and target loads have been issued (for the drain after an abort)
 
@@ -340,7 +374,7 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                 // ---- forward, layers 1..3 ----
 #pragma unroll
                 for (int l = 1; l < NL - 1; ++l) {
-                    const uint32_t wpanel = (uint32_t)out_dim(l) * 128u;
+                    const uint32_t wpanel = (uint32_t)out_dim(l, NL) * 128u;
                     const uint32_t abuf = kA1 + (uint32_t)(l - 1) * 16384u;
 #pragma unroll
                     for (int h = 0; h < NCH; ++h) {
@@ -350,7 +384,7 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                             const uint32_t half = (uint32_t)h * (uint32_t)(CH * 2);  // the chain's samples inside a feature row
 #pragma unroll
                             for (int k = 0; k < H / 16; ++k)
-                                umma_f16(acc, desc_k(w_off(l), wpanel, k), desc_mn(abuf + half, 8192u, k), kIdescFwd, k > 0);
+                                umma_f16(acc, desc_k(w_off(l, NL), wpanel, k), desc_mn(abuf + half, 8192u, k), kIdescFwd, k > 0);
                             umma_commit(&acc_full[h]);
                             MLPB200_TRACE_AT(tr_on, (tr_step * 2 + h) * 3 + 2);
                         }
@@ -368,7 +402,7 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                 if (ok && leader) {
 #pragma unroll
                     for (int k = 0; k < H / 16; ++k)
-                        umma_f16(tmem_base + kColAcc, desc_mn(kA1 + 3u * 16384u, 0u, k), desc_k(kW4, 8192u, k), kIdescOut, k > 0);
+                        umma_f16(tmem_base + kColAcc, desc_mn(kA1 + (uint32_t)(NL - 2) * 16384u, 0u, k), desc_k(kW4, 8192u, k), kIdescOut, k > 0);
                     umma_commit(out_full);
                     MLPB200_TRACE_AT(tr_on, (tr_step * 2 + 0) * 3 + 2);
                 }
@@ -382,7 +416,7 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                 MLPB200_TRACE_AT(tr_on, (tr_step * 2 + 0) * 3 + 1);
 #pragma unroll
                 for (int l = NL - 1; l >= 1; --l) {
-                    const uint32_t wpanel = (uint32_t)out_dim(l) * 128u;
+                    const uint32_t wpanel = (uint32_t)out_dim(l, NL) * 128u;
                     const uint32_t dzbuf = (l == NL - 1) ? kDZ4 : kA1 + (uint32_t)l * 16384u;  // dZ_l lives in A_{l+1}'s buffer
                     const uint32_t abuf = kA1 + (uint32_t)(l - 1) * 16384u;                   // A_l
 #pragma unroll
@@ -395,16 +429,16 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                             const uint32_t prior = (it > 0 || h > 0) ? 1u : 0u;  // the launch's first product overwrites
                             if (l == NL - 1) {
 #pragma unroll
-                                for (int k = 0; k < out_dim(l) / 16; ++k)
-                                    umma_f16(acc, desc_mn(w_off(l), wpanel, k), desc_k(dzbuf + row, 8192u, k), kIdescDx4, k > 0);
+                                for (int k = 0; k < out_dim(l, NL) / 16; ++k)
+                                    umma_f16(acc, desc_mn(w_off(l, NL), wpanel, k), desc_k(dzbuf + row, 8192u, k), kIdescDx4, k > 0);
 #pragma unroll
                                 for (int k = 0; k < CH / 16; ++k)
                                     umma_f16(tmem_base + kColDW4T, desc_k(abuf + half, 0u, k), desc_mn(dzbuf + row, 8192u, k),
                                              kIdescDw64, prior | (uint32_t)(k > 0));
                             } else {
 #pragma unroll
-                                for (int k = 0; k < out_dim(l) / 16; ++k)
-                                    umma_f16(acc, desc_mn(w_off(l), wpanel, k), desc_mn(dzbuf + half, 8192u, k), kIdescDx, k > 0);
+                                for (int k = 0; k < out_dim(l, NL) / 16; ++k)
+                                    umma_f16(acc, desc_mn(w_off(l, NL), wpanel, k), desc_mn(dzbuf + half, 8192u, k), kIdescDx, k > 0);
 #pragma unroll
                                 for (int k = 0; k < CH / 16; ++k)
                                     umma_f16(tmem_base + kColDW1 + (uint32_t)(l - 1) * 128u, desc_k(dzbuf + half, 0u, k),
@@ -434,8 +468,10 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                             // Both chains are past every product that read the other X buffer and dZ_4.
                             mbar_expect_tx(&x_full[b ^ 1u], 8192);
                             tma_load_2d(smem + kX + (b ^ 1u) * 8192u, &tmap_x, 0, (int32_t)(next_tile * NS), &x_full[b ^ 1u]);
-                            mbar_expect_tx(t_full, 8192);
-                            tma_load_2d(smem + kDZ4, &tmap_t, 0, (int32_t)(next_tile * NS), t_full);
+                            if (!p.t_direct) {
+                                mbar_expect_tx(t_full, 8192);
+                                tma_load_2d(smem + kDZ4, &tmap_t, 0, (int32_t)(next_tile * NS), t_full);
+                            }
                         }
                     }
                     if (has_next) ++loads_issued;
@@ -445,7 +481,7 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
             if (*abort_flag && leader) {
                 // Give the copies still in flight a bounded time to land before the CTA exits.
                 mbar_drain(&x_full[(loads_issued - 1) & 1u], ((loads_issued - 1) >> 1) & 1u);
-                mbar_drain(t_full, (loads_issued - 1) & 1u);
+                if (!p.t_direct) mbar_drain(t_full, (loads_issued - 1) & 1u);
             }
         }
 #ifdef MLPB200_TRACE
@@ -543,7 +579,12 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                             const float2 zf = __fadd2_rn(make_float2(__uint_as_float(v[s]), __uint_as_float(v[s + 1])), bias2);
                             const uint32_t zr = E::pack2(zf.x, zf.y);
                             float2 a, d;
-                            act_pair2<ACT>(make_float2(E::unpack_lo(zr), E::unpack_hi(zr)), p.act_alpha, a, d);
+                            if constexpr (ACT >= 0) {
+                                act_pair2<ACT>(make_float2(E::unpack_lo(zr), E::unpack_hi(zr)), p.act_alpha, a, d);
+                            } else {
+                                act_pair_rt(p.hidden_act, E::unpack_lo(zr), p.act_alpha, a.x, d.x);
+                                act_pair_rt(p.hidden_act, E::unpack_hi(zr), p.act_alpha, a.y, d.y);
+                            }
                             aw[s >> 1] = E::pack2(a.x, a.y);
                             dreg[h][l][s >> 1] = E::pack2(d.x, d.y);
                         }
@@ -564,7 +605,7 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
             //      and eight features: one 16-byte chunk of the target row, replaced in place by dZ_4 ----
             {
                 ok = ok && mbar_wait(out_full, it & 1u, abort_flag, p.status, kStatusEpiAcc);
-                ok = ok && mbar_wait(t_full, it & 1u, abort_flag, p.status, kStatusEpiTarget);
+                if (!p.t_direct) ok = ok && mbar_wait(t_full, it & 1u, abort_flag, p.status, kStatusEpiTarget);
                 if (!ok) break;
                 MLPB200_TRACE_AT(tr_on, 64u + tr_step * 4 + 0);
                 tc_fence_after();
@@ -575,12 +616,23 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                 tmem_ld_wait();
                 MLPB200_TRACE_AT(tr_on, 64u + tr_step * 4 + 1);
                 uint4* slot = (uint4*)(smem + kDZ4 + (uint32_t)s * 128u + ((((uint32_t)(fb >> 3)) ^ (uint32_t)(s & 7)) << 4));
-                const uint4 tq = *slot;
-                const uint32_t tw[4] = {tq.x, tq.y, tq.z, tq.w};
-                const float4 b0 = *(const float4*)(s_bias + (NL - 1) * 128 + fb);
-                const float4 b1 = *(const float4*)(s_bias + (NL - 1) * 128 + fb + 4);
-                const float bo[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
                 const bool valid = tile * NS + (uint32_t)s < p.count;
+                float tf[8];
+                if (!p.t_direct) {
+                    const uint4 tq = *slot;
+                    const uint32_t tw[4] = {tq.x, tq.y, tq.z, tq.w};
+#pragma unroll
+                    for (int j = 0; j < 8; j += 2) { tf[j] = E::unpack_lo(tw[j >> 1]); tf[j + 1] = E::unpack_hi(tw[j >> 1]); }
+                } else {
+                    // targets of any width or number format: this sample's eight features straight from global memory
+                    const int od = p.dims[NL];
+                    const size_t row = ((size_t)tile * NS + (size_t)s) * (size_t)od;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) tf[j] = (valid && fb + j < od) ? load_as_f32(p.target_dtype, p.targets, (int64_t)(row + fb + j)) : 0.0f;
+                }
+                const float4 b0 = *(const float4*)(s_bias + (kMaxLayers - 1) * 128 + fb);
+                const float4 b1 = *(const float4*)(s_bias + (kMaxLayers - 1) * 128 + fb + 4);
+                const float bo[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
                 const float two_scale = 2.0f * p.loss_scale;
                 float dzf[8];
                 uint32_t zw[4];
@@ -588,8 +640,8 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
 #pragma unroll
                 for (int j = 0; j < 8; j += 2) {
                     const uint32_t op = E::pack2(__uint_as_float(v[j]) + bo[j], __uint_as_float(v[j + 1]) + bo[j + 1]);  // storage rounding
-                    const float d0 = E::unpack_lo(op) - E::unpack_lo(tw[j >> 1]);
-                    const float d1 = E::unpack_hi(op) - E::unpack_hi(tw[j >> 1]);
+                    const float d0 = E::unpack_lo(op) - tf[j];
+                    const float d1 = E::unpack_hi(op) - tf[j + 1];
                     const uint32_t zp = valid ? E::pack2(two_scale * d0, two_scale * d1) : 0u;
                     zw[j >> 1] = zp;
                     dzf[j] = E::unpack_lo(zp);
@@ -703,34 +755,50 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
         // ---- one add per parameter per CTA ----
         if (ok && !*abort_flag && n_my_tiles > 0) {
             tc_fence_after();
-            for (int l = 1; l <= 3; ++l) {
-                float* dW = (float*)p.net[l].weightsGrad + (size_t)f * 128;
+            // Only real rows and columns leave; the gradients are row-major [out][in] with the network's own widths.
+#pragma unroll
+            for (int l = 1; l <= NL - 2; ++l) {
+                const int in = p.dims[l], out = p.dims[l + 1];
+                float* dW = (float*)p.net[l].weightsGrad + (size_t)f * in;
                 const int col = e * 32;
                 uint32_t v[32];
                 tmem_ld_cols(lane_base + kColDW1 + (uint32_t)(l - 1) * 128u + (uint32_t)col, v);
                 tmem_ld_wait();
+                if (f < out) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) atomicAdd(dW + col + i, __uint_as_float(v[i]));
+                    for (int i = 0; i < 32; ++i)
+                        if (col + i < in) atomicAdd(dW + col + i, __uint_as_float(v[i]));
+                }
             }
             {
-                // dW_4^T: lane = input feature, column = output feature.
-                float* dW = (float*)p.net[4].weightsGrad;
+                // dW of the output layer, transposed: lane = input feature, column = output feature.
+                const int in = p.dims[NL - 1], out = p.dims[NL];
+                float* dW = (float*)p.net[NL - 1].weightsGrad;
                 uint32_t v[16];
                 tmem_ld_cols(lane_base + kColDW4T + (uint32_t)(e * 16), v);
                 tmem_ld_wait();
+                if (f < in) {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) atomicAdd(dW + (size_t)(e * 16 + i) * 128 + f, __uint_as_float(v[i]));
+                    for (int i = 0; i < 16; ++i)
+                        if (e * 16 + i < out) atomicAdd(dW + (size_t)(e * 16 + i) * in + f, __uint_as_float(v[i]));
+                }
             }
             {
-                float* dW = (float*)p.net[0].weightsGrad + (size_t)f * 64 + e * 16;
+                const int in = p.dims[0], out = p.dims[1];
+                float* dW = (float*)p.net[0].weightsGrad + (size_t)f * in + e * 16;
+                if (f < out) {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) atomicAdd(dW + i, dw0[i]);
+                    for (int i = 0; i < 16; ++i)
+                        if (e * 16 + i < in) atomicAdd(dW + i, dw0[i]);
+                }
             }
 #pragma unroll
-            for (int l = 0; l < NL - 1; ++l) atomicAdd((float*)p.net[l].biasesGrad + f, db[l]);
+            for (int l = 0; l < NL - 1; ++l)
+                if (f < p.dims[l + 1]) atomicAdd((float*)p.net[l].biasesGrad + f, db[l]);
             if ((lane & 3) == 0) {
                 const int j = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
-                atomicAdd((float*)p.net[NL - 1].biasesGrad + (q >> 1) * 32 + e * 8 + j, db_out);
+                const int feat = (q >> 1) * 32 + e * 8 + j;
+                if (feat < p.dims[NL]) atomicAdd((float*)p.net[NL - 1].biasesGrad + feat, db_out);
             }
             if (e == 0 && q < 2) {
                 float mx = run_max, tot = run_sum;
@@ -764,15 +832,21 @@ bool tc_train_supported(const MlpConfig& c) { return wide_supported(c) || tc_tra
 
 static bool wide_supported(const MlpConfig& c)
 {
-    static const int dims[6] = {64, 128, 128, 128, 128, 64};
-    if (c.n_layers != 5) return false;
-    for (int i = 0; i < 6; ++i)
-        if (c.dims[i] != dims[i]) return false;
+    // Two to five layers; inputs and outputs up to 64 wide, hidden layers up to 128; at least one width
+    // above 64 (narrower networks run the padded 64-wide kernel); 16-bit storage with inputs in the same
+    // format and rows that start on 16-byte boundaries (the input tile arrives by TMA); identity output.
+    const int nl = c.n_layers;
+    if (nl < 2 || nl > wide::kMaxLayers) return false;
     if (c.dtype != MLP_BF16 && c.dtype != MLP_F16) return false;
-    if (c.input_dtype != c.dtype || c.target_dtype != c.dtype) return false;
-    if (c.hidden_act != MLP_ACT_GELU_TANH && c.hidden_act != MLP_ACT_RELU && c.hidden_act != MLP_ACT_LEAKY_RELU) return false;
+    if (c.input_dtype != c.dtype) return false;
     if (c.output_act != MLP_ACT_IDENTITY || c.encoding != MLP_ENC_NONE) return false;
-    return true;
+    if (c.dims[0] > wide::D0 || (c.dims[0] & 7) != 0 || c.dims[nl] > wide::DOUT) return false;
+    bool any_wide = false;
+    for (int l = 1; l < nl; ++l) {
+        if (c.dims[l] > wide::H) return false;
+        any_wide = any_wide || c.dims[l] > 64;
+    }
+    return any_wide;
 }
 
 TcWorkspace* tc_workspace_create(int ordinal, std::string* err)
@@ -845,11 +919,11 @@ bool make_tile_map(TcWorkspace* ws, CUtensorMap* map, CUtensorMapDataType type, 
     return true;
 }
 
-template <int FMT, int ACT>
+template <int FMT, int ACT, int NL>
 static cudaError_t launch_wide(cudaStream_t st, TcWorkspace* ws, const CUtensorMap& mx, const CUtensorMap& mt,
                                const WideTrainParams& p)
 {
-    auto kern = learn_gradient_wide_kernel<FMT, ACT>;
+    auto kern = learn_gradient_wide_kernel<FMT, ACT, NL>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)wide::kSmemBytes);
     if (e != cudaSuccess) return e;
     const uint32_t grid = p.n_tiles < (uint32_t)ws->sm_count ? p.n_tiles : (uint32_t)ws->sm_count;
@@ -857,34 +931,63 @@ static cudaError_t launch_wide(cudaStream_t st, TcWorkspace* ws, const CUtensorM
     return cudaGetLastError();
 }
 
+// The builds of the kernel: the five-layer family with each of its three compile-time activations, shorter
+// networks with ReLU, and every layer count with the activation chosen at run time.
+template <int FMT>
+static cudaError_t launch_wide_fmt(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const CUtensorMap& mx,
+                                   const CUtensorMap& mt, const WideTrainParams& p)
+{
+    const int act = c.hidden_act;
+    switch (c.n_layers) {
+    case 5:
+        if (act == MLP_ACT_GELU_TANH) return launch_wide<FMT, MLP_ACT_GELU_TANH, 5>(st, ws, mx, mt, p);
+        if (act == MLP_ACT_RELU) return launch_wide<FMT, MLP_ACT_RELU, 5>(st, ws, mx, mt, p);
+        if (act == MLP_ACT_LEAKY_RELU) return launch_wide<FMT, MLP_ACT_LEAKY_RELU, 5>(st, ws, mx, mt, p);
+        return launch_wide<FMT, -1, 5>(st, ws, mx, mt, p);
+    case 4:
+        if (act == MLP_ACT_RELU) return launch_wide<FMT, MLP_ACT_RELU, 4>(st, ws, mx, mt, p);
+        return launch_wide<FMT, -1, 4>(st, ws, mx, mt, p);
+    case 3:
+        if (act == MLP_ACT_RELU) return launch_wide<FMT, MLP_ACT_RELU, 3>(st, ws, mx, mt, p);
+        return launch_wide<FMT, -1, 3>(st, ws, mx, mt, p);
+    case 2:
+        if (act == MLP_ACT_RELU) return launch_wide<FMT, MLP_ACT_RELU, 2>(st, ws, mx, mt, p);
+        return launch_wide<FMT, -1, 2>(st, ws, mx, mt, p);
+    }
+    return cudaErrorInvalidValue;
+}
+
 cudaError_t launch_learn_gradient_tc(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const MlpLearnGradParamsEx& a,
                                      int* launches, std::string* err)
 {
     if (!wide_supported(c)) return launch_learn_gradient_narrow(st, ws, c, a, launches, err);
     if (a.count == 0) return cudaSuccess;
+    const int nl = c.n_layers;
+    const int d0 = c.dims[0], dout = c.dims[nl];
     CUtensorMap mx, mt;
     const CUtensorMapDataType dt = c.dtype == MLP_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    if (!make_tile_map(ws, &mx, dt, 2, a.inputs, a.count, 64, 64, wide::NS, CU_TENSOR_MAP_SWIZZLE_128B, err)) return cudaErrorInvalidValue;
-    if (!make_tile_map(ws, &mt, dt, 2, a.targets, a.count, 64, 64, wide::NS, CU_TENSOR_MAP_SWIZZLE_128B, err)) return cudaErrorInvalidValue;
+    // Boxes of 64 rows x 64 columns over [count][width]: columns past the real width arrive as zeros.
+    if (!make_tile_map(ws, &mx, dt, 2, a.inputs, a.count, (uint32_t)d0, 64, wide::NS, CU_TENSOR_MAP_SWIZZLE_128B, err)) return cudaErrorInvalidValue;
+    // Targets come by TMA when their rows are 16-byte multiples in the storage format, else the epilogue reads them.
+    const bool t_direct = c.target_dtype != c.dtype || (dout & 7) != 0 || (a.targets & 15u) != 0;
+    if (t_direct) mt = mx;
+    else if (!make_tile_map(ws, &mt, dt, 2, a.targets, a.count, (uint32_t)dout, 64, wide::NS, CU_TENSOR_MAP_SWIZZLE_128B, err)) return cudaErrorInvalidValue;
     WideTrainParams p;
+    for (int l = 0; l <= wide::kMaxLayers; ++l) p.dims[l] = l <= nl ? c.dims[l] : 0;
+    p.hidden_act = c.hidden_act;
+    p.t_direct = t_direct ? 1 : 0;
+    p.target_dtype = c.target_dtype;
+    p.targets = (const void*)a.targets;
     p.net = (const MlpLayerPointers*)a.networkBuffer;
     p.loss_words = (uint32_t*)a.lossBuffer;
     p.status = ws->status;
     p.count = a.count;
     p.n_tiles = (a.count + wide::NS - 1) / wide::NS;
-    p.loss_scale = c.loss == MLP_LOSS_MSE_MEAN ? 1.0f / 64.0f : 1.0f;
+    p.loss_scale = c.loss == MLP_LOSS_MSE_MEAN ? 1.0f / (float)dout : 1.0f;
     p.act_alpha = c.act_alpha;
     p.timing = ws->timing;
-    cudaError_t e = cudaErrorInvalidValue;
-#define MLPB200_DISPATCH(FMT_, ACT_) \
-    if (c.dtype == FMT_ && c.hidden_act == ACT_) e = launch_wide<FMT_, ACT_>(st, ws, mx, mt, p);
-    MLPB200_DISPATCH(MLP_BF16, MLP_ACT_GELU_TANH)
-    MLPB200_DISPATCH(MLP_BF16, MLP_ACT_RELU)
-    MLPB200_DISPATCH(MLP_BF16, MLP_ACT_LEAKY_RELU)
-    MLPB200_DISPATCH(MLP_F16, MLP_ACT_GELU_TANH)
-    MLPB200_DISPATCH(MLP_F16, MLP_ACT_RELU)
-    MLPB200_DISPATCH(MLP_F16, MLP_ACT_LEAKY_RELU)
-#undef MLPB200_DISPATCH
+    const cudaError_t e = c.dtype == MLP_BF16 ? launch_wide_fmt<MLP_BF16>(st, ws, c, mx, mt, p)
+                                              : launch_wide_fmt<MLP_F16>(st, ws, c, mx, mt, p);
     *launches += 1;
     return e;
 }

@@ -212,3 +212,43 @@ def test_c4_large_batch_properties(device):
     tt.learn_gradient(x, own)
     assert tt.grads.abs().max().item() <= 2e-3 * scale
     assert tt.loss()[0] < 1e-4
+
+
+@pytest.mark.parametrize("dims,dtype,act,tdtype", [
+    ([32, 128, 128, 3], C.F16, C.ACT_RELU, C.F32),            # odd output width: targets read by the epilogue
+    ([64, 96, 96, 64], C.BF16, C.ACT_GELU_TANH, C.BF16),       # hidden widths padded to 128, targets by TMA
+    ([16, 128, 8], C.F16, C.ACT_LEAKY_RELU, C.F16),            # two layers
+    ([8, 100, 120, 60, 24], C.BF16, C.ACT_TANH, C.BF16),       # widths that are not multiples of 8 or 16, run-time activation
+    ([64, 128, 128, 128, 128, 64], C.F16, C.ACT_SIGMOID, C.F16),  # the benchmark shape with a run-time activation
+    ([40, 72, 64, 128, 33], C.F16, C.ACT_RELU, C.F16),
+])
+def test_wide_kernel_other_shapes(device, dims, dtype, act, tdtype):
+    """Networks with a width above 64 run the wide tensor-core kernel zero-padded to 64 -> 128 -> ... -> 64:
+    two to five layers, inputs a multiple of 8 up to 64, hidden widths up to 128, up to 64 outputs; gradients
+    per tensor within 1e-2 of the oracle, loss words within 1e-2.  More tiles than SMs and a ragged tail."""
+    rng = np.random.default_rng(sum(dims))
+    cfg = C.make_config(dims, dtype=dtype, hidden_act=act, output_act=C.ACT_IDENTITY, act_alpha=0.02,
+                        input_dtype=dtype, target_dtype=tdtype, adam_master=1)
+    p0 = C.from_storage(C.init_params(cfg, seed=5, scheme="xavier"), dtype).copy()
+    w_off, b_off, _ = C.param_layout(cfg)
+    for l in range(cfg.n_layers):
+        p0[b_off[l]:b_off[l] + dims[l + 1]] = rng.uniform(-0.2, 0.2, dims[l + 1])
+    p0 = C.to_storage(p0, dtype)
+    count = 64 * 148 + 64 * 3 + 11
+    x = C.to_storage(rng.uniform(-1, 1, (count, dims[0])).astype(np.float32), dtype)
+    t = C.to_storage(rng.uniform(-1, 1, (count, dims[-1])).astype(np.float32), tdtype)
+    _, l_ref, g_ref, _ = oracle_trajectory(cfg, p0, [(x, t)], n_threads=8)
+    _, l_gpu, g_gpu, _, tr = gpu_trajectory(device, cfg, p0, [(x, t)])
+    assert tr.k_learn.implementation == "tcgen05"
+    err = _grad_layer_errs(cfg, g_gpu, g_ref)
+    print(dims, "worst per-tensor gradient rel err %.3g; loss gpu %s ref %s" % (err, l_gpu[0], l_ref[0]))
+    assert err < 1e-2
+    assert abs(l_gpu[0][1] - l_ref[0][1]) <= 1e-2 * abs(l_ref[0][1])
+    assert abs(l_gpu[0][0] - l_ref[0][0]) <= 1e-2 * abs(l_ref[0][0])
+    # the padding beyond each sub-allocation's real elements stays untouched
+    _, _, total = C.param_layout(cfg)
+    mask = np.ones(total, dtype=bool)
+    for l in range(cfg.n_layers):
+        mask[w_off[l]:w_off[l] + dims[l] * dims[l + 1]] = False
+        mask[b_off[l]:b_off[l] + dims[l + 1]] = False
+    assert not g_gpu[mask].any()
