@@ -36,7 +36,7 @@ int32_t fail(int32_t code, const char* fmt, ...)
         if (e_ != cudaSuccess) return fail(MLP_E_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e_)); \
     } while (0)
 
-enum class Entry { ExampleLearn, ExampleLearnCoopVec, ExampleAdjust, Learn, LearnSimt, Adjust, Forward, ForwardNarrow, ForwardSimt, Module };
+enum class Entry { ExampleLearn, ExampleLearnCoopVec, ExampleAdjust, Learn, LearnSimt, Adjust, Forward, ForwardNarrow, ForwardWide, ForwardSimt, Module };
 
 // Driver entry points for caller-supplied device modules, resolved through the runtime so that the
 // library carries no link-time dependency on the driver library.
@@ -290,6 +290,7 @@ int32_t mlp_kernel_get_for_config(MlpDevice* d, const MlpConfig* config, const c
     else if (!std::strcmp(entry_point, "forward")) {
         if (tc_forward_supported(*config)) { k->entry = Entry::Forward; k->impl = "tcgen05"; }
         else if (tc_train_narrow_supported(*config)) { k->entry = Entry::ForwardNarrow; k->impl = "tcgen05"; }
+        else if (tc_forward_wide_supported(*config)) { k->entry = Entry::ForwardWide; k->impl = "tcgen05"; }
         else k->entry = Entry::ForwardSimt;
     } else if (!std::strcmp(entry_point, "forward_simt")) k->entry = Entry::ForwardSimt;
     else { delete k; return fail(MLP_E_NOT_AVAILABLE, "no entry point named '%s'", entry_point); }
@@ -442,6 +443,7 @@ int32_t mlp_dispatch(MlpDevice* d, MlpKernel* k, const void* args, size_t args_s
     }
     case Entry::Forward:
     case Entry::ForwardNarrow:
+    case Entry::ForwardWide:
     case Entry::ForwardSimt: {
         if (args_size != sizeof(MlpForwardParams)) return fail(MLP_E_INVALID_ARG, "forward expects %zu argument bytes, got %zu", sizeof(MlpForwardParams), args_size);
         MlpForwardParams a; std::memcpy(&a, args, sizeof a);
@@ -451,6 +453,7 @@ int32_t mlp_dispatch(MlpDevice* d, MlpKernel* k, const void* args, size_t args_s
             return fail(MLP_E_NOT_AVAILABLE, "MLP_FLAG_OUTPUT_STORAGE_TYPE needs the constant-width tensor-core forward kernel");
         if (k->entry == Entry::Forward) e = launch_forward_tc(d->stream, d->tc, k->cfg, a, &launches, &err);
         else if (k->entry == Entry::ForwardNarrow) e = launch_forward_narrow(d->stream, d->tc, k->cfg, a, &launches, &err);
+        else if (k->entry == Entry::ForwardWide) e = launch_forward_wide(d->stream, d->tc, k->cfg, a, &launches, &err);
         else e = launch_forward_simt(d->stream, k->cfg, a, &launches, &err);
         break;
     }

@@ -43,6 +43,10 @@ cudaError_t launch_forward_tc(cudaStream_t st, TcWorkspace* ws, const MlpConfig&
                               int* launches, std::string* err);
 cudaError_t launch_learn_gradient_tc(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c,
                                      const MlpLearnGradParamsEx& a, int* launches, std::string* err);
+// Forward pass of the wide (zero-padded 64-128-...-64) kernel's shapes; fp32 outputs.
+bool tc_forward_wide_supported(const MlpConfig& c);
+cudaError_t launch_forward_wide(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const MlpForwardParams& a,
+                                int* launches, std::string* err);
 // input_grads (optional): [count][dims[0]] fp32 gradient with respect to the inputs (no input encoding).
 cudaError_t launch_learn_gradient_narrow(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c,
                                          const MlpLearnGradParamsEx& a, int* launches, std::string* err,

@@ -188,6 +188,7 @@ struct WideTrainParams {
     int t_direct;                    // 1: the epilogue reads targets from global memory itself (no tensor map)
     int target_dtype;
     const void* targets;             // for t_direct
+    float* outputs;                  // forward-only builds: fp32 [count][outputs]
     const MlpLayerPointers* net;
     uint32_t* loss_words;
     uint32_t* status;
@@ -198,7 +199,9 @@ struct WideTrainParams {
     unsigned long long* timing;  // trace builds only: time stamps written by CTA 0
 };
 
-template <int FMT, int ACT, int NL>
+// FWD builds stop after the output layer and write the network outputs (the "forward" entry point of the same
+// shapes): no targets, no derivatives, no gradient products.
+template <int FMT, int ACT, int NL, bool FWD>
 __global__ void __launch_bounds__(wide::kThreads, 1)
 learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_t,
                            const WideTrainParams p)
@@ -357,7 +360,15 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                 // ---- forward, layer 0 ----
 #pragma unroll
                 for (int h = 0; h < NCH; ++h) {
-                    if (it > 0) chain_wait(h);  // the previous tile's dW_0 has left the accumulator
+                    if constexpr (FWD) {
+                        // the previous tile's outputs have left the accumulator
+                        if (h == 0 && it > 0) {
+                            ok = ok && mbar_wait(out_free, (it - 1) & 1u, abort_flag, p.status, kStatusCtrlAcc);
+                            tc_fence_after();
+                        }
+                    } else {
+                        if (it > 0) chain_wait(h);  // the previous tile's dW_0 has left the accumulator
+                    }
                     if (h == 0) ok = ok && mbar_wait(&x_full[b], (it >> 1) & 1u, abort_flag, p.status, kStatusCtrlX);
                     if (ok && leader) {
                         const uint32_t acc = tmem_base + kColAcc + (uint32_t)(h * CH);
@@ -409,6 +420,15 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
 #ifdef MLPB200_TRACE
                 ++tr_step;
 #endif
+                if constexpr (FWD) {
+                    // forward only: the next tile's inputs (the other buffer's last reader was the previous tile's layer 0)
+                    if (ok && leader && has_next) {
+                        mbar_expect_tx(&x_full[b ^ 1u], 8192);
+                        tma_load_2d(smem + kX + (b ^ 1u) * 8192u, &tmap_x, 0, (int32_t)(next_tile * NS), &x_full[b ^ 1u]);
+                    }
+                    if (has_next) ++loads_issued;
+                    continue;
+                }
                 // ---- backward ----
                 MLPB200_TRACE_AT(tr_on, (tr_step * 2 + 0) * 3 + 0);
                 ok = ok && mbar_wait(out_free, it & 1u, abort_flag, p.status, kStatusCtrlAcc);  // dZ_4 is in place
@@ -586,7 +606,7 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                                 act_pair_rt(p.hidden_act, E::unpack_hi(zr), p.act_alpha, a.y, d.y);
                             }
                             aw[s >> 1] = E::pack2(a.x, a.y);
-                            dreg[h][l][s >> 1] = E::pack2(d.x, d.y);
+                            if constexpr (!FWD) dreg[h][l][s >> 1] = E::pack2(d.x, d.y);
                         }
                         *(uint4*)(smem + kA1 + (uint32_t)l * 16384u + chunk_of(h)) = make_uint4(aw[0], aw[1], aw[2], aw[3]);
                         MLPB200_TRACE_AT(tr_on, 64u + (uint32_t)h * 64u + tr_step * 4 + 2);
@@ -605,7 +625,7 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
             //      and eight features: one 16-byte chunk of the target row, replaced in place by dZ_4 ----
             {
                 ok = ok && mbar_wait(out_full, it & 1u, abort_flag, p.status, kStatusEpiAcc);
-                if (!p.t_direct) ok = ok && mbar_wait(t_full, it & 1u, abort_flag, p.status, kStatusEpiTarget);
+                if (!FWD && !p.t_direct) ok = ok && mbar_wait(t_full, it & 1u, abort_flag, p.status, kStatusEpiTarget);
                 if (!ok) break;
                 MLPB200_TRACE_AT(tr_on, 64u + tr_step * 4 + 0);
                 tc_fence_after();
@@ -615,8 +635,28 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                 tmem_ld_cols(lane_base + kColAcc + (uint32_t)fb, v);
                 tmem_ld_wait();
                 MLPB200_TRACE_AT(tr_on, 64u + tr_step * 4 + 1);
-                uint4* slot = (uint4*)(smem + kDZ4 + (uint32_t)s * 128u + ((((uint32_t)(fb >> 3)) ^ (uint32_t)(s & 7)) << 4));
                 const bool valid = tile * NS + (uint32_t)s < p.count;
+                if constexpr (FWD) {
+                    // the pre-activations of the output layer, rounded to the storage type, as fp32
+                    const float4 c0 = *(const float4*)(s_bias + (kMaxLayers - 1) * 128 + fb);
+                    const float4 c1 = *(const float4*)(s_bias + (kMaxLayers - 1) * 128 + fb + 4);
+                    const float bb[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+                    const int od = p.dims[NL];
+                    if (valid) {
+                        float* dst = p.outputs + ((size_t)tile * NS + (size_t)s) * (size_t)od + fb;
+#pragma unroll
+                        for (int j = 0; j < 8; j += 2) {
+                            const uint32_t op = E::pack2(__uint_as_float(v[j]) + bb[j], __uint_as_float(v[j + 1]) + bb[j + 1]);
+                            if (fb + j < od) dst[j] = E::unpack_lo(op);
+                            if (fb + j + 1 < od) dst[j + 1] = E::unpack_hi(op);
+                        }
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(out_free);
+                    continue;
+                }
+                uint4* slot = (uint4*)(smem + kDZ4 + (uint32_t)s * 128u + ((((uint32_t)(fb >> 3)) ^ (uint32_t)(s & 7)) << 4));
                 float tf[8];
                 if (!p.t_direct) {
                     const uint4 tq = *slot;
@@ -753,7 +793,7 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
         }
 
         // ---- one add per parameter per CTA ----
-        if (ok && !*abort_flag && n_my_tiles > 0) {
+        if (!FWD && ok && !*abort_flag && n_my_tiles > 0) {
             tc_fence_after();
             // Only real rows and columns leave; the gradients are row-major [out][in] with the network's own widths.
 #pragma unroll
@@ -824,12 +864,12 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
 }
 
 // ------------------------------------------------------------------------------------------------
-// Host side
+// Host side.  This file is compiled twice (slang_b200/build.py): MLPB200_WIDE_PART 0 holds the workspace,
+// the tensor-map helper and the training builds of the kernel, part 1 the forward-only builds.
 // ------------------------------------------------------------------------------------------------
-static bool wide_supported(const MlpConfig& c);
-
-bool tc_train_supported(const MlpConfig& c) { return wide_supported(c) || tc_train_narrow_supported(c); }
-
+#ifndef MLPB200_WIDE_PART
+#error "compile with -DMLPB200_WIDE_PART=0 or 1"
+#endif
 static bool wide_supported(const MlpConfig& c)
 {
     // Two to five layers; inputs and outputs up to 64 wide, hidden layers up to 128; at least one width
@@ -848,6 +888,11 @@ static bool wide_supported(const MlpConfig& c)
     }
     return any_wide;
 }
+
+
+#if MLPB200_WIDE_PART == 0
+
+bool tc_train_supported(const MlpConfig& c) { return wide_supported(c) || tc_train_narrow_supported(c); }
 
 TcWorkspace* tc_workspace_create(int ordinal, std::string* err)
 {
@@ -919,11 +964,13 @@ bool make_tile_map(TcWorkspace* ws, CUtensorMap* map, CUtensorMapDataType type, 
     return true;
 }
 
-template <int FMT, int ACT, int NL>
+#endif  // part 0
+
+template <int FMT, int ACT, int NL, bool FWD>
 static cudaError_t launch_wide(cudaStream_t st, TcWorkspace* ws, const CUtensorMap& mx, const CUtensorMap& mt,
                                const WideTrainParams& p)
 {
-    auto kern = learn_gradient_wide_kernel<FMT, ACT, NL>;
+    auto kern = learn_gradient_wide_kernel<FMT, ACT, NL, FWD>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)wide::kSmemBytes);
     if (e != cudaSuccess) return e;
     const uint32_t grid = p.n_tiles < (uint32_t)ws->sm_count ? p.n_tiles : (uint32_t)ws->sm_count;
@@ -933,30 +980,31 @@ static cudaError_t launch_wide(cudaStream_t st, TcWorkspace* ws, const CUtensorM
 
 // The builds of the kernel: the five-layer family with each of its three compile-time activations, shorter
 // networks with ReLU, and every layer count with the activation chosen at run time.
-template <int FMT>
+template <int FMT, bool FWD>
 static cudaError_t launch_wide_fmt(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const CUtensorMap& mx,
                                    const CUtensorMap& mt, const WideTrainParams& p)
 {
     const int act = c.hidden_act;
     switch (c.n_layers) {
     case 5:
-        if (act == MLP_ACT_GELU_TANH) return launch_wide<FMT, MLP_ACT_GELU_TANH, 5>(st, ws, mx, mt, p);
-        if (act == MLP_ACT_RELU) return launch_wide<FMT, MLP_ACT_RELU, 5>(st, ws, mx, mt, p);
-        if (act == MLP_ACT_LEAKY_RELU) return launch_wide<FMT, MLP_ACT_LEAKY_RELU, 5>(st, ws, mx, mt, p);
-        return launch_wide<FMT, -1, 5>(st, ws, mx, mt, p);
+        if (act == MLP_ACT_GELU_TANH) return launch_wide<FMT, MLP_ACT_GELU_TANH, 5, FWD>(st, ws, mx, mt, p);
+        if (act == MLP_ACT_RELU) return launch_wide<FMT, MLP_ACT_RELU, 5, FWD>(st, ws, mx, mt, p);
+        if (act == MLP_ACT_LEAKY_RELU) return launch_wide<FMT, MLP_ACT_LEAKY_RELU, 5, FWD>(st, ws, mx, mt, p);
+        return launch_wide<FMT, -1, 5, FWD>(st, ws, mx, mt, p);
     case 4:
-        if (act == MLP_ACT_RELU) return launch_wide<FMT, MLP_ACT_RELU, 4>(st, ws, mx, mt, p);
-        return launch_wide<FMT, -1, 4>(st, ws, mx, mt, p);
+        if (act == MLP_ACT_RELU) return launch_wide<FMT, MLP_ACT_RELU, 4, FWD>(st, ws, mx, mt, p);
+        return launch_wide<FMT, -1, 4, FWD>(st, ws, mx, mt, p);
     case 3:
-        if (act == MLP_ACT_RELU) return launch_wide<FMT, MLP_ACT_RELU, 3>(st, ws, mx, mt, p);
-        return launch_wide<FMT, -1, 3>(st, ws, mx, mt, p);
+        if (act == MLP_ACT_RELU) return launch_wide<FMT, MLP_ACT_RELU, 3, FWD>(st, ws, mx, mt, p);
+        return launch_wide<FMT, -1, 3, FWD>(st, ws, mx, mt, p);
     case 2:
-        if (act == MLP_ACT_RELU) return launch_wide<FMT, MLP_ACT_RELU, 2>(st, ws, mx, mt, p);
-        return launch_wide<FMT, -1, 2>(st, ws, mx, mt, p);
+        if (act == MLP_ACT_RELU) return launch_wide<FMT, MLP_ACT_RELU, 2, FWD>(st, ws, mx, mt, p);
+        return launch_wide<FMT, -1, 2, FWD>(st, ws, mx, mt, p);
     }
     return cudaErrorInvalidValue;
 }
 
+#if MLPB200_WIDE_PART == 0
 cudaError_t launch_learn_gradient_tc(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const MlpLearnGradParamsEx& a,
                                      int* launches, std::string* err)
 {
@@ -986,10 +1034,45 @@ cudaError_t launch_learn_gradient_tc(cudaStream_t st, TcWorkspace* ws, const Mlp
     p.loss_scale = c.loss == MLP_LOSS_MSE_MEAN ? 1.0f / (float)dout : 1.0f;
     p.act_alpha = c.act_alpha;
     p.timing = ws->timing;
-    const cudaError_t e = c.dtype == MLP_BF16 ? launch_wide_fmt<MLP_BF16>(st, ws, c, mx, mt, p)
-                                              : launch_wide_fmt<MLP_F16>(st, ws, c, mx, mt, p);
+    p.outputs = nullptr;
+    const cudaError_t e = c.dtype == MLP_BF16 ? launch_wide_fmt<MLP_BF16, false>(st, ws, c, mx, mt, p)
+                                              : launch_wide_fmt<MLP_F16, false>(st, ws, c, mx, mt, p);
     *launches += 1;
     return e;
 }
+#else  // part 1: the forward entry point of the same shapes
+
+bool tc_forward_wide_supported(const MlpConfig& c) { return wide_supported(c); }
+
+cudaError_t launch_forward_wide(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const MlpForwardParams& a,
+                                int* launches, std::string* err)
+{
+    if (!wide_supported(c)) { if (err) *err = "shape not built for the wide tensor-core path"; return cudaErrorInvalidValue; }
+    if (a.count == 0) return cudaSuccess;
+    const int nl = c.n_layers;
+    CUtensorMap mx;
+    const CUtensorMapDataType dt = c.dtype == MLP_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    if (!make_tile_map(ws, &mx, dt, 2, a.inputs, a.count, (uint32_t)c.dims[0], 64, wide::NS, CU_TENSOR_MAP_SWIZZLE_128B, err)) return cudaErrorInvalidValue;
+    WideTrainParams p;
+    for (int l = 0; l <= wide::kMaxLayers; ++l) p.dims[l] = l <= nl ? c.dims[l] : 0;
+    p.hidden_act = c.hidden_act;
+    p.t_direct = 1;
+    p.target_dtype = c.target_dtype;
+    p.targets = nullptr;
+    p.outputs = (float*)a.outputs;
+    p.net = (const MlpLayerPointers*)a.networkBuffer;
+    p.loss_words = nullptr;
+    p.status = ws->status;
+    p.count = a.count;
+    p.n_tiles = (a.count + wide::NS - 1) / wide::NS;
+    p.loss_scale = 1.0f;
+    p.act_alpha = c.act_alpha;
+    p.timing = nullptr;
+    const cudaError_t e = c.dtype == MLP_BF16 ? launch_wide_fmt<MLP_BF16, true>(st, ws, c, mx, mx, p)
+                                              : launch_wide_fmt<MLP_F16, true>(st, ws, c, mx, mx, p);
+    *launches += 1;
+    return e;
+}
+#endif
 
 }  // namespace mlpb200

@@ -252,3 +252,15 @@ def test_wide_kernel_other_shapes(device, dims, dtype, act, tdtype):
         mask[w_off[l]:w_off[l] + dims[l] * dims[l + 1]] = False
         mask[b_off[l]:b_off[l] + dims[l + 1]] = False
     assert not g_gpu[mask].any()
+    # the forward entry point of the same shape runs the same kernel without its backward half
+    from oracle import oracle
+    from slang_b200.api import Trainer
+    fresh = Trainer(device, cfg, p0)
+    assert fresh.k_forward.implementation == "tcgen05"
+    xb = device.create_buffer(x.nbytes, x)
+    yb = device.create_buffer(count * dims[-1] * 4, np.full(count * dims[-1], 7.0, dtype=np.float32))
+    fresh.forward(xb.address, yb.address, count)
+    y = yb.read(np.float32).reshape(count, dims[-1])
+    y_ref = oracle.forward(cfg, p0, x, count)
+    step = 2.0 ** -7 if dtype == C.BF16 else 2.0 ** -10
+    assert np.max(np.abs(y - y_ref)) <= 4 * step * max(1.0, float(np.max(np.abs(y_ref))))
