@@ -337,6 +337,41 @@ def measure_narrow(torch, device, dev_t, name, count, warmup, steps):
     return line
 
 
+def measure_other_widths(torch, device, dev_t):
+    """Networks that are neither a benchmark configuration nor at most 64 wide: learnGradient + adjustParameters
+    on 2^20 samples through the shape's fastest kernel and, for scale, through the one-thread-per-sample kernel
+    (2^17 samples)."""
+    from slang_b200 import config as C
+    from slang_b200.api import Trainer
+    out = []
+    for dims, dtype, act in (([32, 128, 128, 3], C.F16, C.ACT_RELU), ([64, 96, 96, 64], C.BF16, C.ACT_GELU_TANH)):
+        cfg = C.make_config(dims, dtype=dtype, hidden_act=act, input_dtype=dtype, target_dtype=dtype, adam_master=1)
+        p0 = C.init_params(cfg, seed=1, scheme="xavier")
+        tdt = torch.float16 if dtype == C.F16 else torch.bfloat16
+        n = 1 << 20
+        gen = torch.Generator(device=dev_t); gen.manual_seed(3)
+        x = torch.randn((n, dims[0]), device=dev_t, generator=gen).to(tdt)
+        t = (torch.randn((n, dims[-1]), device=dev_t, generator=gen) * 0.3).to(tdt)
+        rates = {}
+        for entry, cnt in (("learnGradient", n), ("learnGradient_simt", 1 << 17)):
+            tr = Trainer(device, cfg, p0, learn_entry=entry)
+            for _ in range(2):
+                tr.learn_gradient(x.data_ptr(), t.data_ptr(), cnt); tr.adjust_parameters()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(3):
+                tr.learn_gradient(x.data_ptr(), t.data_ptr(), cnt); tr.adjust_parameters()
+            e1.record()
+            torch.cuda.synchronize()
+            rates[entry] = (3 * cnt / (e0.elapsed_time(e1) * 1e-3), tr.k_learn.implementation)
+        out.append({"dims": dims, "dtype": C.DTYPE_NAME[dtype], "samples_per_s": rates["learnGradient"][0],
+                    "implementation": rates["learnGradient"][1], "one_thread_per_sample_samples_per_s": rates["learnGradient_simt"][0],
+                    "tflops": rates["learnGradient"][0] * C.flops_per_sample(cfg) / 1e12})
+        del x, t
+    return out
+
+
 def bench_permuto(args):
     """Permutohedral encoder: 3-D positions, 16 levels of 2^19 entries, 2 features per entry (fp32 or fp16
     tables).  Reports encode and reverse-pass rates; the roofline is HBM against the bytes that must cross
@@ -734,6 +769,7 @@ def main():
             pts = measure_forward_points(torch, device, dev_t, (16, 32, 64, 128), (1 << 20, 1 << 24), 3, 5)
             sub["c5"] = {"points": [{k: p[k] for k in ("width", "batch", "samples_per_s", "hbm_frac", "tflops", "tensor_frac_of_burst")} for p in pts],
                          "workload": "forward only, depth-4 ReLU, fp16 weights, fp32 outputs; hbm_frac = 6w bytes per sample over the measured copy bandwidth"}
+            sub["other_widths"] = measure_other_widths(torch, device, dev_t)
             line["sub"] = sub
         print(json.dumps(line), flush=True)
     if comm is not None:

@@ -805,9 +805,18 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                 tmem_ld_cols(lane_base + kColDW1 + (uint32_t)(l - 1) * 128u + (uint32_t)col, v);
                 tmem_ld_wait();
                 if (f < out) {
+                    if ((in & 3) == 0) {
+                        // four parameters per reduction (16-byte aligned: rows are multiples of 16 bytes)
 #pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (col + i < in) atomicAdd(dW + col + i, __uint_as_float(v[i]));
+                        for (int i = 0; i < 32; i += 4)
+                            if (col + i < in)
+                                atomicAdd((float4*)(dW + col + i), make_float4(__uint_as_float(v[i]), __uint_as_float(v[i + 1]),
+                                                                               __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3])));
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (col + i < in) atomicAdd(dW + col + i, __uint_as_float(v[i]));
+                    }
                 }
             }
             {
@@ -827,9 +836,15 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                 const int in = p.dims[0], out = p.dims[1];
                 float* dW = (float*)p.net[0].weightsGrad + (size_t)f * in + e * 16;
                 if (f < out) {
+                    if ((in & 3) == 0) {
 #pragma unroll
-                    for (int i = 0; i < 16; ++i)
-                        if (e * 16 + i < in) atomicAdd(dW + i, dw0[i]);
+                        for (int i = 0; i < 16; i += 4)
+                            if (e * 16 + i < in) atomicAdd((float4*)(dW + i), make_float4(dw0[i], dw0[i + 1], dw0[i + 2], dw0[i + 3]));
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            if (e * 16 + i < in) atomicAdd(dW + i, dw0[i]);
+                    }
                 }
             }
 #pragma unroll
