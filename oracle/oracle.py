@@ -21,6 +21,13 @@ def build(force=False):
     return so
 
 
+def build_ref():
+    """oracle/_ref/libref_prelude.so: the reference's CPU prelude behind a C wrapper, compiled from the
+    reference tree where it lies (a no-op that keeps a prebuilt library where the tree is absent)."""
+    subprocess.check_call(["make", "-C", _HERE, "-s", "ref"])
+    return os.path.join(_HERE, "_ref", "libref_prelude.so")
+
+
 def lib():
     global _LIB
     if _LIB is None:

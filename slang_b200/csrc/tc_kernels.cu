@@ -993,8 +993,9 @@ static cudaError_t launch_wide(cudaStream_t st, TcWorkspace* ws, const CUtensorM
     return cudaGetLastError();
 }
 
-// The builds of the kernel: the five-layer family with each of its three compile-time activations, shorter
-// networks with ReLU, and every layer count with the activation chosen at run time.
+// The builds of the kernel: GELU (tanh form) and ReLU as compile-time activations for every layer count,
+// leaky ReLU for five layers, and every layer count with the activation chosen at run time (slower: every
+// element goes through a switch and the library's scalar math).
 template <int FMT, bool FWD>
 static cudaError_t launch_wide_fmt(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const CUtensorMap& mx,
                                    const CUtensorMap& mt, const WideTrainParams& p)
@@ -1007,12 +1008,15 @@ static cudaError_t launch_wide_fmt(cudaStream_t st, TcWorkspace* ws, const MlpCo
         if (act == MLP_ACT_LEAKY_RELU) return launch_wide<FMT, MLP_ACT_LEAKY_RELU, 5, FWD>(st, ws, mx, mt, p);
         return launch_wide<FMT, -1, 5, FWD>(st, ws, mx, mt, p);
     case 4:
+        if (act == MLP_ACT_GELU_TANH) return launch_wide<FMT, MLP_ACT_GELU_TANH, 4, FWD>(st, ws, mx, mt, p);
         if (act == MLP_ACT_RELU) return launch_wide<FMT, MLP_ACT_RELU, 4, FWD>(st, ws, mx, mt, p);
         return launch_wide<FMT, -1, 4, FWD>(st, ws, mx, mt, p);
     case 3:
+        if (act == MLP_ACT_GELU_TANH) return launch_wide<FMT, MLP_ACT_GELU_TANH, 3, FWD>(st, ws, mx, mt, p);
         if (act == MLP_ACT_RELU) return launch_wide<FMT, MLP_ACT_RELU, 3, FWD>(st, ws, mx, mt, p);
         return launch_wide<FMT, -1, 3, FWD>(st, ws, mx, mt, p);
     case 2:
+        if (act == MLP_ACT_GELU_TANH) return launch_wide<FMT, MLP_ACT_GELU_TANH, 2, FWD>(st, ws, mx, mt, p);
         if (act == MLP_ACT_RELU) return launch_wide<FMT, MLP_ACT_RELU, 2, FWD>(st, ws, mx, mt, p);
         return launch_wide<FMT, -1, 2, FWD>(st, ws, mx, mt, p);
     }

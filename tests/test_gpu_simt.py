@@ -57,10 +57,15 @@ def test_c1_block_sum_within_bar(device):
 @pytest.mark.parametrize("name,count,steps", [("c2", 2048, 10), ("c3", 1024, 10), ("c4", 512, 6)])
 def test_16bit_configs_simt(device, name, count, steps):
     """fp16 / bf16 configurations: per-step loss within 1e-2 relative, final parameters within 2e-2
-    relative (per layer, weights and biases together, relative to the layer's largest magnitude)."""
+    relative (per layer, weights and biases together, relative to the layer's largest magnitude).
+    The trajectory runs with ordered sums: the block-level sums leave through atomics whose order changes
+    from run to run, and with Adam a near-zero gradient whose sign flips moves a parameter by 2 lr, which at
+    lr = 1e-2 (configuration 3) made this bar pass or fail by chance.  The block sums are held to the
+    gradient bar on the first step."""
+    from slang_b200.api import FLAG_SEQUENTIAL_SUM
     cfg, p0, batches = make_problem(name, count, seed=3, steps=steps)
     p_ref, l_ref, g_ref, _ = oracle_trajectory(cfg, p0, batches)
-    p_gpu, l_gpu, g_gpu, _, _ = gpu_trajectory(device, cfg, p0, batches, "learnGradient_simt")
+    p_gpu, l_gpu, g_gpu, _, _ = gpu_trajectory(device, cfg, p0, batches, "learnGradient_simt", FLAG_SEQUENTIAL_SUM)
     assert rel_err(g_gpu, g_ref) < 1e-2
     for (mg, sg), (mr, sr) in zip(l_gpu, l_ref):
         assert abs(sg - sr) <= 1e-2 * abs(sr)
@@ -68,6 +73,9 @@ def test_16bit_configs_simt(device, name, count, steps):
     errs = per_layer_rel_errs(cfg, C.from_storage(p_gpu, cfg.dtype), C.from_storage(p_ref, cfg.dtype))
     print(name, "worst per-layer rel err", max(errs))
     assert max(errs) < 2e-2
+    _, l_blk, g_blk, _, _ = gpu_trajectory(device, cfg, p0, batches[:1], "learnGradient_simt")
+    assert rel_err(g_blk, g_ref) < 1e-2
+    assert abs(l_blk[0][1] - l_ref[0][1]) <= 1e-2 * abs(l_ref[0][1])
 
 
 def test_sum_order_known_answers_on_gpu(device):
