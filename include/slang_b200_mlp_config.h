@@ -60,6 +60,17 @@ enum MlpEncoding { MLP_ENC_NONE = 0, MLP_ENC_FREQ2D = 1 };
  * multiply-add.  The tensor-core kernels accumulate in fp32 in the hardware's own order and ignore it. */
 enum MlpSumOrder { MLP_SUM_NEURAL = 0, MLP_SUM_BIAS_FIRST_FUSED = 1 };
 
+/* How a layer's weights lie behind MlpLayerPointers.weights.  ROW_MAJOR is the example's layout, [out][in]
+ * (examples/mlp-training/mlp-training.cpp:217-250).  OPTIMAL is the neural module's OptimalLayout on CUDA
+ * (source/standard-modules/neural/layers.slang:53-71, network-parameter-layout-converter.slang:54-68,
+ * 176-181): rows and columns padded to multiples of 16, 16x16 tiles ordered input-tile-major, inside a tile
+ * the register order of a tensor-core B fragment; a layer's biases follow its weights in a padded slot
+ * (MlpLayerPointers.biases points at that slot).  The forward entry points read either; weights a shader
+ * holds in OptimalLayout are used in place, no conversion pass.  The training entry points take ROW_MAJOR
+ * only (the reference keeps OptimalLayout gradients in the target's accumulator-fragment order, a second
+ * format; mlp_layout_to_portable / mlp_layout_to_optimal convert between training and rendering). */
+enum MlpParamLayout { MLP_PARAMS_ROW_MAJOR = 0, MLP_PARAMS_OPTIMAL = 1 };
+
 typedef struct MlpConfig {
     int32_t n_layers;                  /* number of linear layers, 1..MLP_MAX_LAYERS */
     int32_t dims[MLP_MAX_LAYERS + 1];  /* dims[0] = width entering layer 0 (after encoding), dims[n_layers] = outputs */
@@ -75,7 +86,8 @@ typedef struct MlpConfig {
     float lr, beta1, beta2, eps;       /* Adam constants (adam.slang:15-19) */
     int32_t adam_master;               /* 1: Adam keeps an fp32 copy of each parameter in its state */
     int32_t sum_order;                 /* MlpSumOrder of the one-thread-per-sample kernels */
-    int32_t reserved[2];
+    int32_t param_layout;              /* MlpParamLayout of the weights (forward entry points) */
+    int32_t reserved[1];
 } MlpConfig;
 
 /* Optimiser state per parameter for the configurable path: the fp32 widening of the reference's

@@ -277,3 +277,26 @@ class Trainer:
 
     def read_states(self):
         return self.states.read(np.uint8).view(C.ADAM_STATE_DTYPE)
+
+
+class OptimalLayoutNetwork:
+    """Forward pass over parameters that lie in the neural module's OptimalLayout (16x16 tiles in tensor-core
+    B-fragment order, a padded bias slot behind every layer's weights: FFLayer's storage,
+    source/standard-modules/neural/layers.slang:53-71), used in place: the per-layer device addresses point
+    into the caller's buffer, nothing is converted.  `params_address` is that buffer on the device
+    (C.optimal_layout_offsets gives its element offsets)."""
+
+    def __init__(self, device, cfg, params_address, forward_entry="forward"):
+        assert cfg.param_layout == C.PARAMS_OPTIMAL
+        self.device, self.cfg = device, cfg
+        esz = C.DTYPE_SIZE[cfg.dtype]
+        w_off, b_off, self.total = C.optimal_layout_offsets(cfg.layer_dims)
+        net = np.zeros((cfg.n_layers, 4), dtype=np.uint64)
+        for l in range(cfg.n_layers):
+            net[l] = [params_address + w_off[l] * esz, 0, params_address + b_off[l] * esz, 0]
+        self.network = device.create_buffer(net.nbytes, net)
+        self.k_forward = device.kernel(forward_entry, cfg)
+
+    def forward(self, inputs_address, outputs_address, count, flags=0):
+        args = ForwardParams(self.network.address, inputs_address, outputs_address, count, flags)
+        self.k_forward.dispatch(args, groups_for(count))

@@ -23,6 +23,9 @@ ENC_NONE, ENC_FREQ2D = 0, 1
 # MlpSumOrder: neural module / cooperative-vector fallback order (zero start, rounded products, bias
 # last) and the example's order (bias first, fused multiply-adds).
 SUM_NEURAL, SUM_BIAS_FIRST_FUSED = 0, 1
+# MlpParamLayout: the example's row-major weights, or the neural module's OptimalLayout (16x16 tiles in
+# tensor-core B-fragment order, a padded bias slot behind every layer's weights).
+PARAMS_ROW_MAJOR, PARAMS_OPTIMAL = 0, 1
 
 DTYPE_SIZE = {F32: 4, F16: 2, BF16: 2}
 DTYPE_NAME = {F32: "f32", F16: "f16", BF16: "bf16"}
@@ -47,7 +50,8 @@ class MlpConfig(ctypes.Structure):
         ("eps", ctypes.c_float),
         ("adam_master", ctypes.c_int32),
         ("sum_order", ctypes.c_int32),
-        ("reserved", ctypes.c_int32 * 2),
+        ("param_layout", ctypes.c_int32),
+        ("reserved", ctypes.c_int32 * 1),
     ]
 
     @property
@@ -141,6 +145,19 @@ def param_layout(cfg):
         off += (nw + align - 1) // align * align
         b_off.append(off)
         off += (dims[l + 1] + align - 1) // align * align
+    return w_off, b_off, off
+
+
+def optimal_layout_offsets(dims):
+    """Element offsets (weights, biases) per layer and the element count of a network in OptimalLayout:
+    per layer align16(in) * align16(out) weights, then align16(out) bias slots (reserved for every layer)."""
+    a16 = lambda v: (v + 15) // 16 * 16
+    off, w_off, b_off = 0, [], []
+    for l in range(len(dims) - 1):
+        w_off.append(off)
+        off += a16(dims[l]) * a16(dims[l + 1])
+        b_off.append(off)
+        off += a16(dims[l + 1])
     return w_off, b_off, off
 
 

@@ -94,6 +94,7 @@ bool config_ok(const MlpConfig* c, std::string* why)
         c->output_act > MLP_ACT_LEAKY_MAX) { *why = "unknown activation"; return false; }
     if (c->loss != MLP_LOSS_MSE_MEAN && c->loss != MLP_LOSS_L2_SUM) { *why = "unknown loss"; return false; }
     if (c->sum_order != MLP_SUM_NEURAL && c->sum_order != MLP_SUM_BIAS_FIRST_FUSED) { *why = "unknown sum_order"; return false; }
+    if (c->param_layout != MLP_PARAMS_ROW_MAJOR && c->param_layout != MLP_PARAMS_OPTIMAL) { *why = "unknown param_layout"; return false; }
     if (c->encoding == MLP_ENC_FREQ2D && (c->dims[0] != 32 || c->input_width != 2)) {
         *why = "frequency encoding needs dims[0] = 32 and input_width = 2"; return false;
     }
@@ -279,6 +280,8 @@ int32_t mlp_kernel_get_for_config(MlpDevice* d, const MlpConfig* config, const c
     *out_kernel = nullptr;
     std::string why;
     if (!config_ok(config, &why)) return fail(MLP_E_INVALID_ARG, "bad config: %s", why.c_str());
+    if (config->param_layout != MLP_PARAMS_ROW_MAJOR && std::strncmp(entry_point, "forward", 7) != 0)
+        return fail(MLP_E_NOT_AVAILABLE, "'%s' takes row-major parameters; OptimalLayout parameters are read by the forward entry points only", entry_point);
     MlpKernel* k = new MlpKernel();
     k->cfg = *config;
     k->impl = "simt";

@@ -34,6 +34,20 @@ __device__ __forceinline__ void store_from_f32(int dtype, void* base, int64_t id
     else ((float*)base)[idx] = v;
 }
 
+// Element index of weight (output o, input i) of a layer behind MlpLayerPointers.weights.  OptimalLayout
+// (source/standard-modules/neural/network-parameter-layout-converter.slang:54-68, 176-181): 16x16 tiles,
+// tile (input tile, output tile) at (input_tile * tile_cols + output_tile) * 256, inside a tile the register
+// order of a tensor-core B fragment (lane = 4 * (output % 8) + (input % 8) / 2, then the output half, the
+// input half and the parity of the input).
+__host__ __device__ inline int64_t weight_index(int layout, int in, int out, int o, int i)
+{
+    if (layout != MLP_PARAMS_OPTIMAL) return int64_t(o) * in + i;
+    const int tile_cols = (out + 15) / 16;
+    const int row = i & 15, col = o & 15;
+    const int pos = (((col & 7) * 4 + ((row & 7) >> 1)) * 8) + (col >> 3) * 4 + (row >> 3) * 2 + (row & 1);
+    return int64_t((i >> 4) * tile_cols + (o >> 4)) * 256 + pos;
+}
+
 #define MLPB200_SQRT_2_OVER_PI 0.7978845608028654f
 #define MLPB200_GELU_C 0.044715f
 

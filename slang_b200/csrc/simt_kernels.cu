@@ -75,10 +75,10 @@ __device__ void simt_forward(const SimtNet& net, const MlpLayerPointers* __restr
             float r;
             if (fused) {
                 r = bias;
-                for (int i = 0; i < in; ++i) r = fmaf(load_as_f32(c.dtype, W, int64_t(j) * in + i), ain[i], r);
+                for (int i = 0; i < in; ++i) r = fmaf(load_as_f32(c.dtype, W, weight_index(c.param_layout, in, out, j, i)), ain[i], r);
             } else {
                 r = 0.0f;
-                for (int i = 0; i < in; ++i) r = mac(load_as_f32(c.dtype, W, int64_t(j) * in + i), ain[i], r, false);
+                for (int i = 0; i < in; ++i) r = mac(load_as_f32(c.dtype, W, weight_index(c.param_layout, in, out, j, i)), ain[i], r, false);
                 r = r + bias;
             }
             const float zs = round_to(c.dtype, r);
@@ -413,6 +413,7 @@ extern "C" int32_t mlp_learn_gradient_ordered_noalloc(int32_t device_ordinal, vo
         if (!config_ok(config, &why)) { set_last_error(("bad config: " + why).c_str()); return MLP_E_INVALID_ARG; }
     }
     const MlpConfig& c = *config;
+    if (c.param_layout != MLP_PARAMS_ROW_MAJOR) { set_last_error("learnGradient takes row-major parameters"); return MLP_E_NOT_AVAILABLE; }
     if (args->flags & MLP_FLAG_INPUT_GRADIENT) {
         set_last_error("this entry point takes MlpLearnGradParamsEx, which has no input-gradient address: MLP_FLAG_INPUT_GRADIENT is not available here");
         return MLP_E_NOT_AVAILABLE;

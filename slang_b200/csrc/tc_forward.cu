@@ -48,6 +48,7 @@ struct Params {
     uint32_t n_tiles;
     float act_alpha;
     uint32_t out_storage;  // 1: outputs are written in the network's 16-bit storage type instead of fp32
+    int param_layout;      // MlpParamLayout of the weights
 };
 
 template <int FMT> struct Cvt;
@@ -162,11 +163,23 @@ forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
     for (int l = 0; l < NL; ++l) {
         const int in = G::in_dim(l), out = G::out_dim(l);
         const uint4* src = (const uint4*)p.net[l].weights;
+        const uint16_t* src16 = (const uint16_t*)p.net[l].weights;
         const int cpr = in / 8;
         for (int idx = threadIdx.x; idx < out * cpr; idx += G::kThreads) {
             const int o = idx / cpr, j = idx % cpr;
             const uint32_t off = (l == 0) ? chunk_offset<DIN>(out, o, j) : chunk_offset<DH>(out, o, j);
-            *(uint4*)(smem + G::w_off(l) + off) = src[idx];
+            uint4 v;
+            if (p.param_layout == MLP_PARAMS_ROW_MAJOR) {
+                v = src[idx];
+            } else {
+                // OptimalLayout: the eight inputs of a chunk are four pairs inside one 16x16 tile
+                uint16_t hw[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) hw[e] = src16[weight_index(MLP_PARAMS_OPTIMAL, in, out, o, j * 8 + e)];
+                v = make_uint4(hw[0] | ((uint32_t)hw[1] << 16), hw[2] | ((uint32_t)hw[3] << 16), hw[4] | ((uint32_t)hw[5] << 16),
+                               hw[6] | ((uint32_t)hw[7] << 16));
+            }
+            *(uint4*)(smem + G::w_off(l) + off) = v;
         }
         for (int j = threadIdx.x; j < 128; j += G::kThreads)
             s_bias[l * 128 + j] = j < out ? load_as_f32(FMT, (const void*)p.net[l].biases, j) : 0.0f;
@@ -427,6 +440,7 @@ static cudaError_t launch_fwd(cudaStream_t st, TcWorkspace* ws, const MlpConfig&
     p.net = (const MlpLayerPointers*)a.networkBuffer;
     p.out = (float*)a.outputs;
     p.status = ws->status;
+    p.param_layout = c.param_layout;
     p.count = a.count;
     p.n_tiles = (a.count + 127u) / 128u;
     p.act_alpha = c.act_alpha;

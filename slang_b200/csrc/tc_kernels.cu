@@ -185,6 +185,7 @@ __device__ __forceinline__ void act_pair2(float2 z, float alpha, float2& a, floa
 struct WideTrainParams {
     int dims[wide::kMaxLayers + 1];  // the network's real widths
     int hidden_act;                  // used when the kernel is built for a run-time activation
+    int param_layout;                // MlpParamLayout of the weights (forward-only builds read either)
     int t_direct;                    // 1: the epilogue reads targets from global memory itself (no tensor map)
     int target_dtype;
     const void* targets;             // for t_direct
@@ -258,7 +259,7 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
         const uint16_t* w16 = (const uint16_t*)p.net[l].weights;
         const int chunks_per_row = inp / 8;  // 16-byte chunks: 8 elements
         const uint32_t panel_stride = (uint32_t)outp * 128u;
-        const bool rows_aligned = (in & 7) == 0;
+        const bool rows_aligned = (in & 7) == 0 && p.param_layout == MLP_PARAMS_ROW_MAJOR;
         for (int idx = threadIdx.x; idx < outp * chunks_per_row; idx += kThreads) {
             const int o = idx / chunks_per_row, c = idx % chunks_per_row;
             uint4 v = make_uint4(0u, 0u, 0u, 0u);
@@ -268,7 +269,7 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                 } else {
                     uint16_t hw[8];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) hw[j] = c * 8 + j < in ? w16[(size_t)o * in + c * 8 + j] : (uint16_t)0;
+                    for (int j = 0; j < 8; ++j) hw[j] = c * 8 + j < in ? w16[weight_index(p.param_layout, in, out, o, c * 8 + j)] : (uint16_t)0;
                     v = make_uint4(hw[0] | ((uint32_t)hw[1] << 16), hw[2] | ((uint32_t)hw[3] << 16), hw[4] | ((uint32_t)hw[5] << 16),
                                    hw[6] | ((uint32_t)hw[7] << 16));
                 }
@@ -1042,6 +1043,7 @@ cudaError_t launch_learn_gradient_tc(cudaStream_t st, TcWorkspace* ws, const Mlp
     WideTrainParams p;
     for (int l = 0; l <= wide::kMaxLayers; ++l) p.dims[l] = l <= nl ? c.dims[l] : 0;
     p.hidden_act = c.hidden_act;
+    p.param_layout = MLP_PARAMS_ROW_MAJOR;
     p.t_direct = t_direct ? 1 : 0;
     p.target_dtype = c.target_dtype;
     p.targets = (const void*)a.targets;
@@ -1075,6 +1077,7 @@ cudaError_t launch_forward_wide(cudaStream_t st, TcWorkspace* ws, const MlpConfi
     WideTrainParams p;
     for (int l = 0; l <= wide::kMaxLayers; ++l) p.dims[l] = l <= nl ? c.dims[l] : 0;
     p.hidden_act = c.hidden_act;
+    p.param_layout = c.param_layout;
     p.t_direct = 1;
     p.target_dtype = c.target_dtype;
     p.targets = nullptr;

@@ -167,7 +167,7 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
         const uint16_t* W = (const uint16_t*)p.net[l].weights;
         for (int idx = threadIdx.x; idx < H * H; idx += kThreads) {
             const int o = idx / H, i = idx % H;
-            const uint16_t v = (o < out && i < in) ? W[o * in + i] : (uint16_t)0;
+            const uint16_t v = (o < out && i < in) ? W[weight_index(c.param_layout, in, out, o, i)] : (uint16_t)0;
             *(uint16_t*)(smem + M::kW + l * kMat + chunk_offset<H>(H, o, i / 8) + (i % 8) * 2) = v;
         }
         for (int j = threadIdx.x; j < H; j += kThreads)

@@ -61,3 +61,94 @@ def test_converter_round_trip_on_gpu(elem):
         assert np.array_equal(ob2.read(p2.dtype).view(np.uint8), LO.to_optimal(p2, dims, mask).view(np.uint8))
     finally:
         dev.destroy()
+
+
+def test_fflayer_optimal_layout_envelope():
+    """tests/neural/fflayer-wavetangled-vector-tiled-test.slang:87-180: a 4 -> 2 layer in OptimalLayout has
+    ParameterCount 10, WeightStorageSize 256, BiasStorageSize 16, StorageSize 272, its bias at element 256;
+    the layer without a bias keeps the 272-element envelope (ParameterCount 8)."""
+    assert LO.sizes([4, 2], 0b1) == (10, 272)
+    assert LO.sizes([4, 2], 0b0) == (8, 272)
+    w_off, b_off, total = C.optimal_layout_offsets([4, 2])
+    assert (w_off, b_off, total) == ([0], [256], 272)
+    portable = np.array([1, 2, 3, 4, 5, 6, 7, 8, 9, 10], dtype=np.float32)   # W = [[1..4],[5..8]], b = [9, 10]
+    opt = LO.to_optimal(portable, [4, 2], 0b1)
+    assert opt.size == 272 and list(opt[256:258]) == [9.0, 10.0] and not opt[258:].any()
+    assert np.count_nonzero(opt[:256]) == 8
+    from slang_b200 import lib
+    lo, po = ctypes.c_int64(), ctypes.c_int64()
+    for mask, want in ((1, (10, 272)), (0, (8, 272))):
+        shape = C.network_shape([4, 2], mask, 4)
+        assert lib.load().mlp_layout_sizes(ctypes.byref(shape), ctypes.byref(lo), ctypes.byref(po)) == 0
+        assert (lo.value, po.value) == want
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dims,dtype,entry", [
+    ([4, 2], "f32", "forward_simt"),               # the tiled test's own layer: [39, 80]
+    ([4, 4, 2], "f16", "forward"),                 # padded 64-wide tensor-core kernel
+    ([64, 64, 64, 64, 64], "f16", "forward"),      # constant-width tensor-core kernel
+    ([128, 128, 128, 128, 128], "bf16", "forward"),
+    ([32, 128, 128, 3], "f16", "forward"),         # wide tensor-core kernel
+    ([5, 13, 7, 19], "f32", "forward_simt"),       # the converter test's shape, nothing a multiple of 16
+])
+def test_forward_reads_optimal_layout_in_place(dims, dtype, entry):
+    """The forward entry points read OptimalLayout parameters where they lie (FFLayer's storage,
+    source/standard-modules/neural/layers.slang:53-71): same outputs, bit for bit, as the same network in the
+    row-major layout; the 4 -> 2 layer of fflayer-wavetangled-vector-tiled-test.slang:93-110 gives [39, 80]."""
+    from slang_b200 import lib
+    from slang_b200.api import Device, OptimalLayoutNetwork, Trainer
+    from slang_b200.lib import check
+    dt = {"f32": C.F32, "f16": C.F16, "bf16": C.BF16}[dtype]
+    dev = Device(0)
+    try:
+        rng = np.random.default_rng(sum(dims))
+        act = C.ACT_IDENTITY if dims == [4, 2] else C.ACT_RELU
+        cfg = C.make_config(dims, dtype=dt, hidden_act=act, input_dtype=dt if dt != C.F32 else C.F32, target_dtype=C.F32)
+        w_off, b_off, total = C.param_layout(cfg)
+        p = np.zeros(total, dtype=np.float32)
+        for l in range(cfg.n_layers):
+            n = dims[l] * dims[l + 1]
+            p[w_off[l]:w_off[l] + n] = rng.uniform(-1, 1, n) * (2.0 / dims[l]) ** 0.5
+            p[b_off[l]:b_off[l] + dims[l + 1]] = rng.uniform(-0.5, 0.5, dims[l + 1])
+        if dims == [4, 2]:
+            p[w_off[0]:w_off[0] + 8] = np.arange(1, 9)
+            p[b_off[0]:b_off[0] + 2] = [9, 10]
+        ps = C.to_storage(p, dt)
+        count = 300
+        x = rng.uniform(-1, 1, (count, dims[0])).astype(np.float32)
+        if dims == [4, 2]:
+            x[:] = [1, 2, 3, 4]
+        xs = C.to_storage(x, cfg.input_dtype)
+        xb = dev.create_buffer(xs.nbytes, xs)
+        # row-major reference run
+        tr = Trainer(dev, cfg, ps, forward_entry=entry)
+        yb = dev.create_buffer(count * dims[-1] * 4)
+        tr.forward(xb.address, yb.address, count)
+        want = yb.read(np.float32).copy()
+        # portable (unpadded) parameters -> OptimalLayout with the library's converter, then used in place
+        portable = np.concatenate([np.concatenate([ps[w_off[l]:w_off[l] + dims[l] * dims[l + 1]], ps[b_off[l]:b_off[l] + dims[l + 1]]])
+                                   for l in range(cfg.n_layers)])
+        mask = (1 << cfg.n_layers) - 1
+        lo, po = LO.sizes(dims, mask)
+        assert portable.size == lo and po == C.optimal_layout_offsets(dims)[2]
+        shape = C.network_shape(dims, mask, portable.itemsize)
+        pb = dev.create_buffer(portable.nbytes, portable)
+        ob = dev.create_buffer(po * portable.itemsize)
+        check(lib.load().mlp_layout_to_optimal(dev.handle, ctypes.byref(shape), pb.address, ob.address))
+        cfg_opt = C.make_config(dims, dtype=dt, hidden_act=act, input_dtype=cfg.input_dtype, target_dtype=C.F32)
+        cfg_opt.param_layout = C.PARAMS_OPTIMAL
+        net = OptimalLayoutNetwork(dev, cfg_opt, ob.address, forward_entry=entry)
+        assert net.k_forward.implementation == tr.k_forward.implementation
+        y2 = dev.create_buffer(count * dims[-1] * 4)
+        net.forward(xb.address, y2.address, count)
+        got = y2.read(np.float32)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+        if dims == [4, 2]:
+            assert np.all(got.reshape(count, 2) == [39.0, 80.0])
+        # the training entry points refuse the layout
+        with pytest.raises(lib.MlpError) as info:
+            dev.kernel("learnGradient", cfg_opt)
+        assert info.value.code == -3
+    finally:
+        dev.destroy()

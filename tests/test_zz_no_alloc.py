@@ -157,21 +157,27 @@ def test_noalloc_entry_point_on_a_second_device_keeps_the_current_device():
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs: the area's address is looked up once per device")
-    from slang_b200.api import Device
-    torch.cuda.set_device(0)
+    from cuda.bindings import runtime as cudart
+    from slang_b200.api import Device, LearnGradParamsEx, Trainer
+    from slang_b200.lib import check
     device = Device(1)
     try:
         cfg, p0, batches = make_problem("c1", 500, seed=43, steps=1)
         x, t = batches[0]
         xb, tb = device.create_buffer(x.nbytes, x), device.create_buffer(t.nbytes, t)
         g_ref, l_ref = _reference(device, cfg, p0, xb, tb, 500)
-        torch.cuda.set_device(0)
-        g_new, l_new = _noalloc(device, cfg, p0, xb, tb, 500)
-        _same(g_new, l_new, g_ref, l_ref, "device 1")
-        # the current device is a property of the calling thread in the driver, so any binding of the
-        # runtime sees what the library left behind
-        from cuda.bindings import runtime as cudart
+        new = Trainer(device, cfg, p0, learn_entry="learnGradient_simt")  # only for its buffers
+        new.loss.clear()
+        device.wait()
+        # The current device is a property of the calling thread in the driver, so any binding of the runtime
+        # sets and sees it.  The handle-based calls above left device 1 current; make it device 0 and check
+        # that the call on device 1 puts device 0 back.
+        assert int(cudart.cudaSetDevice(0)[0]) == 0
+        args = LearnGradParamsEx(new.network.address, new.loss.address, xb.address, tb.address, 500, 0)
+        check(_call(1, None, cfg, args))
         err, cur = cudart.cudaGetDevice()
         assert int(err) == 0 and cur == 0
+        torch.cuda.synchronize(1)
+        _same(new.read_grads(), new.loss.read(np.uint32).copy(), g_ref, l_ref, "device 1")
     finally:
         device.destroy()
