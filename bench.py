@@ -520,6 +520,7 @@ def main():
     ap.add_argument("--batch", type=int, default=1 << 26, help="global batch (samples per step over all GPUs)")
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--no-sub", action="store_true", help="N=1: skip the block of the other configurations")
+    ap.add_argument("--log-jsonl", default=None, help="write one JSON object per timed step (phase times, samples/s) to this file (rank 0)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--deterministic-sum", action="store_true",
@@ -625,16 +626,19 @@ def main():
     sampler = ClockSampler(local_rank)
     sampler.start()
     launches0 = device.launch_count
+    from slang_b200.metrics import JsonlLogger, PhaseTimer
+    phase_timer = PhaseTimer(stream)
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    k_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     ev0.record()
     for i in range(args.steps):
         b = i % n_batches
-        k_ev[i][0].record()
+        phase_timer.begin_step()
         trainer.learn_gradient(xs[b].data_ptr(), ts[b].data_ptr(), count)
-        k_ev[i][1].record()
+        phase_timer.mark("learn_gradient")
         allreduce()
+        phase_timer.mark("exchange")
         trainer.adjust_parameters()
+        phase_timer.mark("adjust_parameters")
     ev1.record()
     torch.cuda.synchronize()
     if world > 1:
@@ -645,7 +649,15 @@ def main():
     device.wait()  # raises if a kernel set the status word
 
     elapsed_ms = ev0.elapsed_time(ev1)
-    kernel_ms = float(np.mean([a.elapsed_time(b) for a, b in k_ev]))
+    phase_rows = phase_timer.collect()
+    # the learn_gradient phase includes the 8-byte clear of the loss words that precedes the kernel
+    kernel_ms = float(np.mean([r["learn_gradient_ms"] for r in phase_rows]))
+    phases = {k: float(np.mean([r[k] for r in phase_rows])) for k in phase_rows[0]}
+    if args.log_jsonl and rank == 0:
+        log = JsonlLogger(args.log_jsonl)
+        for i, r in enumerate(phase_rows):
+            log.log(i, args.batch, r, n_gpus=world)
+        log.close()
     if world > 1:
         tt = torch.tensor([elapsed_ms, kernel_ms], dtype=torch.float64, device=dev_t)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
@@ -719,7 +731,7 @@ def main():
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": workload_name(args), "global_batch": args.batch, "per_gpu_batch": count,
                        "parallelism": "dp%d" % world, "gradient_sum": ("rank-ordered gather" if args.deterministic_sum else "all-reduce") + " through mlp_allreduce_grads (NCCL bound inside the library)", "l2": "inputs (%.1f GB per step per GPU) larger than L2; two batches alternate" % (count * 256 / 1e9)},
-            "clocks": clocks, "gpu_launches": launches, "e2e": e2e,
+            "clocks": clocks, "gpu_launches": launches, "e2e": e2e, "phases_ms": phases,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_sustained"], "unit": "TFLOP/s",
                          "frac": achieved / peaks["bf16_sustained"], "frac_of_burst": achieved / peaks["bf16_burst"],
                          # DRAM read + write bytes of one launch: a constant from one profiler capture of a
