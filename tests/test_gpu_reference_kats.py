@@ -171,3 +171,80 @@ def test_config2_trajectory_at_its_stated_length(device):
     assert dev_gpu.max() <= 3 * max(dev_alt.max(), 1e-2)
     assert perr_gpu <= 3 * max(perr_alt, 2e-2)
     assert abs(tail(l_gpu) - tail(l_ref)) <= 5e-2 * tail(l_ref)
+
+
+def _run_learn(device, cfg, p, x, t, entry="learnGradient"):
+    from slang_b200.api import Trainer
+    tr = Trainer(device, cfg, p, learn_entry=entry)
+    xs, ts = C.to_storage(x, cfg.input_dtype), C.to_storage(t, cfg.target_dtype)
+    xb, tb = device.create_buffer(xs.nbytes, xs), device.create_buffer(ts.nbytes, ts)
+    tr.learn_gradient(xb.address, tb.address, x.shape[0])
+    return tr, tr.read_grads()
+
+
+@pytest.mark.parametrize("entry", ["learnGradient", "learnGradient_simt"], ids=["tcgen05", "simt"])
+@pytest.mark.parametrize("dtype", [C.F16, C.BF16], ids=["f16", "bf16"])
+@pytest.mark.parametrize("size", [16, 32, 64])
+def test_tiled_backward_identity_known_answer(device, size, dtype, entry):
+    """tests/neural/mma-tiled-backward-test.slang:67-127: W = identity, input ones, dOut of thread t equal to
+    t + 1 in every component, 32 threads: dInput = W^T dOut = dOut.  Here the tested layer is the second of
+    two identity layers, so its dInput shows up as the first layer's bias gradient: sum over the 32 samples
+    of (t + 1) = 528 per component; the tested layer's own dW and db are 528 as well (inputs are ones)."""
+    batch = 32
+    cfg = C.make_config([size, size, size], dtype, C.ACT_IDENTITY, loss=C.LOSS_L2_SUM, input_dtype=C.F32, target_dtype=C.F32)
+    w_off, b_off, total = C.param_layout(cfg)
+    p = np.zeros(total, dtype=np.float32)
+    for l in range(2):
+        p[w_off[l]:w_off[l] + size * size] = np.eye(size).reshape(-1)
+    x = np.ones((batch, size), dtype=np.float32)
+    # dOut = 2 (out - target) with out = 1  ->  target = 1 - (t + 1) / 2
+    t = np.repeat((1.0 - (np.arange(batch) + 1) / 2.0)[:, None], size, axis=1).astype(np.float32)
+    tr, g = _run_learn(device, cfg, C.to_storage(p, dtype), x, t, entry)
+    assert tr.k_learn.implementation == ("tcgen05" if entry == "learnGradient" else "simt")
+    want = batch * (batch + 1) / 2
+    assert np.all(g[b_off[0]:b_off[0] + size] == want)                      # sum of dInput of the tested layer
+    assert np.all(g[b_off[1]:b_off[1] + size] == want)                      # its bias gradient
+    assert np.all(g[w_off[1]:w_off[1] + size * size] == want)               # its weight gradient (inputs are ones)
+
+
+@pytest.mark.parametrize("dtype", [C.F16, C.BF16], ids=["f16", "bf16"])
+@pytest.mark.parametrize("m", [3, 15, 23, 47])
+def test_bias_sum_reduce_known_answer(device, m, dtype):
+    """tests/neural/bias-sum-reduce.slang:38-67: every one of 128 threads holds dOut[i] = (i + 1) / 128 for an
+    output width of 3, 15, 23 or 47; the reduced bias gradient is i + 1 (tolerance 0.001 there, exact here).
+    Zero weights make the outputs zero, so the L2 targets -(i + 1) / 256 give exactly that dOut."""
+    batch = 128
+    cfg = C.make_config([8, 8, m], dtype, C.ACT_IDENTITY, loss=C.LOSS_L2_SUM, input_dtype=C.F32, target_dtype=C.F32)
+    w_off, b_off, total = C.param_layout(cfg)
+    p = np.zeros(total, dtype=np.float32)
+    p[w_off[0]:w_off[0] + 64] = np.eye(8).reshape(-1)
+    x = np.ones((batch, 8), dtype=np.float32)
+    t = np.tile(-(np.arange(m) + 1) / 256.0, (batch, 1)).astype(np.float32)
+    tr, g = _run_learn(device, cfg, C.to_storage(p, dtype), x, t)
+    assert tr.k_learn.implementation == "tcgen05"
+    assert list(g[b_off[1]:b_off[1] + m]) == [float(i + 1) for i in range(m)]
+
+
+@pytest.mark.parametrize("dtype", [C.F16, C.BF16], ids=["f16", "bf16"])
+@pytest.mark.parametrize("k,m", [(8, 8), (16, 32), (32, 16), (64, 64), (24, 40)])
+def test_outer_product_accumulate_known_answer(device, k, m, dtype):
+    """tests/neural/outerproduct-accumulate-test.slang:47-92: 128 threads, input[j] = (j + 1)(t + 1) / 128,
+    dOut[i] = (M - i) / 128; the accumulated outer product is dW[i][j] = (M - i)(j + 1) * 129 / 256 within
+    WorkgroupSize * 0.016 = 2.05 (the test's tolerance for half inputs), and within 1e-2 relative of the
+    oracle, which rounds the inputs to the storage type as the kernel does."""
+    batch = 128
+    cfg = C.make_config([k, k, m], dtype, C.ACT_IDENTITY, loss=C.LOSS_L2_SUM, input_dtype=C.F32, target_dtype=C.F32)
+    w_off, b_off, total = C.param_layout(cfg)
+    p = np.zeros(total, dtype=np.float32)
+    p[w_off[0]:w_off[0] + k * k] = np.eye(k).reshape(-1)
+    x = ((np.arange(k) + 1)[None, :] * (np.arange(batch) + 1)[:, None] / 128.0).astype(np.float32)
+    t = np.tile(-(m - np.arange(m)) / 256.0, (batch, 1)).astype(np.float32)
+    ps = C.to_storage(p, dtype)
+    tr, g = _run_learn(device, cfg, ps, x, t)
+    assert tr.k_learn.implementation == "tcgen05"
+    got = g[w_off[1]:w_off[1] + m * k].reshape(m, k)
+    want = (m - np.arange(m))[:, None] * (np.arange(k) + 1)[None, :] * (129.0 / 256.0)
+    assert np.max(np.abs(got - want)) <= 128 * 0.016
+    _, _, g_ref, _ = oracle_trajectory(cfg, ps, [(x, t)])
+    ref = g_ref[w_off[1]:w_off[1] + m * k].reshape(m, k)
+    assert np.max(np.abs(got - ref)) <= 1e-2 * np.max(np.abs(ref))
