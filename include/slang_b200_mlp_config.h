@@ -87,7 +87,13 @@ typedef struct MlpConfig {
     int32_t adam_master;               /* 1: Adam keeps an fp32 copy of each parameter in its state */
     int32_t sum_order;                 /* MlpSumOrder of the one-thread-per-sample kernels */
     int32_t param_layout;              /* MlpParamLayout of the weights (forward entry points) */
-    int32_t reserved[1];
+    int32_t operand_dtype;             /* 0: products read the storage type.  MLP_F16 / MLP_BF16 with dtype = MLP_F32:
+                                          the neural module's T = float on its tensor-core path, whose matrix
+                                          operands are half whatever T is (source/standard-modules/neural/
+                                          mma-tiled-cuda.slang:104-118, WaveMatrix.slang:62-64): weights and the
+                                          vectors passed between layers are converted to that type where a product
+                                          reads them; biases, sums, pre-activations, outputs, gradients and the
+                                          optimiser stay fp32 */
 } MlpConfig;
 
 /* Optimiser state per parameter for the configurable path: the fp32 widening of the reference's

@@ -237,6 +237,13 @@ template <> struct AccOps<double> {
 
 const float kPi = 3.14159265358979323846f;
 
+// The type a product reads its operands in: the storage type, or MlpConfig.operand_dtype for fp32 storage with
+// 16-bit tensor-core operands (the neural module's T = float: source/standard-modules/neural/
+// mma-tiled-cuda.slang:104-118 converts both matrix operands to half whatever the element type is).
+inline int operand_type(const MlpConfig& c) { return c.operand_dtype ? c.operand_dtype : c.dtype; }
+inline float round_op(const MlpConfig& c, float v) { return round_to(operand_type(c), v); }
+
+
 void encode_input(const MlpConfig& c, const void* inputs, int64_t s, float* a0)
 {
     if (c.encoding == MLP_ENC_FREQ2D) {
@@ -244,13 +251,13 @@ void encode_input(const MlpConfig& c, const void* inputs, int64_t s, float* a0)
             float v = load_as_f32(c.input_dtype, inputs, s * 2 + u);
             for (int k = 0; k < 8; ++k) {
                 float arg = std::ldexp(kPi, k) * v;
-                a0[u * 16 + k * 2 + 0] = round_to(c.dtype, std::sin(arg));
-                a0[u * 16 + k * 2 + 1] = round_to(c.dtype, std::cos(arg));
+                a0[u * 16 + k * 2 + 0] = round_op(c, std::sin(arg));
+                a0[u * 16 + k * 2 + 1] = round_op(c, std::cos(arg));
             }
         }
     } else {
         for (int i = 0; i < c.dims[0]; ++i)
-            a0[i] = round_to(c.dtype, load_as_f32(c.input_dtype, inputs, s * c.dims[0] + i));
+            a0[i] = round_op(c, load_as_f32(c.input_dtype, inputs, s * c.dims[0] + i));
     }
 }
 
@@ -261,6 +268,12 @@ struct FloatParams {
     FloatParams(const MlpConfig& c, const Layout& L, const void* params) : v(size_t(L.total))
     {
         for (int64_t i = 0; i < L.total; ++i) v[size_t(i)] = load_as_f32(c.dtype, params, i);
+        if (c.operand_dtype) {
+            // weights as the products read them; biases keep the storage type
+            for (int l = 0; l < c.n_layers; ++l)
+                for (int64_t i = 0; i < int64_t(c.dims[l]) * c.dims[l + 1]; ++i)
+                    v[size_t(L.w[l] + i)] = round_op(c, v[size_t(L.w[l] + i)]);
+        }
     }
 };
 
@@ -309,7 +322,7 @@ void forward_sample(const MlpConfig& c, const Layout& L, const float* params, co
             float zs = round_to(c.dtype, zf);
             sc.z[l][j] = zs;
             if (last) sc.a[l + 1][j] = act_value(c.output_act, c.act_alpha, zs);
-            else sc.a[l + 1][j] = round_to(c.dtype, act_value(c.hidden_act, c.act_alpha, zs));
+            else sc.a[l + 1][j] = round_op(c, act_value(c.hidden_act, c.act_alpha, zs));
         }
     }
 }
@@ -331,7 +344,7 @@ float learn_sample(const MlpConfig& c, const Layout& L, const float* params, flo
         loss = std::fmaf(diff * scale, diff, loss);
         float dout = 2.0f * scale * diff;
         float d = act_deriv(c.output_act, c.act_alpha, sc.z[nl - 1][j]);
-        sc.dz[j] = round_to(c.dtype, dout * d);
+        sc.dz[j] = round_op(c, dout * d);
     }
     for (int l = nl - 1; l >= 0; --l) {
         const int in = c.dims[l], out = c.dims[l + 1];
@@ -379,8 +392,8 @@ float learn_sample(const MlpConfig& c, const Layout& L, const float* params, flo
                 for (int j = 0; j < out; ++j) r = AccOps<Acc>::mac(r, wcol[int64_t(j) * in], sc.dz[j], fused);
                 v = float(r);
             }
-            float d = round_to(c.dtype, act_deriv(c.hidden_act, c.act_alpha, sc.z[l - 1][i]));
-            sc.da[i] = round_to(c.dtype, v * d);
+            float d = round_op(c, act_deriv(c.hidden_act, c.act_alpha, sc.z[l - 1][i]));
+            sc.da[i] = round_op(c, v * d);
         }
         std::swap(sc.dz, sc.da);
     }

@@ -51,7 +51,7 @@ class MlpConfig(ctypes.Structure):
         ("adam_master", ctypes.c_int32),
         ("sum_order", ctypes.c_int32),
         ("param_layout", ctypes.c_int32),
-        ("reserved", ctypes.c_int32 * 1),
+        ("operand_dtype", ctypes.c_int32),
     ]
 
     @property
@@ -89,7 +89,7 @@ EXAMPLE_ADAM_STATE_DTYPE = np.dtype([("mean", "<u2"), ("variance", "<u2"), ("ite
 
 def make_config(dims, dtype=F32, hidden_act=ACT_RELU, output_act=ACT_IDENTITY, act_alpha=0.01,
                 loss=LOSS_MSE_MEAN, encoding=ENC_NONE, input_dtype=F32, target_dtype=F32,
-                lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, adam_master=0, sum_order=SUM_NEURAL):
+                lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, adam_master=0, sum_order=SUM_NEURAL, operand_dtype=0):
     dims = list(dims)
     if not (1 <= len(dims) - 1 <= MLP_MAX_LAYERS):
         raise ValueError("layer count out of range")
@@ -104,6 +104,7 @@ def make_config(dims, dtype=F32, hidden_act=ACT_RELU, output_act=ACT_IDENTITY, a
     c.lr, c.beta1, c.beta2, c.eps = lr, beta1, beta2, eps
     c.adam_master = adam_master
     c.sum_order = sum_order
+    c.operand_dtype = operand_dtype  # F16 / BF16 with dtype F32: fp32 storage, 16-bit tensor-core operands
     return c
 
 

@@ -95,6 +95,9 @@ bool config_ok(const MlpConfig* c, std::string* why)
     if (c->loss != MLP_LOSS_MSE_MEAN && c->loss != MLP_LOSS_L2_SUM) { *why = "unknown loss"; return false; }
     if (c->sum_order != MLP_SUM_NEURAL && c->sum_order != MLP_SUM_BIAS_FIRST_FUSED) { *why = "unknown sum_order"; return false; }
     if (c->param_layout != MLP_PARAMS_ROW_MAJOR && c->param_layout != MLP_PARAMS_OPTIMAL) { *why = "unknown param_layout"; return false; }
+    if (c->operand_dtype != 0 && !(c->dtype == MLP_F32 && (c->operand_dtype == MLP_F16 || c->operand_dtype == MLP_BF16))) {
+        *why = "operand_dtype must be 0, or MLP_F16 / MLP_BF16 with dtype = MLP_F32"; return false;
+    }
     if (c->encoding == MLP_ENC_FREQ2D && (c->dims[0] != 32 || c->input_width != 2)) {
         *why = "frequency encoding needs dims[0] = 32 and input_width = 2"; return false;
     }

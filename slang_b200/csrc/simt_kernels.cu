@@ -29,20 +29,30 @@ struct SimtNet {
     int a_off[MLP_MAX_LAYERS + 2];  // offset of the vector entering layer l in the per-thread arrays
 };
 
+// The type products read their operands in: the storage type, or MlpConfig.operand_dtype (fp32 storage whose
+// weights and inter-layer vectors are converted to a 16-bit type where a product reads them).
+__device__ __forceinline__ int operand_type(const MlpConfig& c) { return c.operand_dtype ? c.operand_dtype : c.dtype; }
+__device__ __forceinline__ float load_weight(const MlpConfig& c, const void* W, int64_t idx)
+{
+    const float w = load_as_f32(c.dtype, W, idx);
+    return c.operand_dtype ? round_to(c.operand_dtype, w) : w;
+}
+
 __device__ __forceinline__ void encode_input(const MlpConfig& c, const void* inputs, int64_t s, float* a0)
 {
+    const int opd = operand_type(c);
     if (c.encoding == MLP_ENC_FREQ2D) {
         for (int u = 0; u < 2; ++u) {
             const float v = load_as_f32(c.input_dtype, inputs, s * 2 + u);
             for (int k = 0; k < 8; ++k) {
                 const float arg = ldexpf(3.14159265358979323846f, k) * v;
-                a0[u * 16 + k * 2 + 0] = round_to(c.dtype, sinf(arg));
-                a0[u * 16 + k * 2 + 1] = round_to(c.dtype, cosf(arg));
+                a0[u * 16 + k * 2 + 0] = round_to(opd, sinf(arg));
+                a0[u * 16 + k * 2 + 1] = round_to(opd, cosf(arg));
             }
         }
     } else {
         for (int i = 0; i < c.dims[0]; ++i)
-            a0[i] = round_to(c.dtype, load_as_f32(c.input_dtype, inputs, s * c.dims[0] + i));
+            a0[i] = round_to(opd, load_as_f32(c.input_dtype, inputs, s * c.dims[0] + i));
     }
 }
 
@@ -75,16 +85,16 @@ __device__ void simt_forward(const SimtNet& net, const MlpLayerPointers* __restr
             float r;
             if (fused) {
                 r = bias;
-                for (int i = 0; i < in; ++i) r = fmaf(load_as_f32(c.dtype, W, weight_index(c.param_layout, in, out, j, i)), ain[i], r);
+                for (int i = 0; i < in; ++i) r = fmaf(load_weight(c, W, weight_index(c.param_layout, in, out, j, i)), ain[i], r);
             } else {
                 r = 0.0f;
-                for (int i = 0; i < in; ++i) r = mac(load_as_f32(c.dtype, W, weight_index(c.param_layout, in, out, j, i)), ain[i], r, false);
+                for (int i = 0; i < in; ++i) r = mac(load_weight(c, W, weight_index(c.param_layout, in, out, j, i)), ain[i], r, false);
                 r = r + bias;
             }
             const float zs = round_to(c.dtype, r);
             zl[j] = zs;
             aout[j] = last ? act_value(c.output_act, c.act_alpha, zs)
-                           : round_to(c.dtype, act_value(c.hidden_act, c.act_alpha, zs));
+                           : round_to(operand_type(c), act_value(c.hidden_act, c.act_alpha, zs));
         }
     }
 }
@@ -134,7 +144,7 @@ learn_gradient_simt_kernel(SimtNet net, const MlpLayerPointers* __restrict__ lp,
             loss = fmaf(diff * scale, diff, loss);
             const float dout = (2.0f * scale) * diff;
             const float d = act_deriv(c.output_act, c.act_alpha, dzl[j]);
-            dzl[j] = round_to(c.dtype, dout * d);
+            dzl[j] = round_to(operand_type(c), dout * d);
         }
         for (int l = nl - 1; l >= 1; --l) {
             const int in = c.dims[l], out = c.dims[l + 1];
@@ -143,9 +153,9 @@ learn_gradient_simt_kernel(SimtNet net, const MlpLayerPointers* __restrict__ lp,
             const void* W = (const void*)lp[l].weights;
             for (int i = 0; i < in; ++i) {
                 float r = 0.0f;
-                for (int j = 0; j < out; ++j) r = mac(load_as_f32(c.dtype, W, int64_t(j) * in + i), dz[j], r, fused);
-                const float d = round_to(c.dtype, act_deriv(c.hidden_act, c.act_alpha, zprev[i]));
-                zprev[i] = round_to(c.dtype, r * d);
+                for (int j = 0; j < out; ++j) r = mac(load_weight(c, W, int64_t(j) * in + i), dz[j], r, fused);
+                const float d = round_to(operand_type(c), act_deriv(c.hidden_act, c.act_alpha, zprev[i]));
+                zprev[i] = round_to(operand_type(c), r * d);
             }
         }
         if (input_grads) {
@@ -155,7 +165,7 @@ learn_gradient_simt_kernel(SimtNet net, const MlpLayerPointers* __restrict__ lp,
             const void* W = (const void*)lp[0].weights;
             for (int i = 0; i < in; ++i) {
                 float r = 0.0f;
-                for (int j = 0; j < out; ++j) r = mac(load_as_f32(c.dtype, W, int64_t(j) * in + i), dz[j], r, fused);
+                for (int j = 0; j < out; ++j) r = mac(load_weight(c, W, int64_t(j) * in + i), dz[j], r, fused);
                 input_grads[int64_t(tid) * in + i] = round_to(c.dtype, r);
             }
         }

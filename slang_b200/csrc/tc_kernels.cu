@@ -186,6 +186,8 @@ struct WideTrainParams {
     int dims[wide::kMaxLayers + 1];  // the network's real widths
     int hidden_act;                  // used when the kernel is built for a run-time activation
     int param_layout;                // MlpParamLayout of the weights (forward-only builds read either)
+    int storage_dtype;               // MlpDType of parameters and biases in memory; MLP_F32 = fp32 storage with 16-bit
+                                     // operands: weights converted at staging, pre-activations and outputs not rounded
     int t_direct;                    // 1: the epilogue reads targets from global memory itself (no tensor map)
     int target_dtype;
     const void* targets;             // for t_direct
@@ -257,9 +259,11 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
         const int in = p.dims[l], out = p.dims[l + 1];
         const int inp = in_dim(l), outp = out_dim(l, NL);
         const uint16_t* w16 = (const uint16_t*)p.net[l].weights;
+        const float* w32 = (const float*)p.net[l].weights;
+        const bool fp32_storage = p.storage_dtype == MLP_F32;
         const int chunks_per_row = inp / 8;  // 16-byte chunks: 8 elements
         const uint32_t panel_stride = (uint32_t)outp * 128u;
-        const bool rows_aligned = (in & 7) == 0 && p.param_layout == MLP_PARAMS_ROW_MAJOR;
+        const bool rows_aligned = (in & 7) == 0 && p.param_layout == MLP_PARAMS_ROW_MAJOR && !fp32_storage;
         for (int idx = threadIdx.x; idx < outp * chunks_per_row; idx += kThreads) {
             const int o = idx / chunks_per_row, c = idx % chunks_per_row;
             uint4 v = make_uint4(0u, 0u, 0u, 0u);
@@ -269,7 +273,13 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                 } else {
                     uint16_t hw[8];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) hw[j] = c * 8 + j < in ? w16[weight_index(p.param_layout, in, out, o, c * 8 + j)] : (uint16_t)0;
+                    for (int j = 0; j < 8; ++j) {
+                        hw[j] = 0;
+                        if (c * 8 + j < in) {
+                            const int64_t wi = weight_index(p.param_layout, in, out, o, c * 8 + j);
+                            hw[j] = fp32_storage ? E::pack(w32[wi]) : w16[wi];
+                        }
+                    }
                     v = make_uint4(hw[0] | ((uint32_t)hw[1] << 16), hw[2] | ((uint32_t)hw[3] << 16), hw[4] | ((uint32_t)hw[5] << 16),
                                    hw[6] | ((uint32_t)hw[7] << 16));
                 }
@@ -279,7 +289,7 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
         }
         const int brow = l == NL - 1 ? kMaxLayers - 1 : l;
         for (int j = threadIdx.x; j < 128; j += kThreads)
-            s_bias[brow * 128 + j] = j < out ? load_as_f32(FMT, (const void*)p.net[l].biases, j) : 0.0f;
+            s_bias[brow * 128 + j] = j < out ? load_as_f32(p.storage_dtype, (const void*)p.net[l].biases, j) : 0.0f;
     }
     fence_async_smem();
     tc_fence_before();
@@ -555,6 +565,7 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
         for (int l = 0; l < NL - 1; ++l) db[l] = 0.0f;
         float run_max = 0.0f, run_sum = 0.0f;  // per-lane (per sample slot) in the two warps that total the losses
         uint32_t n_full0 = 0, n_full1 = 0;     // phases of acc_full[h] this warp has consumed
+        const bool fp32_storage = p.storage_dtype == MLP_F32;  // pre-activations and outputs are not rounded
         bool ok = true;
 #ifdef MLPB200_TRACE
         bool tr_on = false;
@@ -598,13 +609,17 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                         for (int s = 0; s < CPT; s += 2) {
                             // bias, storage rounding of the pre-activation (one paired conversion), activation
                             const float2 zf = __fadd2_rn(make_float2(__uint_as_float(v[s]), __uint_as_float(v[s + 1])), bias2);
-                            const uint32_t zr = E::pack2(zf.x, zf.y);
+                            float2 z = zf;
+                            if (!fp32_storage) {
+                                const uint32_t zr = E::pack2(zf.x, zf.y);
+                                z = make_float2(E::unpack_lo(zr), E::unpack_hi(zr));
+                            }
                             float2 a, d;
                             if constexpr (ACT >= 0) {
-                                act_pair2<ACT>(make_float2(E::unpack_lo(zr), E::unpack_hi(zr)), p.act_alpha, a, d);
+                                act_pair2<ACT>(z, p.act_alpha, a, d);
                             } else {
-                                act_pair_rt(p.hidden_act, E::unpack_lo(zr), p.act_alpha, a.x, d.x);
-                                act_pair_rt(p.hidden_act, E::unpack_hi(zr), p.act_alpha, a.y, d.y);
+                                act_pair_rt(p.hidden_act, z.x, p.act_alpha, a.x, d.x);
+                                act_pair_rt(p.hidden_act, z.y, p.act_alpha, a.y, d.y);
                             }
                             aw[s >> 1] = E::pack2(a.x, a.y);
                             if constexpr (!FWD) dreg[h][l][s >> 1] = E::pack2(d.x, d.y);
@@ -647,9 +662,10 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                         float* dst = p.outputs + ((size_t)tile * NS + (size_t)s) * (size_t)od + fb;
 #pragma unroll
                         for (int j = 0; j < 8; j += 2) {
-                            const uint32_t op = E::pack2(__uint_as_float(v[j]) + bb[j], __uint_as_float(v[j + 1]) + bb[j + 1]);
-                            if (fb + j < od) dst[j] = E::unpack_lo(op);
-                            if (fb + j + 1 < od) dst[j + 1] = E::unpack_hi(op);
+                            const float r0 = __uint_as_float(v[j]) + bb[j], r1 = __uint_as_float(v[j + 1]) + bb[j + 1];
+                            const uint32_t op = E::pack2(r0, r1);
+                            if (fb + j < od) dst[j] = fp32_storage ? r0 : E::unpack_lo(op);
+                            if (fb + j + 1 < od) dst[j + 1] = fp32_storage ? r1 : E::unpack_hi(op);
                         }
                     }
                     tc_fence_before();
@@ -680,9 +696,10 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                 float loss = 0.0f;
 #pragma unroll
                 for (int j = 0; j < 8; j += 2) {
-                    const uint32_t op = E::pack2(__uint_as_float(v[j]) + bo[j], __uint_as_float(v[j + 1]) + bo[j + 1]);  // storage rounding
-                    const float d0 = E::unpack_lo(op) - tf[j];
-                    const float d1 = E::unpack_hi(op) - tf[j + 1];
+                    const float r0 = __uint_as_float(v[j]) + bo[j], r1 = __uint_as_float(v[j + 1]) + bo[j + 1];
+                    const uint32_t op = E::pack2(r0, r1);  // storage rounding
+                    const float d0 = (fp32_storage ? r0 : E::unpack_lo(op)) - tf[j];
+                    const float d1 = (fp32_storage ? r1 : E::unpack_hi(op)) - tf[j + 1];
                     const uint32_t zp = valid ? E::pack2(two_scale * d0, two_scale * d1) : 0u;
                     zw[j >> 1] = zp;
                     dzf[j] = E::unpack_lo(zp);
@@ -893,8 +910,9 @@ static bool wide_supported(const MlpConfig& c)
     // format and rows that start on 16-byte boundaries (the input tile arrives by TMA); identity output.
     const int nl = c.n_layers;
     if (nl < 2 || nl > wide::kMaxLayers) return false;
-    if (c.dtype != MLP_BF16 && c.dtype != MLP_F16) return false;
-    if (c.input_dtype != c.dtype) return false;
+    const int op = c.operand_dtype ? c.operand_dtype : c.dtype;  // fp32 storage runs here with 16-bit operands
+    if (op != MLP_BF16 && op != MLP_F16) return false;
+    if (c.input_dtype != op) return false;
     if (c.output_act != MLP_ACT_IDENTITY || c.encoding != MLP_ENC_NONE) return false;
     if (c.dims[0] > wide::D0 || (c.dims[0] & 7) != 0 || c.dims[nl] > wide::DOUT) return false;
     bool any_wide = false;
@@ -1033,17 +1051,19 @@ cudaError_t launch_learn_gradient_tc(cudaStream_t st, TcWorkspace* ws, const Mlp
     const int nl = c.n_layers;
     const int d0 = c.dims[0], dout = c.dims[nl];
     CUtensorMap mx, mt;
-    const CUtensorMapDataType dt = c.dtype == MLP_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const int op = c.operand_dtype ? c.operand_dtype : c.dtype;
+    const CUtensorMapDataType dt = op == MLP_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     // Boxes of 64 rows x 64 columns over [count][width]: columns past the real width arrive as zeros.
     if (!make_tile_map(ws, &mx, dt, 2, a.inputs, a.count, (uint32_t)d0, 64, wide::NS, CU_TENSOR_MAP_SWIZZLE_128B, err)) return cudaErrorInvalidValue;
     // Targets come by TMA when their rows are 16-byte multiples in the storage format, else the epilogue reads them.
-    const bool t_direct = c.target_dtype != c.dtype || (dout & 7) != 0 || (a.targets & 15u) != 0;
+    const bool t_direct = c.target_dtype != op || (dout & 7) != 0 || (a.targets & 15u) != 0;
     if (t_direct) mt = mx;
     else if (!make_tile_map(ws, &mt, dt, 2, a.targets, a.count, (uint32_t)dout, 64, wide::NS, CU_TENSOR_MAP_SWIZZLE_128B, err)) return cudaErrorInvalidValue;
     WideTrainParams p;
     for (int l = 0; l <= wide::kMaxLayers; ++l) p.dims[l] = l <= nl ? c.dims[l] : 0;
     p.hidden_act = c.hidden_act;
     p.param_layout = MLP_PARAMS_ROW_MAJOR;
+    p.storage_dtype = c.dtype;
     p.t_direct = t_direct ? 1 : 0;
     p.target_dtype = c.target_dtype;
     p.targets = (const void*)a.targets;
@@ -1056,7 +1076,7 @@ cudaError_t launch_learn_gradient_tc(cudaStream_t st, TcWorkspace* ws, const Mlp
     p.act_alpha = c.act_alpha;
     p.timing = ws->timing;
     p.outputs = nullptr;
-    const cudaError_t e = c.dtype == MLP_BF16 ? launch_wide_fmt<MLP_BF16, false>(st, ws, c, mx, mt, p)
+    const cudaError_t e = op == MLP_BF16 ? launch_wide_fmt<MLP_BF16, false>(st, ws, c, mx, mt, p)
                                               : launch_wide_fmt<MLP_F16, false>(st, ws, c, mx, mt, p);
     *launches += 1;
     return e;
@@ -1072,12 +1092,14 @@ cudaError_t launch_forward_wide(cudaStream_t st, TcWorkspace* ws, const MlpConfi
     if (a.count == 0) return cudaSuccess;
     const int nl = c.n_layers;
     CUtensorMap mx;
-    const CUtensorMapDataType dt = c.dtype == MLP_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const int op = c.operand_dtype ? c.operand_dtype : c.dtype;
+    const CUtensorMapDataType dt = op == MLP_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     if (!make_tile_map(ws, &mx, dt, 2, a.inputs, a.count, (uint32_t)c.dims[0], 64, wide::NS, CU_TENSOR_MAP_SWIZZLE_128B, err)) return cudaErrorInvalidValue;
     WideTrainParams p;
     for (int l = 0; l <= wide::kMaxLayers; ++l) p.dims[l] = l <= nl ? c.dims[l] : 0;
     p.hidden_act = c.hidden_act;
     p.param_layout = c.param_layout;
+    p.storage_dtype = c.dtype;
     p.t_direct = 1;
     p.target_dtype = c.target_dtype;
     p.targets = nullptr;
@@ -1090,7 +1112,7 @@ cudaError_t launch_forward_wide(cudaStream_t st, TcWorkspace* ws, const MlpConfi
     p.loss_scale = 1.0f;
     p.act_alpha = c.act_alpha;
     p.timing = nullptr;
-    const cudaError_t e = c.dtype == MLP_BF16 ? launch_wide_fmt<MLP_BF16, true>(st, ws, c, mx, mx, p)
+    const cudaError_t e = op == MLP_BF16 ? launch_wide_fmt<MLP_BF16, true>(st, ws, c, mx, mx, p)
                                               : launch_wide_fmt<MLP_F16, true>(st, ws, c, mx, mx, p);
     *launches += 1;
     return e;

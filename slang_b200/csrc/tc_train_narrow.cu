@@ -164,14 +164,20 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
     // Padded weights (zero outside [out][in]), biases, and the ones column.
     for (int l = 0; l < NL; ++l) {
         const int in = c.dims[l], out = c.dims[l + 1];
+        // 16-bit storage: the stored bits; fp32 storage with 16-bit operands (MlpConfig.operand_dtype): converted here
         const uint16_t* W = (const uint16_t*)p.net[l].weights;
+        const float* W32 = (const float*)p.net[l].weights;
         for (int idx = threadIdx.x; idx < H * H; idx += kThreads) {
             const int o = idx / H, i = idx % H;
-            const uint16_t v = (o < out && i < in) ? W[weight_index(c.param_layout, in, out, o, i)] : (uint16_t)0;
+            uint16_t v = 0;
+            if (o < out && i < in) {
+                const int64_t wi = weight_index(c.param_layout, in, out, o, i);
+                v = c.dtype == MLP_F32 ? (uint16_t)(C::pack2(W32[wi], 0.0f) & 0xffffu) : W[wi];
+            }
             *(uint16_t*)(smem + M::kW + l * kMat + chunk_offset<H>(H, o, i / 8) + (i % 8) * 2) = v;
         }
         for (int j = threadIdx.x; j < H; j += kThreads)
-            s_bias[l * H + j] = j < out ? load_as_f32(FMT, (const void*)p.net[l].biases, j) : 0.0f;
+            s_bias[l * H + j] = j < out ? load_as_f32(c.dtype, (const void*)p.net[l].biases, j) : 0.0f;
     }
     for (int idx = threadIdx.x; idx < 128 * 16; idx += kThreads) {
         const int r = idx / 16, i = idx % 16;
@@ -317,6 +323,10 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
         float run_max = 0.0f, run_sum = 0.0f;
         uint32_t n_full = 0;
         bool ok = true;
+        // Pre-activations, outputs and input gradients are rounded to the storage type; with fp32 storage (16-bit
+        // operands only) they stay as they are.
+        const bool fp32_storage = c.dtype == MLP_F32;
+        auto round_z = [&](float v) -> float { return fp32_storage ? v : C::round(v); };
         auto release = [&]() {
             tc_fence_before();
             fence_async_smem();
@@ -391,7 +401,7 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
 #pragma unroll
                                 for (int i = 0; i < 16; ++i)
                                     if (c0 + i < od)
-                                        dst[i] = act_value(oact, c.act_alpha, C::round(__uint_as_float(v[i]) + s_bias[l * H + c0 + i]));
+                                        dst[i] = act_value(oact, c.act_alpha, round_z(__uint_as_float(v[i]) + s_bias[l * H + c0 + i]));
                             }
                         }
                         tc_fence_before();
@@ -417,7 +427,7 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
 #pragma unroll
                             for (int e = 0; e < 4; ++e) {
                                 const int j = c0 + k + e;
-                                const float z = C::round(__uint_as_float(v[k + e]) + bb[e]);
+                                const float z = round_z(__uint_as_float(v[k + e]) + bb[e]);
                                 if (!last) {
                                     if constexpr (DFA) {
                                         // max(z, 0), with z == 0 stored as a negative zero: the backward epilogue
@@ -519,7 +529,7 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
                             float* dst = p.input_grads + sample * (uint64_t)in0 + c0;
 #pragma unroll
                             for (int i = 0; i < 16; ++i)
-                                if (c0 + i < in0) dst[i] = C::round(__uint_as_float(v[i]));
+                                if (c0 + i < in0) dst[i] = round_z(__uint_as_float(v[i]));
                         }
                     }
                     release();
@@ -585,7 +595,8 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
 bool tc_train_narrow_supported(const MlpConfig& c)
 {
     if (c.n_layers < 2 || c.n_layers > 5) return false;
-    if (c.dtype != MLP_BF16 && c.dtype != MLP_F16) return false;
+    const int op = c.operand_dtype ? c.operand_dtype : c.dtype;  // fp32 storage runs here with 16-bit operands
+    if (op != MLP_BF16 && op != MLP_F16) return false;
     for (int l = 0; l <= c.n_layers; ++l)
         if (c.dims[l] > narrow::HMAX) return false;
     if (c.encoding == MLP_ENC_FREQ2D && c.dims[0] != 32) return false;
@@ -709,8 +720,11 @@ cudaError_t launch_narrow_generic_c(cudaStream_t st, TcWorkspace* ws, const MlpC
 cudaError_t launch_narrow_generic_d(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const narrow::Params& p);
 
 // Picks the build of the kernel for the shape: padded width, tiles in flight, column split, activations.
-static cudaError_t launch_narrow_any(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const narrow::Params& p)
+// The builds are keyed by the operand format; the kernel itself reads the storage type from its parameters.
+static cudaError_t launch_narrow_any(cudaStream_t st, TcWorkspace* ws, const MlpConfig& real, const narrow::Params& p)
 {
+    MlpConfig c = real;
+    if (c.operand_dtype) c.dtype = c.operand_dtype;
     bool fits32 = c.dims[c.n_layers] <= 16;
     for (int l = 0; l <= c.n_layers; ++l) fits32 = fits32 && c.dims[l] <= 32;
     if (fits32) return launch_narrow_fits32(st, ws, c, p);

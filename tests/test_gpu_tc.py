@@ -264,3 +264,47 @@ def test_wide_kernel_other_shapes(device, dims, dtype, act, tdtype):
     y_ref = oracle.forward(cfg, p0, x, count)
     step = 2.0 ** -7 if dtype == C.BF16 else 2.0 ** -10
     assert np.max(np.abs(y - y_ref)) <= 4 * step * max(1.0, float(np.max(np.abs(y_ref))))
+
+
+@pytest.mark.parametrize("dims,op,act", [
+    ([16, 64, 64, 8], C.F16, C.ACT_RELU),                 # padded 64-wide kernel
+    ([4, 32, 32, 32, 4], C.BF16, C.ACT_LEAKY_RELU),       # its 32-wide build
+    ([64, 128, 128, 64], C.BF16, C.ACT_GELU_TANH),        # wide kernel (16-bit inputs)
+    ([32, 96, 128, 10], C.F16, C.ACT_TANH),               # wide kernel, run-time activation, targets read directly
+])
+def test_fp32_storage_with_16bit_operands(device, dims, op, act):
+    """fp32 parameters, gradients and optimiser with 16-bit tensor-core operands (MlpConfig.operand_dtype): the
+    neural module's T = float on its tensor-core path converts both matrix operands to half
+    (source/standard-modules/neural/mma-tiled-cuda.slang:104-118, WaveMatrix.slang:62-64).  Gradients per
+    tensor within 1e-2 of the oracle in the same mode, loss within 1e-2; the one-thread-per-sample kernel in
+    the same mode agrees with the oracle to fp32 rounding; two Adam steps keep the parameters fp32."""
+    rng = np.random.default_rng(sum(dims) + op)
+    wide = max(dims) > 64
+    in_dt = op if wide else C.F32
+    cfg = C.make_config(dims, dtype=C.F32, hidden_act=act, act_alpha=0.03, input_dtype=in_dt, target_dtype=C.F32,
+                        operand_dtype=op, lr=1e-3)
+    p0 = C.init_params(cfg, seed=9, scheme="xavier")
+    assert p0.dtype == np.float32
+    w_off, b_off, _ = C.param_layout(cfg)
+    for l in range(cfg.n_layers):
+        p0[b_off[l]:b_off[l] + dims[l + 1]] = rng.uniform(-0.2, 0.2, dims[l + 1])
+    count = 128 * 5 + 37
+    batches = []
+    for _ in range(2):
+        x = C.to_storage(rng.uniform(-1, 1, (count, dims[0])).astype(np.float32), in_dt)
+        t = rng.uniform(-1, 1, (count, dims[-1])).astype(np.float32)
+        batches.append((x, t))
+    p_ref, l_ref, g_ref, _ = oracle_trajectory(cfg, p0, batches, n_threads=4)
+    p_gpu, l_gpu, g_gpu, _, tr = gpu_trajectory(device, cfg, p0, batches)
+    assert tr.k_learn.implementation == "tcgen05" and tr.k_forward.implementation == "tcgen05"
+    err = _grad_layer_errs(cfg, g_gpu, g_ref)
+    print(dims, "fp32 storage, 16-bit operands: worst per-tensor gradient rel err %.3g" % err)
+    assert err < 1e-2
+    for (mg, sg), (mr, sr) in zip(l_gpu, l_ref):
+        assert abs(sg - sr) <= 1e-2 * abs(sr) and abs(mg - mr) <= 1e-2 * abs(mr)
+    assert p_gpu.dtype == np.float32 and max(per_layer_rel_errs(cfg, p_gpu, p_ref)) < 2e-2
+    _, l_simt, g_simt, _, _ = gpu_trajectory(device, cfg, p0, batches[:1], "learnGradient_simt")
+    assert _grad_layer_errs(cfg, g_simt, g_ref) < 1e-4
+    # without the operand switch the same fp32 network stays on the exact one-thread-per-sample path
+    cfg32 = C.make_config(dims, dtype=C.F32, hidden_act=act, act_alpha=0.03, input_dtype=C.F32, target_dtype=C.F32)
+    assert device.kernel("learnGradient", cfg32).implementation == "simt"
