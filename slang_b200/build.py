@@ -41,6 +41,7 @@ UNITS = [
     ("matrix_convert", "matrix_convert.cu", []),
     ("permuto", "permuto.cu", ["-fmad=false"]),
     ("selftest", "selftest.cu", []),
+    ("tile_mma", "tile_mma.cu", []),
 ] + [("tc_train_narrow_%d" % i, "tc_train_narrow.cu", ["-DMLPB200_NARROW_PART=%d" % i]) for i in range(8)]
 
 

@@ -18,7 +18,7 @@ EXPORTS = [
     "mlp_buffer_read", "mlp_buffer_write",
     "mlp_kernel_get", "mlp_kernel_load", "mlp_kernel_get_for_config", "mlp_kernel_destroy", "mlp_kernel_implementation",
     "mlp_dispatch", "mlp_device_launch_count", "mlp_param_layout", "mlp_last_error_string",
-    "mlp_learn_gradient_ordered_noalloc", "mlp_selftest_bounded_wait",
+    "mlp_learn_gradient_ordered_noalloc", "mlp_selftest_bounded_wait", "mlp_tile_mma",
     "mlp_layout_sizes", "mlp_layout_to_optimal", "mlp_layout_to_portable",
     "mlp_matrix_size", "mlp_matrix_convert",
     "mlp_permuto_prepare", "mlp_grid_hash", "mlp_permuto_encode", "mlp_permuto_backward",
@@ -87,6 +87,7 @@ def load():
     L.mlp_layout_to_optimal.argtypes = [vp, vp, u64, u64]
     L.mlp_layout_to_portable.argtypes = [vp, vp, u64, u64]
     L.mlp_selftest_bounded_wait.argtypes = [vp, u32]
+    L.mlp_tile_mma.argtypes = [vp, vp, u64, u64, u64, u64]
     L.mlp_learn_gradient_ordered_noalloc.argtypes = [i32, vp, ctypes.POINTER(MlpConfig), vp]
     for name in EXPORTS:
         fn = getattr(L, name)
