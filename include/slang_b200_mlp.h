@@ -95,7 +95,7 @@ typedef struct MlpForwardParams {
 /* forward: write the outputs rounded to the network's storage type (tensor-core path only). */
 #define MLP_FLAG_OUTPUT_STORAGE_TYPE 2u
 /* learnGradient with MlpLearnGradParamsEx2: also write the input gradients (networks without an input
- * encoding; on the tensor cores for 16-bit networks of widths up to 64, else one thread per sample). */
+ * encoding; on the tensor cores wherever learnGradient itself runs there, else one thread per sample). */
 #define MLP_FLAG_INPUT_GRADIENT 4u
 
 /* ---- device ------------------------------------------------------------------------------- */

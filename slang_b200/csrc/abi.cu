@@ -427,11 +427,9 @@ int32_t mlp_dispatch(MlpDevice* d, MlpKernel* k, const void* args, size_t args_s
         if ((uint64_t)gx * 256 < a.count) return fail(MLP_E_INVALID_ARG, "grid of %u groups does not cover %u samples", gx, a.count);
         if (!a.networkBuffer || !a.lossBuffer || (a.count && (!a.inputs || !a.targets))) return fail(MLP_E_INVALID_ARG, "null device address in the argument struct");
         const bool seq = (a.flags & MLP_FLAG_SEQUENTIAL_SUM) != 0;
-        if (k->entry == Entry::Learn && !seq && !input_grads) {
-            e = launch_learn_gradient_tc(d->stream, d->tc, k->cfg, a, &launches, &err);
-        } else if (k->entry == Entry::Learn && !seq && tc_train_narrow_supported(k->cfg)) {
-            // input gradients on the tensor cores: the padded kernel for widths up to 64 writes them
-            e = launch_learn_gradient_narrow(d->stream, d->tc, k->cfg, a, &launches, &err, input_grads);
+        if (k->entry == Entry::Learn && !seq) {
+            // both tensor-core kernels also write the input gradients when asked
+            e = launch_learn_gradient_tc(d->stream, d->tc, k->cfg, a, &launches, &err, input_grads);
         } else {
             if (seq) {
                 const size_t need = sequential_scratch_floats_per_sample(k->cfg) * size_t(a.count);

@@ -41,8 +41,10 @@ TcWorkspace* tc_workspace_create(int device_ordinal, std::string* err);
 void tc_workspace_destroy(TcWorkspace* ws);
 cudaError_t launch_forward_tc(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const MlpForwardParams& a,
                               int* launches, std::string* err);
+// input_grads (optional): [count][dims[0]] fp32 gradient with respect to the inputs (no input encoding).
 cudaError_t launch_learn_gradient_tc(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c,
-                                     const MlpLearnGradParamsEx& a, int* launches, std::string* err);
+                                     const MlpLearnGradParamsEx& a, int* launches, std::string* err,
+                                     float* input_grads = nullptr);
 // Forward pass of the wide (zero-padded 64-128-...-64) kernel's shapes; fp32 outputs.
 bool tc_forward_wide_supported(const MlpConfig& c);
 cudaError_t launch_forward_wide(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const MlpForwardParams& a,

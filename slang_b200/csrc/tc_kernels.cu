@@ -199,6 +199,7 @@ struct WideTrainParams {
     uint32_t n_tiles;
     float loss_scale;  // 1 / outputs for the mean-squared error, 1 for the sum of squares
     float act_alpha;
+    float* input_grads;          // optional (training): fp32 [count][dims[0]] gradient with respect to the inputs
     unsigned long long* timing;  // trace builds only: time stamps written by CTA 0
 };
 
@@ -508,6 +509,26 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                     if (has_next) ++loads_issued;
                     __syncwarp();
                 }
+                // ---- optional: the input gradient dA_0^T [inputs x samples] = W_0^T . dZ_0^T of both chains, once
+                //      dW_0 has left the accumulator.  W_0 holds 64 input columns; the instruction's upper 64 lanes
+                //      read the rows of the next weight buffer and are never looked at ----
+                if (p.input_grads) {
+#pragma unroll
+                    for (int h = 0; h < NCH; ++h) chain_wait(h);
+                    if (ok && leader) {
+#pragma unroll
+                        for (int h = 0; h < NCH; ++h) {
+                            const uint32_t half = (uint32_t)h * (uint32_t)(CH * 2);
+#pragma unroll
+                            for (int k = 0; k < H / 16; ++k)
+                                umma_f16(tmem_base + kColAcc + (uint32_t)(h * CH), desc_mn(kW0, 16384u, k), desc_mn(kA1 + half, 8192u, k),
+                                         kIdescDx, k > 0);
+                        }
+#pragma unroll
+                        for (int h = 0; h < NCH; ++h) umma_commit(&acc_full[h]);
+                    }
+                    __syncwarp();
+                }
             }
             if (*abort_flag && leader) {
                 // Give the copies still in flight a bounded time to land before the CTA exits.
@@ -808,6 +829,34 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                 }
                 MLPB200_TRACE_AT(tr_on, 64u + tr_step * 4 + 3);
             }
+            // ---- optional: the input gradients of this tile, input feature on the lane (quarters 0 and 1), sample
+            //      on the column; a warp writes 32 consecutive features of one sample per store ----
+            if (p.input_grads) {
+                wait_acc(0);
+                wait_acc(1);
+                if (!ok) break;
+                tc_fence_after();
+                if (q < 2) {
+                    uint32_t v[16];
+                    tmem_ld_cols(lane_base + kColAcc + (uint32_t)(e * 16), v);
+                    tmem_ld_wait();
+                    const int in0 = p.dims[0];
+                    if (f < in0) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const size_t sample = (size_t)tile * NS + (size_t)(e * 16 + i);
+                            const float g = __uint_as_float(v[i]);
+                            if (sample < p.count) p.input_grads[sample * (size_t)in0 + f] = fp32_storage ? g : E::unpack_lo(E::pack2(g, 0.0f));
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&acc_free[0]);
+                    mbar_arrive(&acc_free[1]);
+                }
+            }
         }
 
         // ---- one add per parameter per CTA ----
@@ -1044,9 +1093,9 @@ static cudaError_t launch_wide_fmt(cudaStream_t st, TcWorkspace* ws, const MlpCo
 
 #if MLPB200_WIDE_PART == 0
 cudaError_t launch_learn_gradient_tc(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const MlpLearnGradParamsEx& a,
-                                     int* launches, std::string* err)
+                                     int* launches, std::string* err, float* input_grads)
 {
-    if (!wide_supported(c)) return launch_learn_gradient_narrow(st, ws, c, a, launches, err);
+    if (!wide_supported(c)) return launch_learn_gradient_narrow(st, ws, c, a, launches, err, input_grads);
     if (a.count == 0) return cudaSuccess;
     const int nl = c.n_layers;
     const int d0 = c.dims[0], dout = c.dims[nl];
@@ -1076,6 +1125,7 @@ cudaError_t launch_learn_gradient_tc(cudaStream_t st, TcWorkspace* ws, const Mlp
     p.act_alpha = c.act_alpha;
     p.timing = ws->timing;
     p.outputs = nullptr;
+    p.input_grads = input_grads;
     const cudaError_t e = op == MLP_BF16 ? launch_wide_fmt<MLP_BF16, false>(st, ws, c, mx, mt, p)
                                               : launch_wide_fmt<MLP_F16, false>(st, ws, c, mx, mt, p);
     *launches += 1;
@@ -1112,6 +1162,7 @@ cudaError_t launch_forward_wide(cudaStream_t st, TcWorkspace* ws, const MlpConfi
     p.loss_scale = 1.0f;
     p.act_alpha = c.act_alpha;
     p.timing = nullptr;
+    p.input_grads = nullptr;
     const cudaError_t e = op == MLP_BF16 ? launch_wide_fmt<MLP_BF16, true>(st, ws, c, mx, mx, p)
                                               : launch_wide_fmt<MLP_F16, true>(st, ws, c, mx, mx, p);
     *launches += 1;

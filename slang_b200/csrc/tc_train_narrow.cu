@@ -60,7 +60,20 @@ struct Params {
     float* outputs;       // optional: forward only; fp32 [count][dims[n_layers]] network outputs, nothing else is written
     uint32_t count;
     uint32_t n_tiles;
+#ifdef MLPB200_TRACE
+    unsigned long long* timing;   // developer builds only: time stamps of one round of CTA 0
+#endif
 };
+
+// Developer builds (-DMLPB200_TRACE, never the shipped library) record clock64() stamps of the hand-offs of
+// one round of CTA 0: control warp slot (step * NCH + chain) * 3 + {wait begins, wait ends, products issued},
+// epilogue (first thread of each chain) slot 128 + (chain * 11 + step) * 2 + {woken, released}.
+#ifdef MLPB200_TRACE
+#define MLPB200_NTRACE(cond, slot) do { if (cond) p.timing[slot] = (unsigned long long)clock64(); } while (0)
+constexpr uint32_t kTraceRound = 3;
+#else
+#define MLPB200_NTRACE(cond, slot) do { } while (0)
+#endif
 
 template <int FMT> struct Cvt;
 template <> struct Cvt<MLP_BF16> {
@@ -74,6 +87,24 @@ template <> struct Cvt<MLP_BF16> {
     __device__ static __forceinline__ float lo(uint32_t p) { return __uint_as_float(p << 16); }
     __device__ static __forceinline__ float hi(uint32_t p) { return __uint_as_float(p & 0xffff0000u); }
     __device__ static __forceinline__ uint16_t one() { return 0x3F80; }
+    // max(z, 0) of a pair; a zero z (either sign) comes out as a negative zero
+    __device__ static __forceinline__ uint32_t relu_marked(uint32_t z2)
+    {
+        const __nv_bfloat162 z = *reinterpret_cast<const __nv_bfloat162*>(&z2), zero = __floats2bfloat162_rn(0.0f, 0.0f);
+        const __nv_bfloat162 r = __hmax2(z, zero);
+        return (*reinterpret_cast<const uint32_t*>(&r) & 0x7fff7fffu) | (__heq2_mask(z, zero) & 0x80008000u);
+    }
+    // 0xffff in the halves whose value is above zero
+    __device__ static __forceinline__ uint32_t positive_mask(uint32_t a2)
+    {
+        return __hgt2_mask(*reinterpret_cast<const __nv_bfloat162*>(&a2), __floats2bfloat162_rn(0.0f, 0.0f));
+    }
+    // z < 0 ? round(alpha z) : z of a pair; the sign bit of the result is set exactly where z < 0
+    __device__ static __forceinline__ uint32_t leaky_signed(uint32_t z2, float alpha)
+    {
+        const uint32_t m = __hlt2_mask(*reinterpret_cast<const __nv_bfloat162*>(&z2), __floats2bfloat162_rn(0.0f, 0.0f));
+        return (pack2(__fmul_rn(alpha, lo(z2)), __fmul_rn(alpha, hi(z2))) & m) | (z2 & 0x7fff7fffu & ~m);
+    }
 };
 template <> struct Cvt<MLP_F16> {
     static constexpr uint32_t kUmmaFmt = 0;
@@ -86,6 +117,21 @@ template <> struct Cvt<MLP_F16> {
     __device__ static __forceinline__ float lo(uint32_t p) { return __half2float(__ushort_as_half((uint16_t)(p & 0xffffu))); }
     __device__ static __forceinline__ float hi(uint32_t p) { return __half2float(__ushort_as_half((uint16_t)(p >> 16))); }
     __device__ static __forceinline__ uint16_t one() { return 0x3C00; }
+    __device__ static __forceinline__ uint32_t relu_marked(uint32_t z2)
+    {
+        const __half2 z = *reinterpret_cast<const __half2*>(&z2), zero = __floats2half2_rn(0.0f, 0.0f);
+        const __half2 r = __hmax2(z, zero);
+        return (*reinterpret_cast<const uint32_t*>(&r) & 0x7fff7fffu) | (__heq2_mask(z, zero) & 0x80008000u);
+    }
+    __device__ static __forceinline__ uint32_t positive_mask(uint32_t a2)
+    {
+        return __hgt2_mask(*reinterpret_cast<const __half2*>(&a2), __floats2half2_rn(0.0f, 0.0f));
+    }
+    __device__ static __forceinline__ uint32_t leaky_signed(uint32_t z2, float alpha)
+    {
+        const uint32_t m = __hlt2_mask(*reinterpret_cast<const __half2*>(&z2), __floats2half2_rn(0.0f, 0.0f));
+        return (pack2(__fmul_rn(alpha, lo(z2)), __fmul_rn(alpha, hi(z2))) & m) | (z2 & 0x7fff7fffu & ~m);
+    }
 };
 
 // Shared-memory map for NL layers and NCH tiles in flight (bytes from a 1024-aligned base).  DFA: the
@@ -132,7 +178,8 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
     constexpr int GW = H / CS;   // columns per epilogue group
     static_assert(H == 64 || H == 32, "padded width");
     static_assert(GW % 16 == 0, "an epilogue group works on whole 16-column accumulator reads");
-    static_assert(!DFA || HACT == MLP_ACT_RELU, "the derivative is recovered from the activation only for ReLU");
+    static_assert(!DFA || HACT == MLP_ACT_RELU || HACT == MLP_ACT_LEAKY_RELU,
+                  "the derivative is recovered from the activation only for ReLU and leaky ReLU");
     using M = Map<NL, NCH, DFA, H>;
     using C = Cvt<FMT>;
     constexpr uint32_t kMat = M::kMat, kTile = M::kTile;
@@ -221,10 +268,16 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
 #pragma unroll
             for (int h = 0; h < NCH; ++h) n_free[h] = 0;
             bool ok = true;
+#ifdef MLPB200_TRACE
+            bool tr_on = false;
+            int tr_step = 0;
+#endif
             auto wait_free = [&](int h) {
+                MLPB200_NTRACE(tr_on, (tr_step * NCH + h) * 3 + 0);
                 ok = ok && mbar_wait(&bars[3 * h + 1], n_free[h] & 1u, abort_flag, p.status, kStatusCtrl);
                 ++n_free[h];
                 tc_fence_after();
+                MLPB200_NTRACE(tr_on, (tr_step * NCH + h) * 3 + 1);
             };
             // dW_l and db_l of a tile; `first` is true only for the launch's first product into them.
             auto grads = [&](int l, uint32_t dzbuf, uint32_t abuf, bool first) {
@@ -237,9 +290,15 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
             };
             const uint32_t rounds = (n_my_tiles + NCH - 1) / NCH;
             for (uint32_t rd = 0; rd < rounds && ok; ++rd) {
+#ifdef MLPB200_TRACE
+                tr_on = leader && blockIdx.x == 0 && rd == kTraceRound && p.timing;
+#endif
                 // ---- forward ----
 #pragma unroll
                 for (int l = 0; l < NL; ++l) {
+#ifdef MLPB200_TRACE
+                    tr_step = l;
+#endif
 #pragma unroll
                     for (int h = 0; h < NCH; ++h) {
                         if (rd * NCH + h >= n_my_tiles) continue;
@@ -252,6 +311,7 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
                                     umma_f16(tmem_base + M::kColAcc + (uint32_t)(h * H), desc_k(cb + M::kA + (uint32_t)l * kTile, k),
                                              desc_k(M::kW + (uint32_t)l * kMat, k), kIdFwd, k > 0);
                                 umma_commit(&bars[3 * h + 0]);
+                                MLPB200_NTRACE(tr_on, (tr_step * NCH + h) * 3 + 2);
                             }
                             __syncwarp();
                         }
@@ -261,6 +321,9 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
                 // ---- backward ----
 #pragma unroll
                 for (int l = NL - 1; l >= 1; --l) {
+#ifdef MLPB200_TRACE
+                    tr_step = NL + (NL - 1 - l);
+#endif
 #pragma unroll
                     for (int h = 0; h < NCH; ++h) {
                         if (rd * NCH + h >= n_my_tiles) continue;
@@ -275,11 +338,15 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
                                              kIdDx, k > 0);
                                 grads(l, dzbuf, cb + M::kA + (uint32_t)l * kTile, rd == 0 && h == 0);
                                 umma_commit(&bars[3 * h + 0]);
+                                MLPB200_NTRACE(tr_on, (tr_step * NCH + h) * 3 + 2);
                             }
                             __syncwarp();
                         }
                     }
                 }
+#ifdef MLPB200_TRACE
+                tr_step = 2 * NL - 1;
+#endif
 #pragma unroll
                 for (int h = 0; h < NCH; ++h) {
                     if (rd * NCH + h >= n_my_tiles) continue;
@@ -297,6 +364,7 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
                             grads(0, dz0, cb + M::kA, rd == 0 && h == 0);
                             if (p.input_grads) umma_commit(&bars[3 * h + 0]);
                             umma_commit(&bars[3 * h + 2]);
+                            MLPB200_NTRACE(tr_on, (tr_step * NCH + h) * 3 + 2);
                         }
                         __syncwarp();
                         if (p.input_grads) wait_free(h);  // the epilogue has read dA_0 out of the accumulator
@@ -327,16 +395,26 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
         // operands only) they stay as they are.
         const bool fp32_storage = c.dtype == MLP_F32;
         auto round_z = [&](float v) -> float { return fp32_storage ? v : C::round(v); };
+        const float alpha_op = C::round(c.act_alpha);
+#ifdef MLPB200_TRACE
+        bool tr_on = false;
+        int tr_step = 0;
+#endif
         auto release = [&]() {
             tc_fence_before();
             fence_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_free);
+            MLPB200_NTRACE(tr_on, 128 + (h * 11 + tr_step) * 2 + 1);
+#ifdef MLPB200_TRACE
+            ++tr_step;
+#endif
         };
         auto wait_full = [&]() {
             ok = ok && mbar_wait(acc_full, n_full & 1u, abort_flag, p.status, kStatusEpi);
             ++n_full;
             tc_fence_after();
+            MLPB200_NTRACE(tr_on, 128 + (h * 11 + tr_step) * 2 + 0);
         };
         auto row_chunk = [&](uint32_t buf, int j) -> uint4* { return (uint4*)(smem + cb + buf + chunk_offset<H>(128, r, j)); };
         const uint32_t n_chain_tiles = n_my_tiles > (uint32_t)h ? (n_my_tiles - (uint32_t)h + NCH - 1) / NCH : 0;
@@ -345,14 +423,24 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
             const uint64_t tile = (uint64_t)blockIdx.x + ((uint64_t)it * NCH + (uint64_t)h) * gridDim.x;
             const uint64_t sample = tile * TS + (uint64_t)r;
             const bool valid = sample < p.count;
+#ifdef MLPB200_TRACE
+            tr_on = blockIdx.x == 0 && it == kTraceRound && p.timing && r == 0 && g == 0;
+            tr_step = 0;
+            MLPB200_NTRACE(tr_on, 128 + (h * 11) * 2 + 0);
+#endif
             // ---- the input row: conversion (and zero padding) or the frequency encoding ----
-            // training: dW_0 of the chain's previous tile still reads A_0 until tile_done; forward only: the
-            // layer-0 product that read it has long completed (its accumulator was consumed)
-            if (it > 0 && !p.outputs) ok = ok && mbar_wait(tile_done, (it - 1) & 1u, abort_flag, p.status, kStatusEpi);
-            if (!ok) break;
+            // training: dW_0 of the chain's previous tile still reads A_0 until tile_done, so the row is stored
+            // after that wait; forward only: the layer-0 product that read it has long completed (its
+            // accumulator was consumed)
             {
+                // Blocks of 16 columns are dealt to the column groups in turn, so the groups share the real input
+                // columns (and the two coordinates of the frequency encoding) whatever the padding.  The row is
+                // built in registers first: the loads and the sines overlap the wait below.
+                constexpr int kBlocks = GW / 16;
+                uint4 xa[kBlocks], xb[kBlocks];
 #pragma unroll
-                for (int c0 = cbeg; c0 < cend; c0 += 16) {
+                for (int b = 0; b < kBlocks; ++b) {
+                    const int c0 = 16 * (g + CS * b);
                     float x[16];
 #pragma unroll
                     for (int i = 0; i < 16; ++i) x[i] = 0.0f;
@@ -367,14 +455,22 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
                                     sincosf(arg, &x[k * 2 + 0], &x[k * 2 + 1]);
                                 }
                             }
-                        } else {
+                        } else if (c0 < c.dims[0]) {
 #pragma unroll
                             for (int i = 0; i < 16; ++i)
                                 if (c0 + i < c.dims[0]) x[i] = load_as_f32(c.input_dtype, p.inputs, sample * c.dims[0] + c0 + i);
                         }
                     }
-                    *row_chunk(M::kA, c0 / 8) = make_uint4(C::pack2(x[0], x[1]), C::pack2(x[2], x[3]), C::pack2(x[4], x[5]), C::pack2(x[6], x[7]));
-                    *row_chunk(M::kA, c0 / 8 + 1) = make_uint4(C::pack2(x[8], x[9]), C::pack2(x[10], x[11]), C::pack2(x[12], x[13]), C::pack2(x[14], x[15]));
+                    xa[b] = make_uint4(C::pack2(x[0], x[1]), C::pack2(x[2], x[3]), C::pack2(x[4], x[5]), C::pack2(x[6], x[7]));
+                    xb[b] = make_uint4(C::pack2(x[8], x[9]), C::pack2(x[10], x[11]), C::pack2(x[12], x[13]), C::pack2(x[14], x[15]));
+                }
+                if (it > 0 && !p.outputs) ok = ok && mbar_wait(tile_done, (it - 1) & 1u, abort_flag, p.status, kStatusEpi);
+                if (!ok) break;
+#pragma unroll
+                for (int b = 0; b < kBlocks; ++b) {
+                    const int c0 = 16 * (g + CS * b);
+                    *row_chunk(M::kA, c0 / 8) = xa[b];
+                    *row_chunk(M::kA, c0 / 8 + 1) = xb[b];
                 }
                 release();
             }
@@ -419,6 +515,28 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
                         tmem_ld_32x16(t_acc + (uint32_t)c0, v);
                         tmem_ld_wait();
                         uint32_t pa[8], pd[8];
+                        if constexpr (DFA) {
+                            if (!last && !fp32_storage) {
+                                // ReLU and leaky ReLU on pairs: bias, one paired rounding of the pre-activations,
+                                // the activation on the packed pair with the derivative's case kept in the sign bit
+#pragma unroll
+                                for (int k = 0; k < 16; k += 4) {
+                                    const float4 b4 = *(const float4*)(s_bias + l * H + c0 + k);
+                                    const uint32_t z01 = C::pack2(__uint_as_float(v[k]) + b4.x, __uint_as_float(v[k + 1]) + b4.y);
+                                    const uint32_t z23 = C::pack2(__uint_as_float(v[k + 2]) + b4.z, __uint_as_float(v[k + 3]) + b4.w);
+                                    if constexpr (HACT == MLP_ACT_RELU) {
+                                        pa[k >> 1] = C::relu_marked(z01);
+                                        pa[(k >> 1) + 1] = C::relu_marked(z23);
+                                    } else {
+                                        pa[k >> 1] = C::leaky_signed(z01, c.act_alpha);
+                                        pa[(k >> 1) + 1] = C::leaky_signed(z23, c.act_alpha);
+                                    }
+                                }
+                                *row_chunk(abuf, c0 / 8) = make_uint4(pa[0], pa[1], pa[2], pa[3]);
+                                *row_chunk(abuf, c0 / 8 + 1) = make_uint4(pa[4], pa[5], pa[6], pa[7]);
+                                continue;
+                            }
+                        }
 #pragma unroll
                         for (int k = 0; k < 16; k += 4) {
                             const float4 b4 = *(const float4*)(s_bias + l * H + c0 + k);
@@ -429,10 +547,15 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
                                 const int j = c0 + k + e;
                                 const float z = round_z(__uint_as_float(v[k + e]) + bb[e]);
                                 if (!last) {
-                                    if constexpr (DFA) {
+                                    if constexpr (DFA && HACT == MLP_ACT_RELU) {
                                         // max(z, 0), with z == 0 stored as a negative zero: the backward epilogue
                                         // tells "below zero", "zero" and "above zero" apart by the stored bits
                                         a4[e] = z > 0.0f ? z : (z == 0.0f ? -0.0f : 0.0f);
+                                        d4[e] = 0.0f;
+                                    } else if constexpr (DFA) {
+                                        // leaky ReLU: the sign bit of the stored value is "z < 0" (alpha z keeps its
+                                        // sign when it rounds to zero; a zero z is stored as a positive zero)
+                                        a4[e] = z < 0.0f ? __fmul_rn(c.act_alpha, z) : (z == 0.0f ? 0.0f : z);
                                         d4[e] = 0.0f;
                                     } else {
                                         a4[e] = act_value(hact, c.act_alpha, z);
@@ -473,6 +596,17 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
                 }
             }
             if (p.outputs) continue;   // forward only
+            // the chain's next tile: start its input and target rows on their way into the L2 cache
+            if (g == 0 && it + 1 < n_chain_tiles) {
+                const uint64_t ns = sample + (uint64_t)NCH * gridDim.x * TS;
+                if (ns < p.count) {
+                    const uint64_t in_w = c.encoding == MLP_ENC_FREQ2D ? 2u : (uint64_t)c.dims[0];
+                    const char* xi = (const char*)p.inputs + ns * in_w * (c.input_dtype == MLP_F32 ? 4u : 2u);
+                    const char* ti = (const char*)p.targets + ns * (uint64_t)od * (c.target_dtype == MLP_F32 ? 4u : 2u);
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(xi));
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(ti));
+                }
+            }
             // ---- backward: dA_l in the accumulator times the derivative gives dZ_{l-1}, written over A_l ----
 #pragma unroll
             for (int l = NL - 1; l >= 1; --l) {
@@ -496,12 +630,31 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
                         uint32_t pz[8];
 #pragma unroll
                         for (int k = 0; k < 8; ++k) {
+                            if constexpr (DFA && HACT == MLP_ACT_RELU) {
+                                // no "z was exactly zero" mark in the pair: the rounded dA where the activation is
+                                // positive, zero elsewhere
+                                if ((dd[k] & 0x80008000u) == 0u) {
+                                    pz[k] = C::pack2(__uint_as_float(v[2 * k]), __uint_as_float(v[2 * k + 1])) & C::positive_mask(dd[k]);
+                                    continue;
+                                }
+                            }
+                            if constexpr (DFA && HACT == MLP_ACT_LEAKY_RELU) {
+                                // alpha dA where the stored sign says z < 0, dA elsewhere, each rounded once
+                                const float g0 = __uint_as_float(v[2 * k]), g1 = __uint_as_float(v[2 * k + 1]);
+                                const uint32_t m = ((dd[k] >> 15) & 0x00010001u) * 0xffffu;
+                                pz[k] = (C::pack2(g0 * alpha_op, g1 * alpha_op) & m) | (C::pack2(g0, g1) & ~m);
+                                continue;
+                            }
                             float dl, dh;
-                            if constexpr (DFA) {
+                            if constexpr (DFA && HACT == MLP_ACT_RELU) {
                                 // stored activation: positive -> 1, negative zero -> one half (z was 0), zero -> 0
                                 const uint32_t lo16 = dd[k] & 0xffffu, hi16 = dd[k] >> 16;
                                 dl = (lo16 & 0x7fffu) ? 1.0f : (lo16 ? 0.5f : 0.0f);
                                 dh = (hi16 & 0x7fffu) ? 1.0f : (hi16 ? 0.5f : 0.0f);
+                            } else if constexpr (DFA) {
+                                // leaky ReLU: sign bit set -> alpha (rounded to the operand type like a stored derivative)
+                                dl = (dd[k] & 0x8000u) ? alpha_op : 1.0f;
+                                dh = (dd[k] & 0x80000000u) ? alpha_op : 1.0f;
                             } else {
                                 dl = C::lo(dd[k]);
                                 dh = C::hi(dd[k]);
@@ -612,7 +765,13 @@ static cudaError_t launch_narrow_cs(cudaStream_t st, TcWorkspace* ws, const narr
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)M::kSmemBytes);
     if (e != cudaSuccess) return e;
     const uint32_t grid = p.n_tiles < (uint32_t)ws->sm_count ? p.n_tiles : (uint32_t)ws->sm_count;
+#ifdef MLPB200_TRACE
+    narrow::Params q = p;
+    q.timing = ws->timing;
+    kern<<<grid, narrow::threads_for(CS * NCH), M::kSmemBytes, st>>>(q);
+#else
     kern<<<grid, narrow::threads_for(CS * NCH), M::kSmemBytes, st>>>(p);
+#endif
     return cudaGetLastError();
 }
 
@@ -645,7 +804,7 @@ cudaError_t launch_narrow_fits32(cudaStream_t st, TcWorkspace* ws, const MlpConf
     cudaError_t e = cudaErrorInvalidValue;
     // the benchmark shape gets its activations as compile-time constants
     if (c.n_layers == 5 && c.dtype == MLP_F16 && c.hidden_act == MLP_ACT_LEAKY_RELU && c.output_act == MLP_ACT_IDENTITY)
-        return launch_narrow_cs<5, MLP_F16, MLP_ACT_LEAKY_RELU, MLP_ACT_IDENTITY, 2, 2, false, 32>(st, ws, p);
+        return launch_narrow_cs<5, MLP_F16, MLP_ACT_LEAKY_RELU, MLP_ACT_IDENTITY, 2, 2, true, 32>(st, ws, p);
 #define MLPB200_NARROW32(NL_) \
     if (c.n_layers == NL_) e = c.dtype == MLP_BF16 ? launch_narrow_cs<NL_, MLP_BF16, -1, -1, 2, 2, false, 32>(st, ws, p) \
                                                    : launch_narrow_cs<NL_, MLP_F16, -1, -1, 2, 2, false, 32>(st, ws, p);

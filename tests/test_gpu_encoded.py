@@ -47,6 +47,38 @@ def test_input_gradients_match_oracle(device, name, count):
         tr.learn_gradient(xb.address, tb.address, count, flags=FLAG_INPUT_GRADIENT)
 
 
+@pytest.mark.parametrize("dims,dtype,act", [([32, 128, 128, 3], C.F16, C.ACT_RELU), ([64, 96, 128, 128, 64], C.BF16, C.ACT_GELU_TANH),
+                                            ([8, 128, 16], C.F16, C.ACT_TANH)])
+def test_input_gradients_from_the_wide_kernel(device, dims, dtype, act):
+    """Networks with a hidden width above 64 and 16-bit inputs: the wide tensor-core kernel writes the input
+    gradients itself (one more product per tile, W_0^T . dZ_0^T), ragged last tile included."""
+    from slang_b200.api import Trainer
+    rng = np.random.default_rng(sum(dims))
+    count = 64 * 7 + 19
+    cfg = C.make_config(dims, dtype=dtype, hidden_act=act, input_dtype=dtype, target_dtype=C.F32, adam_master=1)
+    p0 = C.init_params(cfg, seed=4, scheme="xavier")
+    x = C.to_storage(rng.uniform(-1, 1, (count, dims[0])).astype(np.float32), dtype)
+    t = rng.uniform(-1, 1, (count, dims[-1])).astype(np.float32)
+    _, _, total = C.param_layout(cfg)
+    g_ref = np.zeros(total, dtype=np.float32)
+    words = np.zeros(2, dtype=np.uint32)
+    ig_ref = oracle.learn_gradient_inputs(cfg, p0, g_ref, x, t, count, words)
+    tr = Trainer(device, cfg, p0)
+    assert tr.k_learn.implementation == "tcgen05"
+    xb, tb = device.create_buffer(x.nbytes, x), device.create_buffer(t.nbytes, t)
+    igb = device.create_buffer(count * dims[0] * 4)
+    for _ in range(2):      # twice: the second launch must not see state of the first
+        tr.grads.clear()
+        tr.loss.clear()
+        tr.learn_gradient(xb.address, tb.address, count, input_grads_address=igb.address)
+    device.wait()
+    ig = igb.read(np.float32).reshape(count, dims[0])
+    assert np.isfinite(ig).all() and rel_err(ig, ig_ref) <= 1e-2
+    assert rel_err(tr.read_grads(), g_ref) <= 1e-2
+    mx, sm = tr.read_loss()
+    assert abs(sm - float(words[1:].view(np.float32)[0])) <= 1e-2 * abs(sm)
+
+
 @pytest.mark.parametrize("dtype", [C.F32, C.F16])
 def test_encoder_in_front_of_the_network_trains_like_the_oracle(device, dtype):
     """fp32 network: one thread per sample; fp16 network: the padded tensor-core kernel writes the input
