@@ -205,7 +205,9 @@ struct WideTrainParams {
 
 // FWD builds stop after the output layer and write the network outputs (the "forward" entry point of the same
 // shapes): no targets, no derivatives, no gradient products.
-template <int FMT, int ACT, int NL, bool FWD>
+// F32S: fp32 parameter storage with 16-bit operands (weights converted while they are staged, pre-activations and
+// outputs not rounded); such networks run the builds with the activation chosen at run time.
+template <int FMT, int ACT, int NL, bool FWD, bool F32S = false>
 __global__ void __launch_bounds__(wide::kThreads, 1)
 learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_t,
                            const WideTrainParams p)
@@ -261,7 +263,7 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
         const int inp = in_dim(l), outp = out_dim(l, NL);
         const uint16_t* w16 = (const uint16_t*)p.net[l].weights;
         const float* w32 = (const float*)p.net[l].weights;
-        const bool fp32_storage = p.storage_dtype == MLP_F32;
+        constexpr bool fp32_storage = F32S;
         const int chunks_per_row = inp / 8;  // 16-byte chunks: 8 elements
         const uint32_t panel_stride = (uint32_t)outp * 128u;
         const bool rows_aligned = (in & 7) == 0 && p.param_layout == MLP_PARAMS_ROW_MAJOR && !fp32_storage;
@@ -290,7 +292,7 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
         }
         const int brow = l == NL - 1 ? kMaxLayers - 1 : l;
         for (int j = threadIdx.x; j < 128; j += kThreads)
-            s_bias[brow * 128 + j] = j < out ? load_as_f32(p.storage_dtype, (const void*)p.net[l].biases, j) : 0.0f;
+            s_bias[brow * 128 + j] = j < out ? load_as_f32(F32S ? MLP_F32 : FMT, (const void*)p.net[l].biases, j) : 0.0f;
     }
     fence_async_smem();
     tc_fence_before();
@@ -586,7 +588,7 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
         for (int l = 0; l < NL - 1; ++l) db[l] = 0.0f;
         float run_max = 0.0f, run_sum = 0.0f;  // per-lane (per sample slot) in the two warps that total the losses
         uint32_t n_full0 = 0, n_full1 = 0;     // phases of acc_full[h] this warp has consumed
-        const bool fp32_storage = p.storage_dtype == MLP_F32;  // pre-activations and outputs are not rounded
+        constexpr bool fp32_storage = F32S;  // pre-activations and outputs are not rounded
         bool ok = true;
 #ifdef MLPB200_TRACE
         bool tr_on = false;
@@ -631,7 +633,7 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                             // bias, storage rounding of the pre-activation (one paired conversion), activation
                             const float2 zf = __fadd2_rn(make_float2(__uint_as_float(v[s]), __uint_as_float(v[s + 1])), bias2);
                             float2 z = zf;
-                            if (!fp32_storage) {
+                            if constexpr (!fp32_storage) {
                                 const uint32_t zr = E::pack2(zf.x, zf.y);
                                 z = make_float2(E::unpack_lo(zr), E::unpack_hi(zr));
                             }
@@ -1049,11 +1051,11 @@ bool make_tile_map(TcWorkspace* ws, CUtensorMap* map, CUtensorMapDataType type, 
 
 #endif  // part 0
 
-template <int FMT, int ACT, int NL, bool FWD>
+template <int FMT, int ACT, int NL, bool FWD, bool F32S = false>
 static cudaError_t launch_wide(cudaStream_t st, TcWorkspace* ws, const CUtensorMap& mx, const CUtensorMap& mt,
                                const WideTrainParams& p)
 {
-    auto kern = learn_gradient_wide_kernel<FMT, ACT, NL, FWD>;
+    auto kern = learn_gradient_wide_kernel<FMT, ACT, NL, FWD, F32S>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)wide::kSmemBytes);
     if (e != cudaSuccess) return e;
     const uint32_t grid = p.n_tiles < (uint32_t)ws->sm_count ? p.n_tiles : (uint32_t)ws->sm_count;
@@ -1069,6 +1071,15 @@ static cudaError_t launch_wide_fmt(cudaStream_t st, TcWorkspace* ws, const MlpCo
                                    const CUtensorMap& mt, const WideTrainParams& p)
 {
     const int act = c.hidden_act;
+    if (c.dtype == MLP_F32) {   // fp32 storage, 16-bit operands
+        switch (c.n_layers) {
+        case 5: return launch_wide<FMT, -1, 5, FWD, true>(st, ws, mx, mt, p);
+        case 4: return launch_wide<FMT, -1, 4, FWD, true>(st, ws, mx, mt, p);
+        case 3: return launch_wide<FMT, -1, 3, FWD, true>(st, ws, mx, mt, p);
+        case 2: return launch_wide<FMT, -1, 2, FWD, true>(st, ws, mx, mt, p);
+        }
+        return cudaErrorInvalidValue;
+    }
     switch (c.n_layers) {
     case 5:
         if (act == MLP_ACT_GELU_TANH) return launch_wide<FMT, MLP_ACT_GELU_TANH, 5, FWD>(st, ws, mx, mt, p);
