@@ -19,6 +19,8 @@ struct TcWorkspace {
     uint32_t* status_host = nullptr;       // pinned copy
     unsigned long long* timing = nullptr;  // device; allocated by developer trace builds only
     EncodeTiledFn encode = nullptr;        // cuTensorMapEncodeTiled, fetched through the runtime
+    void* input_rows = nullptr;            // device; 16-bit copy of fp32 input rows for the kernels that take them by TMA
+    size_t input_rows_bytes = 0;
 };
 
 // A [rows][cols] row-major matrix viewed in boxes of box_rows x box_cols elements.

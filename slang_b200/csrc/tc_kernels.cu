@@ -954,6 +954,44 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
 #ifndef MLPB200_WIDE_PART
 #error "compile with -DMLPB200_WIDE_PART=0 or 1"
 #endif
+// fp32 input rows -> the operand type, for networks whose inputs arrive as fp32 (an encoder in front of the
+// network writes fp32 features): the wide kernel takes its input tile by TMA in the operand type, so the rows
+// are rounded once by this launch, exactly as the epilogue-built input rows of the padded kernel are.
+template <int FMT>
+__global__ void convert_input_rows_kernel(const float4* __restrict__ src, uint2* __restrict__ dst, size_t n4)
+{
+    using E = Elem<FMT>;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+        const float4 v = src[i];
+        dst[i] = make_uint2(E::pack2(v.x, v.y), E::pack2(v.z, v.w));
+    }
+}
+
+// The 16-bit copy of `count` fp32 rows of `width` (a multiple of 8) values; the scratch buffer grows on demand.
+static cudaError_t converted_input_rows(cudaStream_t st, TcWorkspace* ws, int op, uint64_t inputs, uint32_t count, int width,
+                                        uint64_t* out_address, int* launches)
+{
+    const size_t n = (size_t)count * (size_t)width;
+    if (n * 2 > ws->input_rows_bytes) {
+        cudaError_t e = cudaStreamSynchronize(st);
+        if (e != cudaSuccess) return e;
+        if (ws->input_rows) cudaFree(ws->input_rows);
+        ws->input_rows = nullptr;
+        ws->input_rows_bytes = 0;
+        e = cudaMalloc(&ws->input_rows, n * 2);
+        if (e != cudaSuccess) return e;
+        ws->input_rows_bytes = n * 2;
+    }
+    if (inputs & 15u) return cudaErrorMisalignedAddress;
+    const size_t n4 = n / 4;
+    const unsigned grid = (unsigned)((n4 + 255) / 256 < (size_t)(ws->sm_count * 16) ? (n4 + 255) / 256 : (size_t)(ws->sm_count * 16));
+    if (op == MLP_BF16) convert_input_rows_kernel<MLP_BF16><<<grid, 256, 0, st>>>((const float4*)inputs, (uint2*)ws->input_rows, n4);
+    else convert_input_rows_kernel<MLP_F16><<<grid, 256, 0, st>>>((const float4*)inputs, (uint2*)ws->input_rows, n4);
+    *out_address = (uint64_t)ws->input_rows;
+    *launches += 1;
+    return cudaGetLastError();
+}
+
 static bool wide_supported(const MlpConfig& c)
 {
     // Two to five layers; inputs and outputs up to 64 wide, hidden layers up to 128; at least one width
@@ -963,7 +1001,7 @@ static bool wide_supported(const MlpConfig& c)
     if (nl < 2 || nl > wide::kMaxLayers) return false;
     const int op = c.operand_dtype ? c.operand_dtype : c.dtype;  // fp32 storage runs here with 16-bit operands
     if (op != MLP_BF16 && op != MLP_F16) return false;
-    if (c.input_dtype != op) return false;
+    if (c.input_dtype != op && c.input_dtype != MLP_F32) return false;  // fp32 rows are converted by a launch in front
     if (c.output_act != MLP_ACT_IDENTITY || c.encoding != MLP_ENC_NONE) return false;
     if (c.dims[0] > wide::D0 || (c.dims[0] & 7) != 0 || c.dims[nl] > wide::DOUT) return false;
     bool any_wide = false;
@@ -1012,6 +1050,7 @@ void tc_workspace_destroy(TcWorkspace* ws)
     if (ws->status) cudaFree(ws->status);
     if (ws->status_host) cudaFreeHost(ws->status_host);
     if (ws->timing) cudaFree(ws->timing);
+    if (ws->input_rows) cudaFree(ws->input_rows);
     delete ws;
 }
 
@@ -1113,8 +1152,13 @@ cudaError_t launch_learn_gradient_tc(cudaStream_t st, TcWorkspace* ws, const Mlp
     CUtensorMap mx, mt;
     const int op = c.operand_dtype ? c.operand_dtype : c.dtype;
     const CUtensorMapDataType dt = op == MLP_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    uint64_t inputs = a.inputs;
+    if (c.input_dtype != op) {
+        const cudaError_t ce = converted_input_rows(st, ws, op, a.inputs, a.count, d0, &inputs, launches);
+        if (ce != cudaSuccess) { if (err) *err = "converting the fp32 input rows failed"; return ce; }
+    }
     // Boxes of 64 rows x 64 columns over [count][width]: columns past the real width arrive as zeros.
-    if (!make_tile_map(ws, &mx, dt, 2, a.inputs, a.count, (uint32_t)d0, 64, wide::NS, CU_TENSOR_MAP_SWIZZLE_128B, err)) return cudaErrorInvalidValue;
+    if (!make_tile_map(ws, &mx, dt, 2, inputs, a.count, (uint32_t)d0, 64, wide::NS, CU_TENSOR_MAP_SWIZZLE_128B, err)) return cudaErrorInvalidValue;
     // Targets come by TMA when their rows are 16-byte multiples in the storage format, else the epilogue reads them.
     const bool t_direct = c.target_dtype != op || (dout & 7) != 0 || (a.targets & 15u) != 0;
     if (t_direct) mt = mx;
@@ -1155,7 +1199,12 @@ cudaError_t launch_forward_wide(cudaStream_t st, TcWorkspace* ws, const MlpConfi
     CUtensorMap mx;
     const int op = c.operand_dtype ? c.operand_dtype : c.dtype;
     const CUtensorMapDataType dt = op == MLP_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    if (!make_tile_map(ws, &mx, dt, 2, a.inputs, a.count, (uint32_t)c.dims[0], 64, wide::NS, CU_TENSOR_MAP_SWIZZLE_128B, err)) return cudaErrorInvalidValue;
+    uint64_t inputs = a.inputs;
+    if (c.input_dtype != op) {
+        const cudaError_t ce = converted_input_rows(st, ws, op, a.inputs, a.count, c.dims[0], &inputs, launches);
+        if (ce != cudaSuccess) { if (err) *err = "converting the fp32 input rows failed"; return ce; }
+    }
+    if (!make_tile_map(ws, &mx, dt, 2, inputs, a.count, (uint32_t)c.dims[0], 64, wide::NS, CU_TENSOR_MAP_SWIZZLE_128B, err)) return cudaErrorInvalidValue;
     WideTrainParams p;
     for (int l = 0; l <= wide::kMaxLayers; ++l) p.dims[l] = l <= nl ? c.dims[l] : 0;
     p.hidden_act = c.hidden_act;

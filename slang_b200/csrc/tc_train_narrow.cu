@@ -396,6 +396,9 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
         const bool fp32_storage = c.dtype == MLP_F32;
         auto round_z = [&](float v) -> float { return fp32_storage ? v : C::round(v); };
         const float alpha_op = C::round(c.act_alpha);
+        // few outputs (they sit in column group 0): their targets are read at the start of the tile
+        const bool t_pre = !p.outputs && od <= 4 && g == 0;
+        float tpre[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #ifdef MLPB200_TRACE
         bool tr_on = false;
         int tr_step = 0;
@@ -438,6 +441,12 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
                 // built in registers first: the loads and the sines overlap the wait below.
                 constexpr int kBlocks = GW / 16;
                 uint4 xa[kBlocks], xb[kBlocks];
+                // up to four targets per sample are fetched here too, a whole forward pass ahead of their use
+                if (t_pre && valid) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        if (i < od) tpre[i] = load_as_f32(c.target_dtype, p.targets, sample * od + i);
+                }
 #pragma unroll
                 for (int b = 0; b < kBlocks; ++b) {
                     const int c0 = 16 * (g + CS * b);
@@ -566,7 +575,7 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
                                     float dz = 0.0f;
                                     if (valid && j < od) {
                                         const float o = act_value(oact, c.act_alpha, z);
-                                        const float diff = o - load_as_f32(c.target_dtype, p.targets, sample * od + j);
+                                        const float diff = o - (t_pre ? tpre[(k + e) & 3] : load_as_f32(c.target_dtype, p.targets, sample * od + j));
                                         loss = fmaf(diff * loss_scale, diff, loss);
                                         dz = ((2.0f * loss_scale) * diff) * act_deriv(oact, c.act_alpha, z);
                                     }

@@ -66,6 +66,19 @@ def test_torch_front_end_matches_buffer_front_end():
     assert np.max(np.abs(g_torch - g_buf)) <= 1e-5 * scale  # same kernel; only the atomic order differs
     with pytest.raises(ValueError):
         tt.learn_gradient(xt[:, :2], ttg)
+    # strided views: every other row of a taller tensor, a column slice of a wider one, a transposed target
+    wide_x = torch.zeros((2000, 6), device="cuda")
+    wide_x[::2, 1:5] = xt
+    t_t = ttg.t().contiguous().t()          # same values, column-major strides
+    assert not wide_x[::2, 1:5].is_contiguous() and not t_t.is_contiguous()
+    tt.grads.zero_()
+    tt.learn_gradient(wide_x[::2, 1:5], t_t)
+    g_view = tt.grads.cpu().numpy()
+    assert np.max(np.abs(g_view - g_buf)) <= 1e-5 * scale
+    out_wide = torch.zeros((1000, 8), device="cuda")
+    y = tt.forward(xt)
+    tt.forward(wide_x[::2, 1:5], out=out_wide[:, 2:6])
+    assert torch.equal(out_wide[:, 2:6], y) and not out_wide[:, :2].any() and not out_wide[:, 6:].any()
     tt.adjust_parameters()
     torch.cuda.synchronize()
     assert torch.isfinite(tt.params.float()).all()

@@ -79,14 +79,15 @@ def test_input_gradients_from_the_wide_kernel(device, dims, dtype, act):
     assert abs(sm - float(words[1:].view(np.float32)[0])) <= 1e-2 * abs(sm)
 
 
-@pytest.mark.parametrize("dtype", [C.F32, C.F16])
-def test_encoder_in_front_of_the_network_trains_like_the_oracle(device, dtype):
-    """fp32 network: one thread per sample; fp16 network: the padded tensor-core kernel writes the input
-    gradients."""
+@pytest.mark.parametrize("dtype,hidden", [(C.F32, 16), (C.F16, 16), (C.F16, 128)])
+def test_encoder_in_front_of_the_network_trains_like_the_oracle(device, dtype, hidden):
+    """fp32 network: one thread per sample; fp16 networks: the tensor-core kernel that runs learnGradient writes
+    the input gradients (the padded 64-wide one; for 128 hidden units the wide one, whose fp32 feature rows
+    are rounded to fp16 by a launch in front of it)."""
     from slang_b200.encoded import EncodedTrainer
     rng = np.random.default_rng(12)
     pcfg = P.prepare(2, 2, 10, 4, 2.0, 1.0, 1.1, 1337, C.F32)
-    cfg = C.make_config([8, 16, 16, 3], dtype=dtype, hidden_act=C.ACT_RELU, lr=1e-2, adam_master=0 if dtype == C.F32 else 1)
+    cfg = C.make_config([8, hidden, hidden, 3], dtype=dtype, hidden_act=C.ACT_RELU, lr=1e-2, adam_master=0 if dtype == C.F32 else 1)
     p0 = C.init_params(cfg, seed=2, scheme="kaiming")
     table0 = rng.uniform(-1e-1, 1e-1, pcfg.table_values).astype(np.float32)
     count, steps = 2000, 5
