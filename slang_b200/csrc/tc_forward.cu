@@ -114,8 +114,11 @@ struct Geometry {
     static_assert((DH / CS) % 16 == 0 && (DOUT / CS) % 16 == 0, "column split");
 };
 
-template <int DIN, int DH, int DOUT, int NL, int FMT, int ACT, int OUT_ACT, int NCH, int CS>
-__global__ void __launch_bounds__(64 + 128 * NCH * CS, 1)
+// CPS: CTAs per SM the build is sized for (the narrow widths run two CTAs of three chains each: two control
+// warps walk their chains independently).
+// NCW: control warps (1 or 2).
+template <int DIN, int DH, int DOUT, int NL, int FMT, int ACT, int OUT_ACT, int NCH, int CS, int CPS = 1, int NCW = 1>
+__global__ void __launch_bounds__(64 + 128 * NCH * CS, CPS)
 forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_out, const Params p)
 {
     using G = Geometry<DIN, DH, DOUT, NL, NCH, CS>;
@@ -191,9 +194,13 @@ forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
     const uint32_t tmem_base = *tmem_ptr;
 
     // The i-th tile of this CTA (global tile blockIdx.x + i * gridDim.x) runs on chain i % NCH.
-    if (warp == 0) {
-        // =================================== control warp ==========================================
+    if (warp < NCW) {
+        // =================================== control warps =========================================
+        // With two of them, warp w walks the chains w, w + 2, ... in lock step among themselves only, so a
+        // chain that is late holds up at most half of the others (measured: +9 % at width 64, a loss at
+        // widths 16 and 128).  (Warp 1 also owns the tensor-memory allocation.)
         if (n_my_tiles > 0) {
+            const int cw = warp;
             const bool leader = elect_one();
             constexpr uint32_t F = FMT == MLP_BF16 ? 1u : 0u;
             const uint32_t lo_base = (sbase & 0x3FFFFu) >> 4;
@@ -204,7 +211,7 @@ forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
             if (leader) {
 #pragma unroll
                 for (int c = 0; c < NCH; ++c) {
-                    if ((uint32_t)c < n_my_tiles) {
+                    if (c % NCW == cw && (uint32_t)c < n_my_tiles) {
                         const uint32_t tile = blockIdx.x + (uint32_t)c * gridDim.x;
                         mbar_expect_tx(&x_full[c], kXBytes);
 #pragma unroll
@@ -220,7 +227,7 @@ forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
                 for (int l = 0; l < NL; ++l) {
 #pragma unroll
                     for (int c = 0; c < NCH; ++c) {
-                        if (j * NCH + c < n_my_tiles && ok) {
+                        if (c % NCW == cw && j * NCH + c < n_my_tiles && ok) {
                             // Every phase of the chain's barriers is observed in order.
                             if (steps[c] > 0) ok = mbar_wait(&acc_free[c], (steps[c] - 1) & 1u, abort_flag, p.status, kStatusCtrlAcc);
                             if (l == 0) ok = ok && mbar_wait(&x_full[c], j & 1u, abort_flag, p.status, kStatusCtrlX);
@@ -416,12 +423,12 @@ bool tc_forward_supported(const MlpConfig& c)
     return true;
 }
 
-template <int DIN, int DH, int DOUT, int NL, int FMT, int ACT, int OUT_ACT, int NCH, int CS>
+template <int DIN, int DH, int DOUT, int NL, int FMT, int ACT, int OUT_ACT, int NCH, int CS, int CPS = 1, int NCW = 1>
 static cudaError_t launch_fwd(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const MlpForwardParams& a, std::string* err)
 {
     using G = fwd::Geometry<DIN, DH, DOUT, NL, NCH, CS>;
-    static_assert(G::kSmemBytes <= 227 * 1024, "shared memory budget");
-    static_assert(G::kTmemCols <= 512, "tensor memory budget");
+    static_assert((G::kSmemBytes + (CPS > 1 ? 1024 : 0)) * CPS <= 227 * 1024, "shared memory budget");
+    static_assert(G::kTmemCols * CPS <= 512, "tensor memory budget");
     CUtensorMap mx;
     const CUtensorMapDataType dt = FMT == MLP_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     const CUtensorMapSwizzle sw = DIN >= 64 ? CU_TENSOR_MAP_SWIZZLE_128B : DIN == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
@@ -445,10 +452,11 @@ static cudaError_t launch_fwd(cudaStream_t st, TcWorkspace* ws, const MlpConfig&
     p.n_tiles = (a.count + 127u) / 128u;
     p.act_alpha = c.act_alpha;
     p.out_storage = (a.flags & MLP_FLAG_OUTPUT_STORAGE_TYPE) ? 1u : 0u;
-    auto kern = fwd::forward_tc_kernel<DIN, DH, DOUT, NL, FMT, ACT, OUT_ACT, NCH, CS>;
+    auto kern = fwd::forward_tc_kernel<DIN, DH, DOUT, NL, FMT, ACT, OUT_ACT, NCH, CS, CPS, NCW>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)G::kSmemBytes);
     if (e != cudaSuccess) return e;
-    const uint32_t grid = p.n_tiles < (uint32_t)ws->sm_count ? p.n_tiles : (uint32_t)ws->sm_count;
+    const uint32_t slots = (uint32_t)ws->sm_count * (uint32_t)CPS;
+    const uint32_t grid = p.n_tiles < slots ? p.n_tiles : slots;
     kern<<<grid, G::kThreads, G::kSmemBytes, st>>>(mx, mo, p);
     return cudaGetLastError();
 }
@@ -461,10 +469,11 @@ cudaError_t launch_forward_tc(cudaStream_t st, TcWorkspace* ws, const MlpConfig&
     cudaError_t e = cudaErrorInvalidValue;
     const int w = c.dims[1];
     const bool wide = c.n_layers == 5;
-#define MLPB200_FWD(W_, FMT_, NCH_, CS_) \
-    if (!wide && w == W_ && c.dtype == FMT_) e = launch_fwd<W_, W_, W_, 4, FMT_, MLP_ACT_RELU, MLP_ACT_IDENTITY, NCH_, CS_>(st, ws, c, a, err);
-    MLPB200_FWD(16, MLP_F16, 6, 1) MLPB200_FWD(32, MLP_F16, 6, 1) MLPB200_FWD(64, MLP_F16, 6, 1) MLPB200_FWD(128, MLP_F16, 2, 2)
-    MLPB200_FWD(16, MLP_BF16, 6, 1) MLPB200_FWD(32, MLP_BF16, 6, 1) MLPB200_FWD(64, MLP_BF16, 6, 1) MLPB200_FWD(128, MLP_BF16, 2, 2)
+    // chains per CTA, column split, CTAs per SM, control warps: the measured best per width
+#define MLPB200_FWD(W_, FMT_, NCH_, CS_, CPS_, NCW_) \
+    if (!wide && w == W_ && c.dtype == FMT_) e = launch_fwd<W_, W_, W_, 4, FMT_, MLP_ACT_RELU, MLP_ACT_IDENTITY, NCH_, CS_, CPS_, NCW_>(st, ws, c, a, err);
+    MLPB200_FWD(16, MLP_F16, 3, 1, 2, 1) MLPB200_FWD(32, MLP_F16, 3, 1, 2, 1) MLPB200_FWD(64, MLP_F16, 6, 1, 1, 2) MLPB200_FWD(128, MLP_F16, 2, 2, 1, 1)
+    MLPB200_FWD(16, MLP_BF16, 3, 1, 2, 1) MLPB200_FWD(32, MLP_BF16, 3, 1, 2, 1) MLPB200_FWD(64, MLP_BF16, 6, 1, 1, 2) MLPB200_FWD(128, MLP_BF16, 2, 2, 1, 1)
 #undef MLPB200_FWD
     if (wide && c.dtype == MLP_BF16) e = launch_fwd<64, 128, 64, 5, MLP_BF16, MLP_ACT_GELU_TANH, MLP_ACT_IDENTITY, 2, 2>(st, ws, c, a, err);
     if (wide && c.dtype == MLP_F16) e = launch_fwd<64, 128, 64, 5, MLP_F16, MLP_ACT_GELU_TANH, MLP_ACT_IDENTITY, 2, 2>(st, ws, c, a, err);
