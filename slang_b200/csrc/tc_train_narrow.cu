@@ -146,15 +146,21 @@ struct Map {
     static constexpr uint32_t kD = kA + NL * kTile;            //   activation derivatives of layers 0 .. NL-2 (absent with DFA)
     static constexpr uint32_t kDZ = kD + (DFA ? 0 : (NL - 1) * kTile);   //   dZ of the last layer
     static constexpr uint32_t kChainBytes = kDZ + kTile;
-    static constexpr uint32_t kOnes = kChain + NCH * kChainBytes;  // [128 rows][16 elements]: first column one, rest zero
-    static constexpr uint32_t kBias = kOnes + 128 * 32;        // fp32 [NL][H]
+    // The ones tile (first column one, rest zero): [128 rows][H elements] in the layout of an activation tile, so
+    // that its first 16 columns can follow A_l as a further block of the weight-gradient product's B operand:
+    // dW_l | db_l come out of one product of N = H + 16, H + 16 accumulator columns per layer.
+    static constexpr uint32_t kOnes = kChain + NCH * kChainBytes;
+    static constexpr uint32_t kBias = kOnes + kTile;        // fp32 [NL][H]
     static constexpr uint32_t kBars = kBias + NL * H * 4;      // per chain: acc_full, acc_free, tile_done
     static constexpr uint32_t kTmemPtr = kBars + 3 * NCH * 8;
     static constexpr uint32_t kAbort = kTmemPtr + 4;
     static constexpr uint32_t kSmemBytes = kAbort + 4 + 1024;
     // tensor-memory columns: one working accumulator per chain, then the gradients (shared by the chains)
-    static constexpr uint32_t kColAcc = 0, kColDW = H * NCH, kColDB = kColDW + H * NL, kTmemCols = 512;
-    static_assert(kColDB + 16 * NL <= 512, "tensor memory budget");
+    static constexpr uint32_t kColAcc = 0, kColDW = H * NCH, kDwCols = H + 16;  // columns per layer: dW_l, then db_l
+    static constexpr uint32_t kTmemCols = 512;
+    static_assert(kColDW + kDwCols * NL <= 512, "tensor memory budget");
+    // tensor-memory column of layer l's bias gradient
+    __host__ __device__ static constexpr uint32_t col_db(int l) { return kColDW + kDwCols * l + H; }
     static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 };
 
@@ -226,9 +232,9 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
         for (int j = threadIdx.x; j < H; j += kThreads)
             s_bias[l * H + j] = j < out ? load_as_f32(c.dtype, (const void*)p.net[l].biases, j) : 0.0f;
     }
-    for (int idx = threadIdx.x; idx < 128 * 16; idx += kThreads) {
-        const int r = idx / 16, i = idx % 16;
-        *(uint16_t*)(smem + M::kOnes + chunk_offset<16>(128, r, i / 8) + (i % 8) * 2) = (i == 0) ? C::one() : (uint16_t)0;
+    for (int idx = threadIdx.x; idx < 128 * H; idx += kThreads) {
+        const int r = idx / H, i = idx % H;
+        *(uint16_t*)(smem + M::kOnes + chunk_offset<H>(128, r, i / 8) + (i % 8) * 2) = (i == 0) ? C::one() : (uint16_t)0;
     }
     fence_async_smem();
     tc_fence_before();
@@ -245,13 +251,10 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
             constexpr uint32_t F = C::kUmmaFmt;
             constexpr uint32_t kIdFwd = umma_idesc(F, 0, 0, 128, H);   // acts (K) x W (K)
             constexpr uint32_t kIdDx = umma_idesc(F, 0, 1, 128, H);    // dZ (K) x W (MN)
-            constexpr uint32_t kIdDw = umma_idesc(F, 1, 1, 128, H);    // dZ^T (MN) x acts (MN)
-            constexpr uint32_t kIdDb = umma_idesc(F, 1, 1, 128, 16);   // dZ^T (MN) x ones (MN)
             const uint32_t lo_base = (sbase & 0x3FFFFu) >> 4;
             // operand rows of 2 H bytes with the swizzle of that span; groups of eight rows are 16 H bytes apart
             constexpr uint32_t kRow = (uint32_t)row_bytes(H);
             constexpr uint32_t kHi128 = ((8u * kRow) >> 4) | (1u << 14) | (layout_type(H) << 29);
-            constexpr uint32_t kHi32 = (256u >> 4) | (1u << 14) | (6u << 29);    // 32-byte rows and swizzle (ones column)
             // K-major [rows][H]: a K step of 16 elements is 32 bytes inside the row.
             auto desc_k = [&](uint32_t buf, int k) -> uint64_t {
                 return ((uint64_t)kHi128 << 32) | (lo_base + ((buf + (uint32_t)k * 32u) >> 4) + (1u << 16));
@@ -261,9 +264,11 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
             auto desc_mn = [&](uint32_t buf, int k) -> uint64_t {
                 return ((uint64_t)kHi128 << 32) | (lo_base + ((buf + (uint32_t)k * 16u * kRow) >> 4) + (1u << 16));
             };
-            auto desc_ones = [&](int k) -> uint64_t {
-                return ((uint64_t)kHi32 << 32) | (lo_base + ((M::kOnes + (uint32_t)k * 512u) >> 4) + (1u << 16));
+            // The same with the second H-element block `lbo` bytes after the first (the B operand [A_l | ones]).
+            auto desc_mn_lbo = [&](uint32_t buf, int k, uint32_t lbo) -> uint64_t {
+                return ((uint64_t)kHi128 << 32) | (lo_base + ((buf + (uint32_t)k * 16u * kRow) >> 4) + ((lbo >> 4) << 16));
             };
+            constexpr uint32_t kIdDwDb = umma_idesc(F, 1, 1, 128, H + 16);   // dZ^T (MN) x [acts | ones] (MN)
             uint32_t n_free[NCH];  // acc_free phases observed, per chain
 #pragma unroll
             for (int h = 0; h < NCH; ++h) n_free[h] = 0;
@@ -282,11 +287,9 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
             // dW_l and db_l of a tile; `first` is true only for the launch's first product into them.
             auto grads = [&](int l, uint32_t dzbuf, uint32_t abuf, bool first) {
 #pragma unroll
-                for (int k = 0; k < TS / 16; ++k) {
-                    umma_f16(tmem_base + M::kColDW + (uint32_t)(l * H), desc_mn(dzbuf, k), desc_mn(abuf, k), kIdDw,
-                             (first && k == 0) ? 0u : 1u);
-                    umma_f16(tmem_base + M::kColDB + (uint32_t)l * 16u, desc_mn(dzbuf, k), desc_ones(k), kIdDb, (first && k == 0) ? 0u : 1u);
-                }
+                for (int k = 0; k < TS / 16; ++k)
+                    umma_f16(tmem_base + M::kColDW + (uint32_t)l * M::kDwCols, desc_mn(dzbuf, k), desc_mn_lbo(abuf, k, M::kOnes - abuf),
+                             kIdDwDb, (first && k == 0) ? 0u : 1u);
             };
             const uint32_t rounds = (n_my_tiles + NCH - 1) / NCH;
             for (uint32_t rd = 0; rd < rounds && ok; ++rd) {
@@ -715,7 +718,7 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
                 float* dB = (float*)p.net[l].biasesGrad;
                 for (int c0 = (h * CS + g) * 16; c0 < H; c0 += 16 * G) {
                     uint32_t v[16];
-                    tmem_ld_32x16(lane_base + M::kColDW + (uint32_t)(l * H) + (uint32_t)c0, v);
+                    tmem_ld_32x16(lane_base + M::kColDW + (uint32_t)l * M::kDwCols + (uint32_t)c0, v);
                     tmem_ld_wait();
                     if (r < out) {
 #pragma unroll
@@ -725,7 +728,7 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
                 }
                 if (h == 0 && g == 0) {
                     uint32_t b[16];
-                    tmem_ld_32x16(lane_base + M::kColDB + (uint32_t)l * 16u, b);
+                    tmem_ld_32x16(lane_base + M::col_db(l), b);
                     tmem_ld_wait();
                     if (r < out) atomicAdd(dB + r, __uint_as_float(b[0]));
                 }
