@@ -9,8 +9,8 @@
 // columns; an epilogue thread owns one sample row (or a column group of it).
 //   forward   Z_l [128 x 64]  = A_l [128 x 64] . W_l^T        A: A_l, K-major          B: W_l [out][in], K-major
 //   input     dA_l [128 x 64] = dZ_l [128 x 64] . W_l          A: dZ_l, K-major         B: W_l, MN-major
-//   weights   dW_l [64 x 64] += dZ_l^T . A_l                   A: dZ_l, MN-major        B: A_l, MN-major (K = 128 samples)
-//   biases    db_l [64]      += dZ_l^T . 1                      A: dZ_l, MN-major        B: a constant column of ones
+//   weights   dW_l | db_l [64 x 80] += dZ_l^T . [A_l | 1]      A: dZ_l, MN-major        B: A_l, then a tile whose first column
+//             (one product of 64 rows, K = 128 samples)                                is ones, MN-major
 // The thread that owns a sample builds the sample's input row itself (conversion or the frequency
 // encoding), reads its targets straight from global memory, keeps the activation derivatives of its
 // row in shared memory and keeps the running loss in registers.  Weight and bias gradients
@@ -268,7 +268,7 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
             auto desc_mn_lbo = [&](uint32_t buf, int k, uint32_t lbo) -> uint64_t {
                 return ((uint64_t)kHi128 << 32) | (lo_base + ((buf + (uint32_t)k * 16u * kRow) >> 4) + ((lbo >> 4) << 16));
             };
-            constexpr uint32_t kIdDwDb = umma_idesc(F, 1, 1, 128, H + 16);   // dZ^T (MN) x [acts | ones] (MN)
+            constexpr uint32_t kIdDwDb = umma_idesc(F, 1, 1, 64, H + 16);    // dZ^T (MN, 64 rows) x [acts | ones] (MN)
             uint32_t n_free[NCH];  // acc_free phases observed, per chain
 #pragma unroll
             for (int h = 0; h < NCH; ++h) n_free[h] = 0;
@@ -712,6 +712,10 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
             const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
             // the warp groups of all chains share the columns: group i takes the 16-column pieces i, i + G, ...
             constexpr int G = CS * NCH;
+            // The gradient products have 64 rows: row r of such an accumulator sits on lane 32 (r / 16) + r % 16,
+            // so the first 16 lanes of this warp's quarter hold the output features 16 q .. 16 q + 15.
+            const int fo = q * 16 + lane;
+            const bool has_row = lane < 16;
             for (int l = 0; l < NL; ++l) {
                 const int in = c.dims[l], out = c.dims[l + 1];
                 float* dW = (float*)p.net[l].weightsGrad;
@@ -720,17 +724,17 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
                     uint32_t v[16];
                     tmem_ld_32x16(lane_base + M::kColDW + (uint32_t)l * M::kDwCols + (uint32_t)c0, v);
                     tmem_ld_wait();
-                    if (r < out) {
+                    if (has_row && fo < out) {
 #pragma unroll
                         for (int i = 0; i < 16; ++i)
-                            if (c0 + i < in) atomicAdd(dW + (size_t)r * in + c0 + i, __uint_as_float(v[i]));
+                            if (c0 + i < in) atomicAdd(dW + (size_t)fo * in + c0 + i, __uint_as_float(v[i]));
                     }
                 }
                 if (h == 0 && g == 0) {
                     uint32_t b[16];
                     tmem_ld_32x16(lane_base + M::col_db(l), b);
                     tmem_ld_wait();
-                    if (r < out) atomicAdd(dB + r, __uint_as_float(b[0]));
+                    if (has_row && fo < out) atomicAdd(dB + fo, __uint_as_float(b[0]));
                 }
             }
             float mx = run_max, sm = run_sum;
