@@ -65,10 +65,13 @@ enum MlpSumOrder { MLP_SUM_NEURAL = 0, MLP_SUM_BIAS_FIRST_FUSED = 1 };
  * (source/standard-modules/neural/layers.slang:53-71, network-parameter-layout-converter.slang:54-68,
  * 176-181): rows and columns padded to multiples of 16, 16x16 tiles ordered input-tile-major, inside a tile
  * the register order of a tensor-core B fragment; a layer's biases follow its weights in a padded slot
- * (MlpLayerPointers.biases points at that slot).  The forward entry points read either; weights a shader
- * holds in OptimalLayout are used in place, no conversion pass.  The training entry points take ROW_MAJOR
- * only (the reference keeps OptimalLayout gradients in the target's accumulator-fragment order, a second
- * format; mlp_layout_to_portable / mlp_layout_to_optimal convert between training and rendering). */
+ * (MlpLayerPointers.biases points at that slot).  Every entry point built for an MlpConfig reads either:
+ * weights a shader holds in OptimalLayout are used, and trained, in place, with no conversion pass.
+ * learnGradient adds the gradient of a weight at the weight's own element offset behind
+ * MlpLayerPointers.weightsGrad (an fp32 buffer of the same shape; the reference's own OptimalLayout gradient
+ * buffers are in the target's accumulator-fragment order instead, a format no caller of this library sees),
+ * and adjustParameters runs over all mlp_param_layout() elements, padding included (zero gradients leave
+ * the zero padding as it is).  mlp_learn_gradient_ordered_noalloc takes ROW_MAJOR only. */
 enum MlpParamLayout { MLP_PARAMS_ROW_MAJOR = 0, MLP_PARAMS_OPTIMAL = 1 };
 
 typedef struct MlpConfig {
@@ -86,7 +89,7 @@ typedef struct MlpConfig {
     float lr, beta1, beta2, eps;       /* Adam constants (adam.slang:15-19) */
     int32_t adam_master;               /* 1: Adam keeps an fp32 copy of each parameter in its state */
     int32_t sum_order;                 /* MlpSumOrder of the one-thread-per-sample kernels */
-    int32_t param_layout;              /* MlpParamLayout of the weights (forward entry points) */
+    int32_t param_layout;              /* MlpParamLayout of the weights and of their gradients */
     int32_t operand_dtype;             /* 0: products read the storage type.  MLP_F16 / MLP_BF16 with dtype = MLP_F32:
                                           the neural module's T = float on its tensor-core path, whose matrix
                                           operands are half whatever T is (source/standard-modules/neural/

@@ -135,7 +135,10 @@ def named_config(name):
 
 
 def param_layout(cfg):
-    """Element offsets (weights, biases) per layer and the padded element count."""
+    """Element offsets (weights, biases) per layer and the padded element count (of the row-major segment, or of
+    the OptimalLayout buffer when cfg.param_layout says so)."""
+    if cfg.param_layout == PARAMS_OPTIMAL:
+        return optimal_layout_offsets(cfg.layer_dims)
     align = 64 // DTYPE_SIZE[cfg.dtype]
     off = 0
     w_off, b_off = [], []

@@ -283,8 +283,6 @@ int32_t mlp_kernel_get_for_config(MlpDevice* d, const MlpConfig* config, const c
     *out_kernel = nullptr;
     std::string why;
     if (!config_ok(config, &why)) return fail(MLP_E_INVALID_ARG, "bad config: %s", why.c_str());
-    if (config->param_layout != MLP_PARAMS_ROW_MAJOR && std::strncmp(entry_point, "forward", 7) != 0)
-        return fail(MLP_E_NOT_AVAILABLE, "'%s' takes row-major parameters; OptimalLayout parameters are read by the forward entry points only", entry_point);
     MlpKernel* k = new MlpKernel();
     k->cfg = *config;
     k->impl = "simt";

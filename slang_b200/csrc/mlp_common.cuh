@@ -141,8 +141,19 @@ struct Layout {
 inline Layout make_layout(const MlpConfig& c)
 {
     Layout L{};
-    const int64_t align = 64 / dtype_size(c.dtype);
     int64_t off = 0;
+    if (c.param_layout == MLP_PARAMS_OPTIMAL) {
+        // FFLayer's storage (source/standard-modules/neural/layers.slang:53-71): per layer align16(in) x align16(out)
+        // weights in 16x16 tiles, then align16(out) bias slots
+        for (int l = 0; l < c.n_layers; ++l) {
+            const int64_t in16 = (int64_t(c.dims[l]) + 15) / 16 * 16, out16 = (int64_t(c.dims[l + 1]) + 15) / 16 * 16;
+            L.w[l] = off; off += in16 * out16;
+            L.b[l] = off; off += out16;
+        }
+        L.total = off;
+        return L;
+    }
+    const int64_t align = 64 / dtype_size(c.dtype);
     for (int l = 0; l < c.n_layers; ++l) {
         int64_t nw = int64_t(c.dims[l]) * c.dims[l + 1];
         L.w[l] = off; off += (nw + align - 1) / align * align;

@@ -153,7 +153,7 @@ learn_gradient_simt_kernel(SimtNet net, const MlpLayerPointers* __restrict__ lp,
             const void* W = (const void*)lp[l].weights;
             for (int i = 0; i < in; ++i) {
                 float r = 0.0f;
-                for (int j = 0; j < out; ++j) r = mac(load_weight(c, W, int64_t(j) * in + i), dz[j], r, fused);
+                for (int j = 0; j < out; ++j) r = mac(load_weight(c, W, weight_index(c.param_layout, in, out, j, i)), dz[j], r, fused);
                 const float d = round_to(operand_type(c), act_deriv(c.hidden_act, c.act_alpha, zprev[i]));
                 zprev[i] = round_to(operand_type(c), r * d);
             }
@@ -165,7 +165,7 @@ learn_gradient_simt_kernel(SimtNet net, const MlpLayerPointers* __restrict__ lp,
             const void* W = (const void*)lp[0].weights;
             for (int i = 0; i < in; ++i) {
                 float r = 0.0f;
-                for (int j = 0; j < out; ++j) r = mac(load_weight(c, W, int64_t(j) * in + i), dz[j], r, fused);
+                for (int j = 0; j < out; ++j) r = mac(load_weight(c, W, weight_index(c.param_layout, in, out, j, i)), dz[j], r, fused);
                 input_grads[int64_t(tid) * in + i] = round_to(c.dtype, r);
             }
         }
@@ -218,7 +218,7 @@ learn_gradient_simt_kernel(SimtNet net, const MlpLayerPointers* __restrict__ lp,
                 if (p < in * out) {
                     const int j = p / in, i = p % in;
                     for (int s = 0; s < gn; ++s) acc = mac(smem[s * stride + in + j], smem[s * stride + i], acc, fused);
-                    atomicAdd(dW + p, acc);
+                    atomicAdd(dW + weight_index(c.param_layout, in, out, j, i), acc);
                 } else {
                     const int j = p - in * out;
                     for (int s = 0; s < gn; ++s) acc += smem[s * stride + in + j];
@@ -247,7 +247,7 @@ sequential_sum_kernel(SimtNet net, const MlpLayerPointers* __restrict__ lp, cons
     const float* zbase = scratch + na + net.a_off[layer + 1] - net.a_off[1];
     if (p < in * out) {
         const int j = p / in, i = p % in;
-        float* dst = (float*)lp[layer].weightsGrad + p;
+        float* dst = (float*)lp[layer].weightsGrad + weight_index(c.param_layout, in, out, j, i);
         float acc = *dst;
         for (uint32_t s = 0; s < count; ++s) acc = mac(zbase[s * stride + j], abase[s * stride + i], acc, fused);
         *dst = acc;

@@ -874,7 +874,13 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                 tmem_ld_cols(lane_base + kColDW1 + (uint32_t)(l - 1) * 128u + (uint32_t)col, v);
                 tmem_ld_wait();
                 if (f < out) {
-                    if ((in & 3) == 0) {
+                    if (p.param_layout != MLP_PARAMS_ROW_MAJOR) {
+                        // tiled parameters: the gradient of weight (f, i) goes where the weight itself lies
+                        float* gW = (float*)p.net[l].weightsGrad;
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (col + i < in) atomicAdd(gW + weight_index(p.param_layout, in, out, f, col + i), __uint_as_float(v[i]));
+                    } else if ((in & 3) == 0) {
                         // four parameters per reduction (16-byte aligned: rows are multiples of 16 bytes)
 #pragma unroll
                         for (int i = 0; i < 32; i += 4)
@@ -898,14 +904,19 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                 if (f < in) {
 #pragma unroll
                     for (int i = 0; i < 16; ++i)
-                        if (e * 16 + i < out) atomicAdd(dW + (size_t)(e * 16 + i) * in + f, __uint_as_float(v[i]));
+                        if (e * 16 + i < out) atomicAdd(dW + weight_index(p.param_layout, in, out, e * 16 + i, f), __uint_as_float(v[i]));
                 }
             }
             {
                 const int in = p.dims[0], out = p.dims[1];
                 float* dW = (float*)p.net[0].weightsGrad + (size_t)f * in + e * 16;
                 if (f < out) {
-                    if ((in & 3) == 0) {
+                    if (p.param_layout != MLP_PARAMS_ROW_MAJOR) {
+                        float* gW = (float*)p.net[0].weightsGrad;
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            if (e * 16 + i < in) atomicAdd(gW + weight_index(p.param_layout, in, out, f, e * 16 + i), dw0[i]);
+                    } else if ((in & 3) == 0) {
 #pragma unroll
                         for (int i = 0; i < 16; i += 4)
                             if (e * 16 + i < in) atomicAdd((float4*)(dW + i), make_float4(dw0[i], dw0[i + 1], dw0[i + 2], dw0[i + 3]));
@@ -1166,7 +1177,7 @@ cudaError_t launch_learn_gradient_tc(cudaStream_t st, TcWorkspace* ws, const Mlp
     WideTrainParams p;
     for (int l = 0; l <= wide::kMaxLayers; ++l) p.dims[l] = l <= nl ? c.dims[l] : 0;
     p.hidden_act = c.hidden_act;
-    p.param_layout = MLP_PARAMS_ROW_MAJOR;
+    p.param_layout = c.param_layout;
     p.storage_dtype = c.dtype;
     p.t_direct = t_direct ? 1 : 0;
     p.target_dtype = c.target_dtype;

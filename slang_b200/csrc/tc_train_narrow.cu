@@ -727,7 +727,7 @@ __global__ void __launch_bounds__(threads_for(CS * NCH), 1) learn_gradient_narro
                     if (has_row && fo < out) {
 #pragma unroll
                         for (int i = 0; i < 16; ++i)
-                            if (c0 + i < in) atomicAdd(dW + (size_t)fo * in + c0 + i, __uint_as_float(v[i]));
+                            if (c0 + i < in) atomicAdd(dW + weight_index(c.param_layout, in, out, fo, c0 + i), __uint_as_float(v[i]));
                     }
                 }
                 if (h == 0 && g == 0) {

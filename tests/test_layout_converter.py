@@ -8,6 +8,7 @@ import pytest
 
 from oracle import layout_oracle as LO
 from slang_b200 import config as C
+from mlp_testlib import gpu_trajectory, oracle_trajectory, per_layer_rel_errs
 
 DIMS, MASK = [5, 13, 7, 19], 0b101
 
@@ -146,9 +147,93 @@ def test_forward_reads_optimal_layout_in_place(dims, dtype, entry):
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
         if dims == [4, 2]:
             assert np.all(got.reshape(count, 2) == [39.0, 80.0])
-        # the training entry points refuse the layout
-        with pytest.raises(lib.MlpError) as info:
-            dev.kernel("learnGradient", cfg_opt)
-        assert info.value.code == -3
+        # the training entry points take the layout too (test_training_on_optimal_layout_parameters_in_place)
+        assert dev.kernel("learnGradient", cfg_opt).implementation == dev.kernel("learnGradient", cfg).implementation
+    finally:
+        dev.destroy()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dims,dtype,act,entry", [
+    ([2, 16, 16, 1], "f32", C.ACT_RELU, "learnGradient"),                 # one thread per sample
+    ([20, 48, 64, 3], "f16", C.ACT_LEAKY_RELU, "learnGradient"),          # padded 64-wide tensor-core kernel, ragged tiles
+    ([4, 32, 32, 32, 32, 4], "f16", C.ACT_LEAKY_RELU, "learnGradient"),   # its 32-wide build
+    ([64, 128, 128, 128, 128, 64], "bf16", C.ACT_GELU_TANH, "learnGradient"),  # wide tensor-core kernel
+    ([32, 96, 128, 10], "f16", C.ACT_RELU, "learnGradient"),              # wide kernel, widths that are not tile multiples
+    ([20, 48, 64, 3], "f16", C.ACT_LEAKY_RELU, "learnGradient_simt"),
+])
+def test_training_on_optimal_layout_parameters_in_place(dims, dtype, act, entry):
+    """learnGradient + adjustParameters on parameters that stay in OptimalLayout (what a Slang shader's FFLayer
+    reads, source/standard-modules/neural/layers.slang:53-71): after three steps the parameters, converted back
+    with the numpy layout oracle's index map, equal those of the same run on row-major parameters (to the order
+    of the atomic adds), and the loss words agree; both runs are held against the CPU oracle's trajectory."""
+    from slang_b200.api import Device
+    dt = {"f32": C.F32, "f16": C.F16, "bf16": C.BF16}[dtype]
+    dev = Device(0)
+    try:
+        rng = np.random.default_rng(sum(dims) + len(entry))
+        in_dt = dt if max(dims) > 64 else C.F32
+        cfg = C.make_config(dims, dtype=dt, hidden_act=act, act_alpha=0.02, input_dtype=in_dt, target_dtype=C.F32, lr=1e-3,
+                            adam_master=0 if dt == C.F32 else 1)
+        cfg_opt = C.make_config(dims, dtype=dt, hidden_act=act, act_alpha=0.02, input_dtype=in_dt, target_dtype=C.F32, lr=1e-3,
+                                adam_master=0 if dt == C.F32 else 1)
+        cfg_opt.param_layout = C.PARAMS_OPTIMAL
+        p0 = C.init_params(cfg, seed=11, scheme="xavier")
+        w_off, b_off, total = C.param_layout(cfg)
+        ow, ob, ototal = C.param_layout(cfg_opt)
+        assert (ow, ob, ototal) == C.optimal_layout_offsets(dims)
+        for l in range(cfg.n_layers):
+            p0[b_off[l]:b_off[l] + dims[l + 1]] = C.to_storage(rng.uniform(-0.2, 0.2, dims[l + 1]).astype(np.float32), dt)
+
+        def index_map(l):
+            """optimal element offset of weight (o, i) of layer l, from the layout oracle's tile order"""
+            in16, out16 = LO.align16(dims[l]), LO.align16(dims[l + 1])
+            m = np.empty((dims[l + 1], dims[l]), dtype=np.int64)
+            for o in range(dims[l + 1]):
+                for i in range(dims[l]):
+                    tile = (i // 16) * (out16 // 16) + (o // 16)
+                    m[o, i] = ow[l] + tile * 256 + LO.native_tile_pos(i % 16, o % 16)
+            return m
+
+        maps = [index_map(l) for l in range(cfg.n_layers)]
+
+        def to_opt(flat):
+            out = np.zeros(ototal, dtype=flat.dtype)
+            for l in range(cfg.n_layers):
+                out[maps[l].ravel()] = flat[w_off[l]:w_off[l] + dims[l] * dims[l + 1]]
+                out[ob[l]:ob[l] + dims[l + 1]] = flat[b_off[l]:b_off[l] + dims[l + 1]]
+            return out
+
+        def to_rows(opt):
+            out = np.zeros(total, dtype=opt.dtype)
+            for l in range(cfg.n_layers):
+                out[w_off[l]:w_off[l] + dims[l] * dims[l + 1]] = opt[maps[l].ravel()]
+                out[b_off[l]:b_off[l] + dims[l + 1]] = opt[ob[l]:ob[l] + dims[l + 1]]
+            return out
+
+        count = 128 * 3 + 77
+        batches = []
+        for _ in range(3):
+            x = C.to_storage(rng.uniform(-1, 1, (count, dims[0])).astype(np.float32), in_dt)
+            t = rng.uniform(-1, 1, (count, dims[-1])).astype(np.float32)
+            batches.append((x, t))
+        p_rows, l_rows, g_rows, _, tr_rows = gpu_trajectory(dev, cfg, p0, batches, entry)
+        p_opt, l_opt, g_opt, _, tr_opt = gpu_trajectory(dev, cfg_opt, to_opt(p0), batches, entry)
+        assert tr_opt.k_learn.implementation == tr_rows.k_learn.implementation
+        assert tr_opt.k_learn.implementation == ("simt" if dt == C.F32 or entry.endswith("simt") else "tcgen05")
+        # the padding of the tiled buffer stays zero: gradients and parameters
+        used = np.zeros(ototal, dtype=bool)
+        for l in range(cfg.n_layers):
+            used[maps[l].ravel()] = True
+            used[ob[l]:ob[l] + dims[l + 1]] = True
+        assert not g_opt[~used].any() and not C.from_storage(p_opt, dt)[~used].any()
+        tol = 1e-5 if dt == C.F32 else 2e-3
+        assert max(per_layer_rel_errs(cfg, to_rows(g_opt), g_rows)) <= tol
+        assert max(per_layer_rel_errs(cfg, C.from_storage(to_rows(p_opt), dt), C.from_storage(p_rows, dt))) <= 10 * tol
+        for (m1, s1), (m2, s2) in zip(l_opt, l_rows):
+            assert abs(s1 - s2) <= 10 * tol * abs(s2) and abs(m1 - m2) <= 10 * tol * abs(m2)
+        # and against the oracle
+        _, l_ref, g_ref, _ = oracle_trajectory(cfg, p0, batches, n_threads=4)
+        assert max(per_layer_rel_errs(cfg, to_rows(g_opt), g_ref)) <= (1e-5 if dt == C.F32 else 1e-2)
     finally:
         dev.destroy()
