@@ -29,13 +29,14 @@ COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
 # (object name, source, extra flags).  The one-thread-per-sample kernels must not contract a*b+c into
 # an fma on their own: their fp32 results are compared bit for bit with a sequential CPU.  The padded
 # tensor-core kernel is instantiated some fifty times; its source is compiled in eight parts, the wide
-# kernel's in two (training builds, forward-only builds).
+# kernel's in three (training builds, forward-only builds, training builds with the optional outputs).
 UNITS = [
     ("abi", "abi.cu", []),
     ("simt_kernels", "simt_kernels.cu", ["-fmad=false"]),
     ("layout_convert", "layout_convert.cu", []),
     ("tc_kernels_0", "tc_kernels.cu", ["-DMLPB200_WIDE_PART=0"]),
     ("tc_kernels_1", "tc_kernels.cu", ["-DMLPB200_WIDE_PART=1"]),
+    ("tc_kernels_2", "tc_kernels.cu", ["-DMLPB200_WIDE_PART=2"]),
     ("tc_forward", "tc_forward.cu", []),
     ("comm", "comm.cu", []),
     ("matrix_convert", "matrix_convert.cu", []),

@@ -207,7 +207,10 @@ struct WideTrainParams {
 // shapes): no targets, no derivatives, no gradient products.
 // F32S: fp32 parameter storage with 16-bit operands (weights converted while they are staged, pre-activations and
 // outputs not rounded); such networks run the builds with the activation chosen at run time.
-template <int FMT, int ACT, int NL, bool FWD, bool F32S = false>
+// XTRA: training builds that also write the input gradients (WideTrainParams::input_grads) and / or write the weight
+// gradients in the tiled parameter layout; the plain training builds carry neither test (they cost 2.5 % at
+// the benchmark shape when they were run-time options of one build).
+template <int FMT, int ACT, int NL, bool FWD, bool F32S = false, bool XTRA = false>
 __global__ void __launch_bounds__(wide::kThreads, 1)
 learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_t,
                            const WideTrainParams p)
@@ -514,7 +517,7 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                 // ---- optional: the input gradient dA_0^T [inputs x samples] = W_0^T . dZ_0^T of both chains, once
                 //      dW_0 has left the accumulator.  W_0 holds 64 input columns; the instruction's upper 64 lanes
                 //      read the rows of the next weight buffer and are never looked at ----
-                if (p.input_grads) {
+                if (XTRA && p.input_grads) {
 #pragma unroll
                     for (int h = 0; h < NCH; ++h) chain_wait(h);
                     if (ok && leader) {
@@ -833,7 +836,7 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
             }
             // ---- optional: the input gradients of this tile, input feature on the lane (quarters 0 and 1), sample
             //      on the column; a warp writes 32 consecutive features of one sample per store ----
-            if (p.input_grads) {
+            if (XTRA && p.input_grads) {
                 wait_acc(0);
                 wait_acc(1);
                 if (!ok) break;
@@ -874,7 +877,7 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                 tmem_ld_cols(lane_base + kColDW1 + (uint32_t)(l - 1) * 128u + (uint32_t)col, v);
                 tmem_ld_wait();
                 if (f < out) {
-                    if (p.param_layout != MLP_PARAMS_ROW_MAJOR) {
+                    if (XTRA && p.param_layout != MLP_PARAMS_ROW_MAJOR) {
                         // tiled parameters: the gradient of weight (f, i) goes where the weight itself lies
                         float* gW = (float*)p.net[l].weightsGrad;
 #pragma unroll
@@ -904,14 +907,14 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                 if (f < in) {
 #pragma unroll
                     for (int i = 0; i < 16; ++i)
-                        if (e * 16 + i < out) atomicAdd(dW + weight_index(p.param_layout, in, out, e * 16 + i, f), __uint_as_float(v[i]));
+                        if (e * 16 + i < out) atomicAdd(dW + (XTRA ? weight_index(p.param_layout, in, out, e * 16 + i, f) : (int64_t)(e * 16 + i) * in + f), __uint_as_float(v[i]));
                 }
             }
             {
                 const int in = p.dims[0], out = p.dims[1];
                 float* dW = (float*)p.net[0].weightsGrad + (size_t)f * in + e * 16;
                 if (f < out) {
-                    if (p.param_layout != MLP_PARAMS_ROW_MAJOR) {
+                    if (XTRA && p.param_layout != MLP_PARAMS_ROW_MAJOR) {
                         float* gW = (float*)p.net[0].weightsGrad;
 #pragma unroll
                         for (int i = 0; i < 16; ++i)
@@ -959,11 +962,12 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
 }
 
 // ------------------------------------------------------------------------------------------------
-// Host side.  This file is compiled twice (slang_b200/build.py): MLPB200_WIDE_PART 0 holds the workspace,
-// the tensor-map helper and the training builds of the kernel, part 1 the forward-only builds.
+// Host side.  This file is compiled three times (slang_b200/build.py): MLPB200_WIDE_PART 0 holds the workspace,
+// the tensor-map helper and the plain training builds of the kernel, part 1 the forward-only builds, part 2
+// the training builds with input gradients and tiled-layout gradients.
 // ------------------------------------------------------------------------------------------------
 #ifndef MLPB200_WIDE_PART
-#error "compile with -DMLPB200_WIDE_PART=0 or 1"
+#error "compile with -DMLPB200_WIDE_PART=0, 1 or 2"
 #endif
 // fp32 input rows -> the operand type, for networks whose inputs arrive as fp32 (an encoder in front of the
 // network writes fp32 features): the wide kernel takes its input tile by TMA in the operand type, so the rows
@@ -1101,11 +1105,11 @@ bool make_tile_map(TcWorkspace* ws, CUtensorMap* map, CUtensorMapDataType type, 
 
 #endif  // part 0
 
-template <int FMT, int ACT, int NL, bool FWD, bool F32S = false>
+template <int FMT, int ACT, int NL, bool FWD, bool F32S = false, bool XTRA = false>
 static cudaError_t launch_wide(cudaStream_t st, TcWorkspace* ws, const CUtensorMap& mx, const CUtensorMap& mt,
                                const WideTrainParams& p)
 {
-    auto kern = learn_gradient_wide_kernel<FMT, ACT, NL, FWD, F32S>;
+    auto kern = learn_gradient_wide_kernel<FMT, ACT, NL, FWD, F32S, XTRA>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)wide::kSmemBytes);
     if (e != cudaSuccess) return e;
     const uint32_t grid = p.n_tiles < (uint32_t)ws->sm_count ? p.n_tiles : (uint32_t)ws->sm_count;
@@ -1116,41 +1120,53 @@ static cudaError_t launch_wide(cudaStream_t st, TcWorkspace* ws, const CUtensorM
 // The builds of the kernel: GELU (tanh form) and ReLU as compile-time activations for every layer count,
 // leaky ReLU for five layers, and every layer count with the activation chosen at run time (slower: every
 // element goes through a switch and the library's scalar math).
-template <int FMT, bool FWD>
+template <int FMT, bool FWD, bool XTRA = false>
 static cudaError_t launch_wide_fmt(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const CUtensorMap& mx,
                                    const CUtensorMap& mt, const WideTrainParams& p)
 {
     const int act = c.hidden_act;
     if (c.dtype == MLP_F32) {   // fp32 storage, 16-bit operands
         switch (c.n_layers) {
-        case 5: return launch_wide<FMT, -1, 5, FWD, true>(st, ws, mx, mt, p);
-        case 4: return launch_wide<FMT, -1, 4, FWD, true>(st, ws, mx, mt, p);
-        case 3: return launch_wide<FMT, -1, 3, FWD, true>(st, ws, mx, mt, p);
-        case 2: return launch_wide<FMT, -1, 2, FWD, true>(st, ws, mx, mt, p);
+        case 5: return launch_wide<FMT, -1, 5, FWD, true, XTRA>(st, ws, mx, mt, p);
+        case 4: return launch_wide<FMT, -1, 4, FWD, true, XTRA>(st, ws, mx, mt, p);
+        case 3: return launch_wide<FMT, -1, 3, FWD, true, XTRA>(st, ws, mx, mt, p);
+        case 2: return launch_wide<FMT, -1, 2, FWD, true, XTRA>(st, ws, mx, mt, p);
         }
         return cudaErrorInvalidValue;
     }
     switch (c.n_layers) {
     case 5:
-        if (act == MLP_ACT_GELU_TANH) return launch_wide<FMT, MLP_ACT_GELU_TANH, 5, FWD>(st, ws, mx, mt, p);
-        if (act == MLP_ACT_RELU) return launch_wide<FMT, MLP_ACT_RELU, 5, FWD>(st, ws, mx, mt, p);
-        if (act == MLP_ACT_LEAKY_RELU) return launch_wide<FMT, MLP_ACT_LEAKY_RELU, 5, FWD>(st, ws, mx, mt, p);
-        return launch_wide<FMT, -1, 5, FWD>(st, ws, mx, mt, p);
+        if (act == MLP_ACT_GELU_TANH) return launch_wide<FMT, MLP_ACT_GELU_TANH, 5, FWD, false, XTRA>(st, ws, mx, mt, p);
+        if (act == MLP_ACT_RELU) return launch_wide<FMT, MLP_ACT_RELU, 5, FWD, false, XTRA>(st, ws, mx, mt, p);
+        if (act == MLP_ACT_LEAKY_RELU) return launch_wide<FMT, MLP_ACT_LEAKY_RELU, 5, FWD, false, XTRA>(st, ws, mx, mt, p);
+        return launch_wide<FMT, -1, 5, FWD, false, XTRA>(st, ws, mx, mt, p);
     case 4:
-        if (act == MLP_ACT_GELU_TANH) return launch_wide<FMT, MLP_ACT_GELU_TANH, 4, FWD>(st, ws, mx, mt, p);
-        if (act == MLP_ACT_RELU) return launch_wide<FMT, MLP_ACT_RELU, 4, FWD>(st, ws, mx, mt, p);
-        return launch_wide<FMT, -1, 4, FWD>(st, ws, mx, mt, p);
+        if (act == MLP_ACT_GELU_TANH) return launch_wide<FMT, MLP_ACT_GELU_TANH, 4, FWD, false, XTRA>(st, ws, mx, mt, p);
+        if (act == MLP_ACT_RELU) return launch_wide<FMT, MLP_ACT_RELU, 4, FWD, false, XTRA>(st, ws, mx, mt, p);
+        return launch_wide<FMT, -1, 4, FWD, false, XTRA>(st, ws, mx, mt, p);
     case 3:
-        if (act == MLP_ACT_GELU_TANH) return launch_wide<FMT, MLP_ACT_GELU_TANH, 3, FWD>(st, ws, mx, mt, p);
-        if (act == MLP_ACT_RELU) return launch_wide<FMT, MLP_ACT_RELU, 3, FWD>(st, ws, mx, mt, p);
-        return launch_wide<FMT, -1, 3, FWD>(st, ws, mx, mt, p);
+        if (act == MLP_ACT_GELU_TANH) return launch_wide<FMT, MLP_ACT_GELU_TANH, 3, FWD, false, XTRA>(st, ws, mx, mt, p);
+        if (act == MLP_ACT_RELU) return launch_wide<FMT, MLP_ACT_RELU, 3, FWD, false, XTRA>(st, ws, mx, mt, p);
+        return launch_wide<FMT, -1, 3, FWD, false, XTRA>(st, ws, mx, mt, p);
     case 2:
-        if (act == MLP_ACT_GELU_TANH) return launch_wide<FMT, MLP_ACT_GELU_TANH, 2, FWD>(st, ws, mx, mt, p);
-        if (act == MLP_ACT_RELU) return launch_wide<FMT, MLP_ACT_RELU, 2, FWD>(st, ws, mx, mt, p);
-        return launch_wide<FMT, -1, 2, FWD>(st, ws, mx, mt, p);
+        if (act == MLP_ACT_GELU_TANH) return launch_wide<FMT, MLP_ACT_GELU_TANH, 2, FWD, false, XTRA>(st, ws, mx, mt, p);
+        if (act == MLP_ACT_RELU) return launch_wide<FMT, MLP_ACT_RELU, 2, FWD, false, XTRA>(st, ws, mx, mt, p);
+        return launch_wide<FMT, -1, 2, FWD, false, XTRA>(st, ws, mx, mt, p);
     }
     return cudaErrorInvalidValue;
 }
+
+// Part 2: the training builds with the extras, behind one function for part 0 to call.
+cudaError_t launch_wide_train_extras(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, int op, const CUtensorMap& mx,
+                                     const CUtensorMap& mt, const WideTrainParams& p);
+#if MLPB200_WIDE_PART == 2
+cudaError_t launch_wide_train_extras(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, int op, const CUtensorMap& mx,
+                                     const CUtensorMap& mt, const WideTrainParams& p)
+{
+    return op == MLP_BF16 ? launch_wide_fmt<MLP_BF16, false, true>(st, ws, c, mx, mt, p)
+                          : launch_wide_fmt<MLP_F16, false, true>(st, ws, c, mx, mt, p);
+}
+#endif
 
 #if MLPB200_WIDE_PART == 0
 cudaError_t launch_learn_gradient_tc(cudaStream_t st, TcWorkspace* ws, const MlpConfig& c, const MlpLearnGradParamsEx& a,
@@ -1192,12 +1208,14 @@ cudaError_t launch_learn_gradient_tc(cudaStream_t st, TcWorkspace* ws, const Mlp
     p.timing = ws->timing;
     p.outputs = nullptr;
     p.input_grads = input_grads;
-    const cudaError_t e = op == MLP_BF16 ? launch_wide_fmt<MLP_BF16, false>(st, ws, c, mx, mt, p)
-                                              : launch_wide_fmt<MLP_F16, false>(st, ws, c, mx, mt, p);
+    const bool extras = input_grads != nullptr || c.param_layout != MLP_PARAMS_ROW_MAJOR;
+    const cudaError_t e = extras ? launch_wide_train_extras(st, ws, c, op, mx, mt, p)
+                          : op == MLP_BF16 ? launch_wide_fmt<MLP_BF16, false>(st, ws, c, mx, mt, p)
+                                           : launch_wide_fmt<MLP_F16, false>(st, ws, c, mx, mt, p);
     *launches += 1;
     return e;
 }
-#else  // part 1: the forward entry point of the same shapes
+#elif MLPB200_WIDE_PART == 1  // the forward entry point of the same shapes
 
 bool tc_forward_wide_supported(const MlpConfig& c) { return wide_supported(c); }
 
