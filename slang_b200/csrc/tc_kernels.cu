@@ -207,8 +207,8 @@ struct WideTrainParams {
 // shapes): no targets, no derivatives, no gradient products.
 // F32S: fp32 parameter storage with 16-bit operands (weights converted while they are staged, pre-activations and
 // outputs not rounded); such networks run the builds with the activation chosen at run time.
-// XTRA: training builds that also write the input gradients (WideTrainParams::input_grads), write the weight
-// gradients in the tiled parameter layout and / or read targets of any width or type themselves; the plain training builds carry neither test (they cost 2.5 % at
+// XTRA: training builds that also write the input gradients (WideTrainParams::input_grads) and / or write the weight
+// gradients in the tiled parameter layout; the plain training builds carry neither test (they cost 2.5 % at
 // the benchmark shape when they were run-time options of one build).
 template <int FMT, int ACT, int NL, bool FWD, bool F32S = false, bool XTRA = false>
 __global__ void __launch_bounds__(wide::kThreads, 1)
@@ -238,9 +238,6 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t n_my_tiles = (p.n_tiles > blockIdx.x) ? (p.n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    // targets read by the epilogue itself instead of arriving by TMA: forward builds have none, the plain
-    // training builds always take them by TMA
-    const bool t_direct = FWD ? true : XTRA ? p.t_direct != 0 : false;
 
     // ---- set-up: barriers, tensor memory, weights and biases into shared memory ------------------
     if (threadIdx.x == 0) {
@@ -361,7 +358,7 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
             if (leader) {
                 mbar_expect_tx(&x_full[0], 8192);
                 tma_load_2d(smem + kX, &tmap_x, 0, (int32_t)(blockIdx.x * NS), &x_full[0]);
-                if (!t_direct) {
+                if (!p.t_direct) {
                     mbar_expect_tx(t_full, 8192);
                     tma_load_2d(smem + kDZ4, &tmap_t, 0, (int32_t)(blockIdx.x * NS), t_full);
                 }
@@ -508,7 +505,7 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                             // Both chains are past every product that read the other X buffer and dZ_4.
                             mbar_expect_tx(&x_full[b ^ 1u], 8192);
                             tma_load_2d(smem + kX + (b ^ 1u) * 8192u, &tmap_x, 0, (int32_t)(next_tile * NS), &x_full[b ^ 1u]);
-                            if (!t_direct) {
+                            if (!p.t_direct) {
                                 mbar_expect_tx(t_full, 8192);
                                 tma_load_2d(smem + kDZ4, &tmap_t, 0, (int32_t)(next_tile * NS), t_full);
                             }
@@ -541,7 +538,7 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
             if (*abort_flag && leader) {
                 // Give the copies still in flight a bounded time to land before the CTA exits.
                 mbar_drain(&x_full[(loads_issued - 1) & 1u], ((loads_issued - 1) >> 1) & 1u);
-                if (!t_direct) mbar_drain(t_full, (loads_issued - 1) & 1u);
+                if (!p.t_direct) mbar_drain(t_full, (loads_issued - 1) & 1u);
             }
         }
 #ifdef MLPB200_TRACE
@@ -670,7 +667,7 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
             //      and eight features: one 16-byte chunk of the target row, replaced in place by dZ_4 ----
             {
                 ok = ok && mbar_wait(out_full, it & 1u, abort_flag, p.status, kStatusEpiAcc);
-                if (!FWD && !t_direct) ok = ok && mbar_wait(t_full, it & 1u, abort_flag, p.status, kStatusEpiTarget);
+                if (!FWD && !p.t_direct) ok = ok && mbar_wait(t_full, it & 1u, abort_flag, p.status, kStatusEpiTarget);
                 if (!ok) break;
                 MLPB200_TRACE_AT(tr_on, 64u + tr_step * 4 + 0);
                 tc_fence_after();
@@ -704,7 +701,7 @@ learn_gradient_wide_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                 }
                 uint4* slot = (uint4*)(smem + kDZ4 + (uint32_t)s * 128u + ((((uint32_t)(fb >> 3)) ^ (uint32_t)(s & 7)) << 4));
                 float tf[8];
-                if (!t_direct) {
+                if (!p.t_direct) {
                     const uint4 tq = *slot;
                     const uint32_t tw[4] = {tq.x, tq.y, tq.z, tq.w};
 #pragma unroll
@@ -1211,7 +1208,7 @@ cudaError_t launch_learn_gradient_tc(cudaStream_t st, TcWorkspace* ws, const Mlp
     p.timing = ws->timing;
     p.outputs = nullptr;
     p.input_grads = input_grads;
-    const bool extras = input_grads != nullptr || c.param_layout != MLP_PARAMS_ROW_MAJOR || t_direct;
+    const bool extras = input_grads != nullptr || c.param_layout != MLP_PARAMS_ROW_MAJOR;
     const cudaError_t e = extras ? launch_wide_train_extras(st, ws, c, op, mx, mt, p)
                           : op == MLP_BF16 ? launch_wide_fmt<MLP_BF16, false>(st, ws, c, mx, mt, p)
                                            : launch_wide_fmt<MLP_F16, false>(st, ws, c, mx, mt, p);

@@ -87,14 +87,12 @@ template <> struct Cvt<MLP_BF16> {
     __device__ static __forceinline__ float lo(uint32_t p) { return __uint_as_float(p << 16); }
     __device__ static __forceinline__ float hi(uint32_t p) { return __uint_as_float(p & 0xffff0000u); }
     __device__ static __forceinline__ uint16_t one() { return 0x3F80; }
-    // max(z, 0) of a pair; a zero z (either sign) comes out as a negative zero.  The zero test is on the bits:
-    // adding 0x7fff to a half's magnitude sets its top bit exactly when the magnitude is not zero.
+    // max(z, 0) of a pair; a zero z (either sign) comes out as a negative zero
     __device__ static __forceinline__ uint32_t relu_marked(uint32_t z2)
     {
-        const __nv_bfloat162 z = *reinterpret_cast<const __nv_bfloat162*>(&z2);
-        const __nv_bfloat162 r = __hmax2(z, __floats2bfloat162_rn(0.0f, 0.0f));
-        const uint32_t zero_mark = (((z2 & 0x7fff7fffu) + 0x7fff7fffu) & 0x80008000u) ^ 0x80008000u;
-        return (*reinterpret_cast<const uint32_t*>(&r) & 0x7fff7fffu) | zero_mark;
+        const __nv_bfloat162 z = *reinterpret_cast<const __nv_bfloat162*>(&z2), zero = __floats2bfloat162_rn(0.0f, 0.0f);
+        const __nv_bfloat162 r = __hmax2(z, zero);
+        return (*reinterpret_cast<const uint32_t*>(&r) & 0x7fff7fffu) | (__heq2_mask(z, zero) & 0x80008000u);
     }
     // 0xffff in the halves whose value is above zero
     __device__ static __forceinline__ uint32_t positive_mask(uint32_t a2)
@@ -121,10 +119,9 @@ template <> struct Cvt<MLP_F16> {
     __device__ static __forceinline__ uint16_t one() { return 0x3C00; }
     __device__ static __forceinline__ uint32_t relu_marked(uint32_t z2)
     {
-        const __half2 z = *reinterpret_cast<const __half2*>(&z2);
-        const __half2 r = __hmax2(z, __floats2half2_rn(0.0f, 0.0f));
-        const uint32_t zero_mark = (((z2 & 0x7fff7fffu) + 0x7fff7fffu) & 0x80008000u) ^ 0x80008000u;
-        return (*reinterpret_cast<const uint32_t*>(&r) & 0x7fff7fffu) | zero_mark;
+        const __half2 z = *reinterpret_cast<const __half2*>(&z2), zero = __floats2half2_rn(0.0f, 0.0f);
+        const __half2 r = __hmax2(z, zero);
+        return (*reinterpret_cast<const uint32_t*>(&r) & 0x7fff7fffu) | (__heq2_mask(z, zero) & 0x80008000u);
     }
     __device__ static __forceinline__ uint32_t positive_mask(uint32_t a2)
     {
