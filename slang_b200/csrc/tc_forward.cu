@@ -303,12 +303,18 @@ forward_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
                     const int out = G::out_dim(l);
                     const float* bl = s_bias + l * 128;
                     const uint64_t row_index = (uint64_t)tile * 128u + (uint64_t)r;
+                    // The accumulator is read 16 columns at a time, one read ahead: the next piece's read is issued
+                    // as soon as the current piece has arrived and runs under the current piece's arithmetic.
+                    const int kPieces = G::out_dim(l) / CS / 16;
+                    uint32_t vbuf[2][16];
+                    tmem_ld_32x16(t_acc + (uint32_t)(sub * (G::out_dim(l) / CS)), vbuf[0]);
 #pragma unroll
-                    for (int cc = 0; cc < G::out_dim(l) / CS; cc += 16) {
+                    for (int pc = 0; pc < kPieces; ++pc) {
+                        const int cc = pc * 16;
                         const int c0 = sub * (G::out_dim(l) / CS) + cc;  // this warp's share of the columns
-                        uint32_t v[16];
-                        tmem_ld_32x16(t_acc + (uint32_t)c0, v);
+                        uint32_t (&v)[16] = vbuf[pc & 1];
                         tmem_ld_wait();
+                        if (pc + 1 < kPieces) tmem_ld_32x16(t_acc + (uint32_t)(c0 + 16), vbuf[(pc + 1) & 1]);
                         // bias (packed fp32 adds) and rounding to the storage type, two values per register
                         uint32_t zp[8];
 #pragma unroll
