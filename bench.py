@@ -653,6 +653,13 @@ def main():
     # the learn_gradient phase includes the 8-byte clear of the loss words that precedes the kernel
     kernel_ms = float(np.mean([r["learn_gradient_ms"] for r in phase_rows]))
     phases = {k: float(np.mean([r[k] for r in phase_rows])) for k in phase_rows[0]}
+    if world > 1:
+        # every rank's own GPU: its clock record and its learnGradient time (the step waits for the slowest rank)
+        mine = {"rank": rank, "sm_mhz": clocks["sm_mhz"], "reasons": clocks["reasons"], "learn_gradient_ms": kernel_ms}
+        gathered = [None] * world
+        dist.all_gather_object(gathered, mine)
+        clocks["per_rank"] = gathered
+        clocks["reasons"] = sorted(set(r for g in gathered for r in g["reasons"]))
     if args.log_jsonl and rank == 0:
         log = JsonlLogger(args.log_jsonl)
         for i, r in enumerate(phase_rows):
