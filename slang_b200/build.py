@@ -82,11 +82,30 @@ def _stale(obj, src, depfile):
     return False
 
 
-def build(force=False, verbose=False, jobs=None):
+# Components a build may leave out (--without): their units are replaced by stubs that keep every declared
+# symbol and answer MLP_E_NOT_AVAILABLE.
+OPTIONAL = {"comm": ["comm"], "permuto": ["permuto"], "tile_mma": ["tile_mma"]}
+
+
+def build(force=False, verbose=False, jobs=None, without=(), out=None):
+    """Builds the library.  `without`: names from OPTIONAL to leave out (then `out` must name another output
+    file: the in-tree library is always the full one)."""
     nvcc = _nvcc()
     os.makedirs(OBJDIR, exist_ok=True)
+    without = [w for w in without if w]
+    for w in without:
+        if w not in OPTIONAL:
+            raise ValueError("unknown component %r (optional components: %s)" % (w, ", ".join(sorted(OPTIONAL))))
+    if without and not out:
+        raise ValueError("a build without components needs its own output file (--out)")
+    skipped = {u for w in without for u in OPTIONAL[w]}
+    units = [u for u in UNITS if u[0] not in skipped]
+    if without:
+        units.append(("stubs_" + "_".join(sorted(without)), "component_stubs.cu",
+                      ["-DMLPB200_WITHOUT_" + w.upper() for w in sorted(without)]))
+    target = out or OUT
     objs, todo = [], []
-    for name, src, extra in UNITS:
+    for name, src, extra in units:
         s = os.path.join(CSRC, src)
         o = os.path.join(OBJDIR, name + ".o")
         d = os.path.join(OBJDIR, name + ".d")
@@ -118,13 +137,18 @@ def build(force=False, verbose=False, jobs=None):
         if verbose:
             print(" ".join(cmd), flush=True)
         subprocess.check_call(cmd)
-    if todo or not os.path.exists(OUT):
-        cmd = [nvcc] + ARCH + ["-shared", "-cudart", "static", "-o", OUT] + objs + ["-ldl"]
+    if todo or not os.path.exists(target):
+        cmd = [nvcc] + ARCH + ["-shared", "-cudart", "static", "-o", target] + objs + ["-ldl"]
         if verbose:
             print(" ".join(cmd), flush=True)
         subprocess.check_call(cmd)
-    return OUT
+    return target
+
+
+def _option(name):
+    return sys.argv[sys.argv.index(name) + 1] if name in sys.argv else None
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv,
+                without=(_option("--without") or "").split(","), out=_option("--out")))
