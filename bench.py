@@ -744,7 +744,7 @@ def main():
                          # DRAM read + write bytes of one launch: a constant from one profiler capture of a
                          # 2^20-sample launch (275.1 MB; the algorithmic bytes are 268.4 MB), scaled by this
                          # launch's samples.  Not measured in this run.
-                         "traffic": int(round(275.1e6 / 1048576 * count)), "traffic_static": True,
+                         "traffic": int(round(272.9e6 / 1048576 * count)), "traffic_static": True,
                          "traffic_source": "static: ncu capture of a 2^20-sample launch, scaled per sample",
                          "algorithmic_bytes": count * 256,
                          "peak_source": peaks["source"] + " (sustained bf16 GEMM; kernel timed inside the step loop)",
