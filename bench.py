@@ -742,7 +742,7 @@ def main():
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_sustained"], "unit": "TFLOP/s",
                          "frac": achieved / peaks["bf16_sustained"], "frac_of_burst": achieved / peaks["bf16_burst"],
                          # DRAM read + write bytes of one launch: a constant from one profiler capture of a
-                         # 2^20-sample launch (275.1 MB; the algorithmic bytes are 268.4 MB), scaled by this
+                         # 2^20-sample launch (272.9 MB; the algorithmic bytes are 268.4 MB), scaled by this
                          # launch's samples.  Not measured in this run.
                          "traffic": int(round(272.9e6 / 1048576 * count)), "traffic_static": True,
                          "traffic_source": "static: ncu capture of a 2^20-sample launch, scaled per sample",
