@@ -250,7 +250,7 @@ def bench_narrow(args):
     torch.cuda.set_stream(stream)
     device = Device(0, stream.cuda_stream)
     name = args.config
-    count = args.batch if args.batch != (1 << 26) else (1 << 20 if name == "c2" else 1 << 24)
+    count = args.batch if args.batch != (1 << 26) else {"c1": 4096, "c2": 1 << 20}.get(name, 1 << 24)
     line = measure_narrow(torch, device, dev_t, name, count, args.warmup, args.steps)
     print(json.dumps(line), flush=True)
     device.destroy()
@@ -263,7 +263,12 @@ def measure_narrow(torch, device, dev_t, name, count, warmup, steps):
     from slang_b200.api import Trainer
     cfg = C.named_config(name)
     gen = torch.Generator(device=dev_t); gen.manual_seed(11)
-    if name == "c2":
+    if name == "c1":
+        # the CPU-runnable parity configuration: a launch-bound step (4096 samples), reported as ms per step
+        x = (torch.rand((count, 2), device=dev_t, generator=gen) * 2 - 1).contiguous()
+        t = (torch.sin(np.pi * x[:, 0]) * torch.cos(np.pi * x[:, 1])).reshape(count, 1).contiguous()
+        workload = "fp32 MLP 2-16-16-16-1 ReLU, MSE, Adam lr 1e-3 (one thread per sample)"
+    elif name == "c2":
         x = torch.rand((count, 4), device=dev_t, generator=gen)
         w = torch.from_numpy(C.unit_vectors(1234, 4, 4)).to(dev_t)
         t = torch.sin(2 * np.pi * (x @ w.t())).contiguous()
@@ -283,6 +288,7 @@ def measure_narrow(torch, device, dev_t, name, count, warmup, steps):
         workload = "fp16 MLP enc(2->32)-64-64-64-3 ReLU, sigmoid out, L2, Adam lr 1e-2, 4096x4096 grid"
     tr = Trainer(device, cfg, C.init_params(cfg, seed=1, scheme="xavier" if name == "c2" else "kaiming"))
     impl = tr.k_learn.implementation
+    kernel_name = "learn_gradient_narrow_kernel" if impl == "tcgen05" else "learn_gradient_simt_kernel"
     flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev_t)
 
     def step():
@@ -325,14 +331,23 @@ def measure_narrow(torch, device, dev_t, name, count, warmup, steps):
     flops = C.flops_per_sample(cfg, training=True)
     achieved = flops * count / (kms * 1e-3) / 1e12
     line = {"metric": METRIC, "value": count / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": steps, "warmup": warmup,
-            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32" if name == "c1" else "f16", "data": "synthetic",
             "config": {"workload": workload, "global_batch": count, "l2": "512 MB written between timed steps"},
             "gpu_launches": launches, "implementation": impl,
             "forward": {"ms": fms, "samples_per_s": count / (fms * 1e-3), "implementation": tr.k_forward.implementation},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_burst"], "unit": "TFLOP/s",
-                         "frac": achieved / peaks["bf16_burst"], "traffic": None, "kernel": "learn_gradient_narrow_kernel",
+                         "frac": achieved / peaks["bf16_burst"], "traffic": None, "kernel": kernel_name,
                          "kernel_ms": kms, "flop_per_sample": flops, "peak_source": peaks["source"] + " (burst; kernel timed alone)"},
             "loss": {"max": mx, "mean": sm / count}}
+    if name == "c1":
+        # launch- and latency-bound: the honest yardstick is HBM bytes (12 B per sample plus the parameters), which it is nowhere near
+        _, _, total = C.param_layout(cfg)
+        bytes_step = count * 12 + total * 8
+        gbs = bytes_step / (kms * 1e-3) / 1e9
+        line["roofline"] = {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
+                            "traffic": None, "kernel": kernel_name, "kernel_ms": kms, "flop_per_sample": flops,
+                            "peak_source": peaks["source"], "note": "launch- and latency-bound at 4096 samples per step"}
     del x, t, out, flush
     return line
 
@@ -534,7 +549,7 @@ def main():
     if args.impl == "reference":
         reference_arm(args, rank)
         return
-    if args.config in ("c2", "c3"):
+    if args.config in ("c1", "c2", "c3"):
         if rank == 0:
             bench_narrow(args)
         return
@@ -774,15 +789,16 @@ def main():
                                     "kind": "one thread per sample on the same GPU (the example kernels' structure, this library's learnGradient_simt)",
                                     "sample": "%d samples, learnGradient + adjustParameters once" % n_simt}
         if world == 1 and not args.no_sub:
-            # The other configurations under the same clock, in this process: configurations 2 and 3
+            # The other configurations under the same clock, in this process: configurations 1, 2 and 3
             # at their stated sizes (training step and forward), configuration 5 at two batch sizes per width.
             del xs, ts
             torch.cuda.empty_cache()
             sub = {}
-            for name, n in (("c2", 1 << 20), ("c3", 1 << 24)):
+            for name, n in (("c1", 4096), ("c2", 1 << 20), ("c3", 1 << 24)):
                 r = measure_narrow(torch, device, dev_t, name, n, 3, 5)
                 sub[name] = {"samples_per_s": r["value"], "ms_per_step": r["ms_per_step"], "kernel_ms": r["roofline"]["kernel_ms"],
-                             "tflops": r["roofline"]["achieved"], "roofline_frac_of_burst": r["roofline"]["frac"],
+                             "tflops": r["roofline"]["flop_per_sample"] * n / (r["roofline"]["kernel_ms"] * 1e-3) / 1e12,
+                             "roofline_frac_of_burst": r["roofline"]["flop_per_sample"] * n / (r["roofline"]["kernel_ms"] * 1e-3) / 1e12 / peaks["bf16_burst"],
                              "forward_samples_per_s": r["forward"]["samples_per_s"], "global_batch": n,
                              "implementation": r["implementation"], "workload": r["config"]["workload"]}
             pts = measure_forward_points(torch, device, dev_t, (16, 32, 64, 128), (1 << 20, 1 << 24), 3, 5)
