@@ -114,7 +114,7 @@ struct Geometry {
     static_assert((DH / CS) % 16 == 0 && (DOUT / CS) % 16 == 0, "column split");
 };
 
-// CPS: CTAs per SM the build is sized for (the narrow widths run two CTAs of three chains each: two control
+// CPS: CTAs per SM the build is sized for (the narrow widths run three CTAs of two chains each: three control
 // warps walk their chains independently).
 // NCW: control warps (1 or 2).
 template <int DIN, int DH, int DOUT, int NL, int FMT, int ACT, int OUT_ACT, int NCH, int CS, int CPS = 1, int NCW = 1>
@@ -478,8 +478,8 @@ cudaError_t launch_forward_tc(cudaStream_t st, TcWorkspace* ws, const MlpConfig&
     // chains per CTA, column split, CTAs per SM, control warps: the measured best per width
 #define MLPB200_FWD(W_, FMT_, NCH_, CS_, CPS_, NCW_) \
     if (!wide && w == W_ && c.dtype == FMT_) e = launch_fwd<W_, W_, W_, 4, FMT_, MLP_ACT_RELU, MLP_ACT_IDENTITY, NCH_, CS_, CPS_, NCW_>(st, ws, c, a, err);
-    MLPB200_FWD(16, MLP_F16, 3, 1, 2, 1) MLPB200_FWD(32, MLP_F16, 3, 1, 2, 1) MLPB200_FWD(64, MLP_F16, 6, 1, 1, 2) MLPB200_FWD(128, MLP_F16, 2, 2, 1, 1)
-    MLPB200_FWD(16, MLP_BF16, 3, 1, 2, 1) MLPB200_FWD(32, MLP_BF16, 3, 1, 2, 1) MLPB200_FWD(64, MLP_BF16, 6, 1, 1, 2) MLPB200_FWD(128, MLP_BF16, 2, 2, 1, 1)
+    MLPB200_FWD(16, MLP_F16, 2, 1, 3, 1) MLPB200_FWD(32, MLP_F16, 2, 1, 3, 1) MLPB200_FWD(64, MLP_F16, 6, 1, 1, 2) MLPB200_FWD(128, MLP_F16, 2, 2, 1, 1)
+    MLPB200_FWD(16, MLP_BF16, 2, 1, 3, 1) MLPB200_FWD(32, MLP_BF16, 2, 1, 3, 1) MLPB200_FWD(64, MLP_BF16, 6, 1, 1, 2) MLPB200_FWD(128, MLP_BF16, 2, 2, 1, 1)
 #undef MLPB200_FWD
     if (wide && c.dtype == MLP_BF16) e = launch_fwd<64, 128, 64, 5, MLP_BF16, MLP_ACT_GELU_TANH, MLP_ACT_IDENTITY, 2, 2>(st, ws, c, a, err);
     if (wide && c.dtype == MLP_F16) e = launch_fwd<64, 128, 64, 5, MLP_F16, MLP_ACT_GELU_TANH, MLP_ACT_IDENTITY, 2, 2>(st, ws, c, a, err);
